@@ -1,0 +1,81 @@
+// Shared helpers of the sm_100a kernels: dtype codes, conversions, reductions and the
+// error channel of the C entry points.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+// dtype codes shared with the Python side (ops.py).
+#define CO_F32 0
+#define CO_BF16 1
+
+#define CO_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Error channel: every entry point returns 0 on success; otherwise a message is left
+// in a thread-local buffer that coheryn_last_error() hands out.
+void co_set_error(const char* fmt, ...);
+#define CO_FAIL(...)                 \
+  do {                               \
+    co_set_error(__VA_ARGS__);       \
+    return 1;                        \
+  } while (0)
+void co_count_launch();
+#define CO_CHECK_LAUNCH(name)                                                        \
+  do {                                                                               \
+    co_count_launch();                                                               \
+    cudaError_t e__ = cudaGetLastError();                                            \
+    if (e__ != cudaSuccess) CO_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float co_to_float(T v);
+template <>
+__device__ __forceinline__ float co_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float co_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T>
+__device__ __forceinline__ T co_from_float(float v);
+template <>
+__device__ __forceinline__ float co_from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 co_from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// Loads element i of an array whose dtype is only known at run time (small vectors:
+// norm weights, biases).
+__device__ __forceinline__ float co_load_any(const void* p, int dtype, size_t i) {
+  return dtype == CO_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+
+__device__ __forceinline__ float co_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float co_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum with a fixed combination order (warp shuffles, then warp 0 adds the
+// per-warp partials in order): the result does not depend on scheduling.
+__device__ __forceinline__ float co_block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = co_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = co_warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}

@@ -1,0 +1,263 @@
+"""Python face of the CUDA kernels: every function takes torch tensors that live on the
+GPU, checks them, and launches a kernel of this package's own library on the current
+CUDA stream.  There is no other implementation behind these functions: without a GPU
+or without the compiled library they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+c_void_p, c_int, c_long, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def require_gpu() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("this engine runs on a CUDA GPU (sm_100a) only; "
+                          "torch.cuda.is_available() is False and there is no CPU path")
+
+
+_core = None
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = build.core_library()
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        _core = lib
+    return _core
+
+
+def launch_count() -> int:
+    """Kernel launches made through the core library since it was loaded."""
+    return int(core().coheryn_launch_count())
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not handled by the kernels") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(lib, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib.coheryn_last_error().decode("utf-8", "replace"))
+
+
+def _dev(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel operands must be CUDA tensors")
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+# ------------------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] as float32.  An id outside the table sets status to 1."""
+    _dev(table, ids, out, status)
+    _i32(ids, "ids")
+    V, H = table.shape
+    T = ids.numel()
+    assert out.dtype == torch.float32 and out.shape == (T, H) and out.is_contiguous()
+    assert table.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_embed_gather(_ptr(table), _code(table), _ptr(ids), _ptr(out), c_int(T),
+                                         c_int(H), c_int(V), _ptr(status), _stream()))
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, update: bool = True) -> None:
+    """x = resid (+ delta); resid = x if update; out = x / sqrt(mean(x^2) + eps) * weight.
+    With ``rows`` only those rows are read (out[r] comes from row rows[r]) and the
+    residual is left as it is."""
+    _dev(resid, delta, weight, out, rows)
+    H = resid.shape[-1]
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    assert out.is_contiguous() and out.shape[-1] == H and weight.shape == (H,)
+    n = out.shape[0]
+    if rows is not None:
+        _i32(rows, "rows")
+        assert rows.numel() == n
+        update = False
+    else:
+        assert resid.shape[0] >= n
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape == resid.shape
+    lib = core()
+    _check(lib, lib.coheryn_add_rmsnorm(
+        _ptr(resid), _ptr(delta), c_int(_code(delta) if delta is not None else F32), _ptr(rows),
+        _ptr(weight), c_int(_code(weight)), c_float(eps), _ptr(out), c_int(_code(out)), c_int(n),
+        c_int(H), c_int(1 if (update and delta is not None) else 0), _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m, j] = silu(gate_up[m, j]) * gate_up[m, I + j]."""
+    _dev(gate_up, out)
+    M, I2 = gate_up.shape
+    assert I2 % 2 == 0 and out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
+    assert gate_up.is_contiguous() and out.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_silu_mul(_ptr(gate_up), _ptr(out), c_int(_code(out)), c_int(M),
+                                     c_int(I2 // 2), _stream()))
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                  slots: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                  v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                  rotary_dim: int, page_size: int) -> None:
+    """Rotate q (in place) and k by position; write rotated k and v into cache pages
+    laid out [page, kv head, slot, head_dim] at ``slots`` (page * page_size + offset).
+    Without caches (a layer that reads another layer's cache) the buffer holds query
+    heads only and they are rotated in place."""
+    _dev(qkv, positions, cos_sin, slots, k_cache, v_cache)
+    _i32(positions, "positions")
+    T = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim
+    if rotary_dim:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+        assert cos_sin.shape[1:] == (rotary_dim // 2, 2)
+    write = k_cache is not None
+    if write:
+        _i32(slots, "slots")
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+        assert k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+    else:
+        assert num_kv_heads == 0, "without a cache to write, only query heads are rotated"
+    lib = core()
+    _check(lib, lib.coheryn_rope_kv_write(
+        _ptr(qkv), c_int(_code(qkv)), _ptr(positions), _ptr(cos_sin), _ptr(slots), _ptr(k_cache),
+        _ptr(v_cache), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(rotary_dim), c_int(page_size), c_int(1 if write else 0), _stream()))
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = x @ w.T (+ bias) with float32 FMA accumulation (no tensor cores)."""
+    _dev(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape == (N, K) and w.is_contiguous() and out.shape == (M, N)
+    assert x.stride(1) == 1 and out.stride(1) == 1
+    if bias is not None:
+        assert bias.shape == (N,) and bias.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_gemm_simt(
+        _ptr(x), c_int(_code(x)), _ptr(w), c_int(_code(w)), _ptr(bias),
+        c_int(_code(bias) if bias is not None else F32), _ptr(out), c_int(_code(out)), c_int(M),
+        c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)), _stream()))
+
+
+def attention_simple(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     block_tables: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
+                     num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                     window: Optional[int], scale: float) -> None:
+    """Causal attention of each token over its request's cache pages (float32 math).
+    ``q`` may be a column slice of a wider buffer (its row stride is honoured)."""
+    _dev(q, out, k_cache, v_cache, block_tables, token_req, positions)
+    _i32(block_tables, "block_tables"); _i32(token_req, "token_req"); _i32(positions, "positions")
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * head_dim
+    assert k_cache.dtype == q.dtype and out.dtype == q.dtype
+    lib = core()
+    _check(lib, lib.coheryn_attention_simple(
+        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_int(_code(q)), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(token_req),
+        _ptr(positions), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_int(window or 0), c_float(scale), _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[r] = lowest index of the maximum of logits[r]; non-finite logits set status 2."""
+    _dev(logits, out, status)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    _i32(out, "out")
+    lib = core()
+    _check(lib, lib.coheryn_argmax(_ptr(logits), c_long(logits.stride(0)), c_int(R), c_int(V),
+                                   _ptr(out), _ptr(status), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """Temperature / top-k / top-p sampling of one token per row from host-made draws."""
+    _dev(logits, temperature, top_k, top_p, uniform, out, status)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32
+    assert uniform.dtype == torch.float64
+    _i32(top_k, "top_k"); _i32(out, "out")
+    lib = core()
+    _check(lib, lib.coheryn_sample(_ptr(logits), c_long(logits.stride(0)), c_int(R), c_int(V),
+                                   _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
+                                   _ptr(out), _ptr(status), _stream()))
+
+
+# ------------------------------------------------------------------------------------
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ w.T (+ bias), float32 accumulation.  float32 operands use FMA on the CUDA
+    cores (no reduced-precision tensor mode); bfloat16 operands use the tensor-core
+    kernels where the shape allows and the FMA kernel otherwise."""
+    M, N = x.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    if M == 0:
+        return out
+    gemm_simt(x, w, bias, out)
+    return out
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step,
+              group: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+              window: Optional[int], scale: float) -> None:
+    """Attention of every token of the step over its request's cache pages of ``group``
+    (``step`` is a StepContext).  Chooses the kernel by dtype and shape."""
+    attention_rows(q, out, k_cache, v_cache, step.block_tables[group], step.token_req,
+                   step.positions, num_heads, num_kv_heads, head_dim, page_size, window, scale,
+                   cu_q=step.cu_q, kv_lens=step.kv_lens, q_lens=step.q_lens)
+
+
+def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads, num_kv_heads,
+                   head_dim, page_size, window, scale, cu_q=None, kv_lens=None, q_lens=None) -> None:
+    """Attention of rows (request token_req[i] at position positions[i]) over cache pages.
+    When the rows are whole runs of consecutive positions per request (``cu_q``,
+    ``kv_lens``, host ``q_lens``), the bfloat16 tensor-core kernels can take them."""
+    attention_simple(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads,
+                     num_kv_heads, head_dim, page_size, window, scale)
+
+
+def gated_silu_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x @ Wg.T) * (x @ Wu.T) for w_gate_up = [Wg; Wu] stacked by rows."""
+    M = x.shape[0]
+    I = w_gate_up.shape[0] // 2
+    gu = linear(x, w_gate_up)
+    out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+    if M:
+        silu_mul(gu, out)
+    return out

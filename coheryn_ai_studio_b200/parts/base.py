@@ -1,0 +1,179 @@
+"""Interfaces of the parts a layer is assembled from, and the registries that map a
+:class:`PartSpec` kind to a class.
+
+A part is built from its parameters alone (``cls(**spec.params)`` plus the runtime's
+dtype and device); it names the tensors it wants (:meth:`Part.tensor_specs`), receives
+them (:meth:`Part.bind`) and runs on the device.  Roles:
+
+* mixer         – ``forward(x, step, cache) -> y``; moves information between the tokens
+                  of a request; says what cache it needs (:meth:`Mixer.cache_requirement`).
+* feed_forward  – ``forward(x, step) -> y``; token-wise.
+* norm          – ``forward(residual, delta, out_rows=None) -> normed``; adds ``delta`` to
+                  the float32 residual stream in place and normalises.
+* position      – owns what a mixer needs to encode positions (here: a rotation table).
+* arrangement   – wires mixer, feed-forward and norms into a block.
+
+New kinds are added with the ``register_*`` functions; nothing else has to change.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.spec import PartSpec
+from ..weights.spec import TensorSpec
+
+
+@dataclass(frozen=True)
+class Runtime:
+    """Where and in which precision the parts run."""
+
+    dtype: torch.dtype            # torch.float32 or torch.bfloat16: activations, matrices, cache
+    device: torch.device
+
+
+# ------------------------------------------------------------------ cache requirements
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values of every position (``window`` None) or of the last ``window``
+    positions, kept in pages."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class FixedState:
+    """State of fixed size per request, zeroed when the request is admitted."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class LayerCache:
+    """What a mixer gets for one execution of its layer.
+
+    Paged: ``k``/``v`` are ``[pages, kv heads, page_size, head_dim]`` views of the
+    group's pool for this schedule entry; ``group`` indexes ``step.block_tables`` and
+    ``step.slots``; ``writes`` is False when the entry reads another entry's cache.
+    Fixed state: ``state`` is ``[slots, *shape]``; ``step.state_slots`` gives each
+    request's slot."""
+
+    kind: str                      # "paged" | "state"
+    group: int = -1
+    page_size: int = 0
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    writes: bool = True
+    state: Optional[torch.Tensor] = None
+
+
+@dataclass
+class StepContext:
+    """One batch of (request, its next tokens) as the device sees it.  Requests are
+    numbered 0..B-1 in the order of the batch; their tokens are laid out one request
+    after the other."""
+
+    num_tokens: int
+    num_requests: int
+    token_ids: torch.Tensor           # [T] int32
+    positions: torch.Tensor           # [T] int32, absolute position of each token
+    token_req: torch.Tensor           # [T] int32, batch index of each token's request
+    cu_q: torch.Tensor                # [B+1] int32, token offsets of the requests
+    kv_lens: torch.Tensor             # [B] int32, tokens of each request after this step
+    block_tables: List[torch.Tensor]  # per cache group: [B, max_blocks] int32
+    slots: List[torch.Tensor]         # per cache group: [T] int32 page*page_size+offset
+    state_slots: torch.Tensor         # [B] int32
+    q_lens: List[int] = field(default_factory=list)       # host copies
+    kv_lens_host: List[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_kv_len: int = 0
+
+
+# ------------------------------------------------------------------------------- parts
+class Part:
+    def __init__(self, runtime: Runtime):
+        self.runtime = runtime
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        """Local tensor name -> what is expected of it."""
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Receive the loaded tensors (same local names); may fuse or re-lay them."""
+
+
+class Mixer(Part):
+    def cache_requirement(self):
+        """PagedKV, FixedState or None."""
+        return None
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Position(Part):
+    pass
+
+
+class Arrangement:
+    """Wires the parts of one layer.  ``forward`` takes and returns the pair
+    (float32 residual stream, pending delta not yet added to it)."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
+                 feed_forward_norm: Norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def parts(self) -> Dict[str, Part]:
+        """Tensor-name component -> part (names follow the checkpoint)."""
+        raise NotImplementedError
+
+    def forward(self, residual, delta, step: StepContext, cache: Optional[LayerCache]):
+        raise NotImplementedError
+
+
+MIXERS: Dict[str, type] = {}
+FEED_FORWARDS: Dict[str, type] = {}
+NORMS: Dict[str, type] = {}
+POSITIONS: Dict[str, type] = {}
+ARRANGEMENTS: Dict[str, type] = {}
+
+
+def _register(table: Dict[str, type], role: str, kind: str, cls: type, replace: bool) -> None:
+    if not kind:
+        raise ValueError(f"a {role} needs a non-empty kind")
+    if kind in table and not replace:
+        raise ValueError(f"{role} kind {kind!r} is already registered")
+    table[kind] = cls
+
+
+def register_mixer(kind, cls, replace=False): _register(MIXERS, "mixer", kind, cls, replace)
+def register_feed_forward(kind, cls, replace=False): _register(FEED_FORWARDS, "feed_forward", kind, cls, replace)
+def register_norm(kind, cls, replace=False): _register(NORMS, "norm", kind, cls, replace)
+def register_position(kind, cls, replace=False): _register(POSITIONS, "position", kind, cls, replace)
+def register_arrangement(kind, cls, replace=False): _register(ARRANGEMENTS, "arrangement", kind, cls, replace)
+
+
+def build_part(table: Dict[str, type], role: str, spec: PartSpec, runtime: Runtime, **extra):
+    try:
+        cls = table[spec.kind]
+    except KeyError:
+        raise ValueError(f"no {role} of kind {spec.kind!r} is registered "
+                         f"(registered: {', '.join(sorted(table)) or 'none'})") from None
+    return cls(runtime=runtime, **spec.params, **extra)

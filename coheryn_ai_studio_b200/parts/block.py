@@ -1,0 +1,27 @@
+"""Arrangements: how a layer's mixer, feed-forward and norms are wired.
+
+``prenorm_residual`` is the layout of crates/coheryn-engine/src/inference.rs:440-540:
+x += mixer(norm(x)); x += feed_forward(norm(x)).  The residual stream is float32; each
+sub-layer's output is handed on as a pending ``delta`` that the NEXT norm adds to the
+stream while it normalises, so the sum and the norm cost one pass over the row.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+from .base import Arrangement, Part, register_arrangement
+
+
+class PreNormResidual(Arrangement):
+    def parts(self) -> Dict[str, Part]:
+        return {"input_layernorm": self.mixer_norm, "self_attn": self.mixer,
+                "post_attention_layernorm": self.feed_forward_norm, "mlp": self.feed_forward}
+
+    def forward(self, residual, delta, step, cache):
+        h = self.mixer_norm.forward(residual, delta)
+        mixed = self.mixer.forward(h, step, cache)
+        h = self.feed_forward_norm.forward(residual, mixed)
+        return residual, self.feed_forward.forward(h, step)
+
+
+register_arrangement("prenorm_residual", PreNormResidual)

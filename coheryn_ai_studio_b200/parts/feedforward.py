@@ -1,0 +1,39 @@
+"""Dense gated feed-forward (SwiGLU): y = W_down (silu(W_gate x) * (W_up x)), no biases,
+silu(g) = g / (1 + exp(-g)) in float32
+(crates/coheryn-engine/src/inference.rs:516-540, crates/coheryn-engine/src/cpu.rs:74-78).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..weights.spec import TensorSpec
+from .base import FeedForward, Runtime, StepContext, register_feed_forward
+
+
+class GatedMLP(FeedForward):
+    def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, activation: str):
+        super().__init__(runtime)
+        if activation != "silu":
+            raise ValueError(f"gated feed-forward: activation {activation!r} is not implemented (silu only)")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        return {"gate_proj.weight": TensorSpec((I, H)), "up_proj.weight": TensorSpec((I, H)),
+                "down_proj.weight": TensorSpec((H, I))}
+
+    def bind(self, tensors):
+        # One matrix product for gate and up: gate rows first, up rows after them.
+        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"]
+
+    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+        act = ops.gated_silu_linear(x, self.w_gate_up)
+        return ops.linear(act, self.w_down)
+
+
+register_feed_forward("gated_mlp", GatedMLP)

@@ -1,0 +1,297 @@
+"""Each kernel alone against a plain float32/float64 restatement of the same operation,
+at sizes other than the engine tests' (odd widths, head sizes in steps of 16, groups of
+1..7, vocabularies that are no power of two)."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from coheryn_ai_studio_b200 import ops as o
+    return o
+
+
+def t32(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(table_dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(301, 72, generator=g).to(table_dtype).to(DEV)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().embed_gather(table, ids, out, status)
+    assert torch.equal(out, table.float()[ids.long()]) and status.item() == 0
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=DEV)
+    ops().embed_gather(table, bad, out[:2], status)
+    assert status.item() == 1
+
+
+@pytest.mark.parametrize("H", [72, 1536, 3000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(H, dtype):
+    rng = np.random.default_rng(H)
+    resid = rng.standard_normal((7, H)).astype(np.float32) * 3
+    delta = rng.standard_normal((7, H)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    d_dev = t32(delta).to(dtype)
+    x = resid + d_dev.float().cpu().numpy()
+    ref = plain.rms_norm(x, w, 1e-5)
+    r_dev = t32(resid)
+    out = torch.empty(7, H, dtype=dtype, device=DEV)
+    for wt in (t32(w), t32(w).to(torch.bfloat16)) if dtype == torch.bfloat16 else (t32(w),):
+        r_dev = t32(resid)
+        ops().add_rmsnorm(r_dev, d_dev, wt, 1e-5, out)
+        refw = plain.rms_norm(x, wt.float().cpu().numpy(), 1e-5)
+        tol = 2e-6 * np.abs(refw).max() if dtype == torch.float32 else 2 ** -8 * np.abs(refw).max()
+        assert np.abs(out.float().cpu().numpy() - refw).max() <= tol
+        assert np.abs(r_dev.cpu().numpy() - x).max() == 0.0       # residual updated in float32
+    # gathered rows, no delta, residual untouched
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    r_dev = t32(resid)
+    out3 = torch.empty(3, H, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(r_dev, None, t32(w), 1e-5, out3, rows=rows)
+    ref3 = plain.rms_norm(resid[[6, 0, 3]], w, 1e-5)
+    tol = 2e-6 * np.abs(ref3).max() if dtype == torch.float32 else 2 ** -8 * np.abs(ref3).max()
+    assert np.abs(out3.float().cpu().numpy() - ref3).max() <= tol
+    assert torch.equal(r_dev, t32(resid))
+    assert ref.shape == (7, H)
+
+
+@pytest.mark.parametrize("shape", [(1, 50, 37), (5, 129, 200), (67, 96, 1000), (130, 300, 77)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_simt(shape, dtype):
+    M, N, K = shape
+    rng = np.random.default_rng(M * N)
+    x = t32(rng.standard_normal((M, K)).astype(np.float32)).to(dtype)
+    w = t32(rng.standard_normal((N, K)).astype(np.float32)).to(dtype)
+    b = t32(rng.standard_normal(N).astype(np.float32))
+    ref = x.double().cpu() @ w.double().cpu().T + b.double().cpu()
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops().gemm_simt(x, w, b, out)
+    assert (out.double().cpu() - ref).abs().max() <= 1e-5 * ref.abs().max() + 1e-5
+    # a strided input (a column slice of a wider buffer)
+    wide = torch.zeros(M, K + 9, dtype=dtype, device=DEV)
+    wide[:, 4:4 + K] = x
+    out2 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops().gemm_simt(wide[:, 4:4 + K], w, b, out2)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rows_do_not_depend_on_batch(dtype):
+    """A row's product is the same alone and inside a larger batch (bitwise)."""
+    rng = np.random.default_rng(1)
+    x = t32(rng.standard_normal((70, 160)).astype(np.float32)).to(dtype)
+    w = t32(rng.standard_normal((90, 160)).astype(np.float32)).to(dtype)
+    full = ops().linear(x, w)
+    for r in (0, 13, 69):
+        assert torch.equal(ops().linear(x[r:r + 1].contiguous(), w)[0], full[r])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    rng = np.random.default_rng(2)
+    gu = t32(rng.standard_normal((9, 2 * 77)).astype(np.float32) * 4).to(dtype)
+    out = torch.empty(9, 77, dtype=dtype, device=DEV)
+    ops().silu_mul(gu, out)
+    g = gu.float().cpu().numpy()
+    ref = plain.swiglu(g[:, :77], g[:, 77:])
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol * max(1, np.abs(ref).max())
+
+
+def paged_setup(rng, lens, nkv, hd, page_size, dtype, shuffle=True):
+    """Random keys/values for requests of the given lengths laid into shuffled pages."""
+    B = len(lens)
+    blocks = [-(-n // page_size) for n in lens]
+    total = sum(blocks) + 3
+    order = rng.permutation(total) if shuffle else np.arange(total)
+    kc = torch.zeros(total, nkv, page_size, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    bt = np.full((B, max(blocks)), -1, np.int32)
+    ks, vs = [], []
+    nxt = 0
+    for b, n in enumerate(lens):
+        k = torch.from_numpy(rng.standard_normal((n, nkv, hd)).astype(np.float32)).to(dtype)
+        v = torch.from_numpy(rng.standard_normal((n, nkv, hd)).astype(np.float32)).to(dtype)
+        ks.append(k.float().numpy()); vs.append(v.float().numpy())
+        for j in range(blocks[b]):
+            p = int(order[nxt]); nxt += 1
+            bt[b, j] = p
+            lo, hi = j * page_size, min(n, (j + 1) * page_size)
+            kc[p, :, :hi - lo] = k[lo:hi].permute(1, 0, 2).to(DEV)
+            vc[p, :, :hi - lo] = v[lo:hi].permute(1, 0, 2).to(DEV)
+    return kc, vc, t32(bt), ks, vs
+
+
+def attention_reference(q_rows, ks, vs, reqs, poss, nh, nkv, hd, window, scale):
+    """Plain attention of single rows: row i belongs to request reqs[i] at position poss[i]."""
+    out = np.zeros((len(reqs), nh * hd), np.float32)
+    for i, (b, p) in enumerate(zip(reqs, poss)):
+        first = max(0, p - window + 1) if window else 0
+        k = ks[b][first:p + 1].astype(np.float64)
+        v = vs[b][first:p + 1].astype(np.float64)
+        for h in range(nh):
+            g = h // (nh // nkv)
+            s = (k[:, g] @ q_rows[i, h * hd:(h + 1) * hd].astype(np.float64)) * scale
+            e = np.exp(s - s.max())
+            out[i, h * hd:(h + 1) * hd] = (e / e.sum()) @ v[:, g]
+    return out
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 16), (3, 1, 32, 16), (7, 7, 48, 8), (12, 2, 128, 16),
+                                            (5, 1, 80, 32), (6, 3, 112, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention(nh, nkv, hd, page, dtype, window):
+    rng = np.random.default_rng(nh * 100 + hd)
+    lens = [1, 130, 47, 64]
+    kc, vc, bt, ks, vs = paged_setup(rng, lens, nkv, hd, page, dtype)
+    # rows: a whole request, the tail of another, single last tokens of the rest
+    reqs = [0] + [1] * 30 + [2] * 47 + [3]
+    poss = [0] + list(range(100, 130)) + list(range(47)) + [63]
+    T = len(reqs)
+    q = torch.from_numpy(rng.standard_normal((T, nh * hd)).astype(np.float32)).to(dtype).to(DEV)
+    out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    scale = 1.0 / np.sqrt(hd)
+    ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
+                         nh, nkv, hd, page, window, scale)
+    ref = attention_reference(q.float().cpu().numpy(), ks, vs, reqs, poss, nh, nkv, hd, window, scale)
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -7
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key(dtype):
+    """One key among 700 is made to stand out (its score dominates): the output must be
+    that key's value.  Random weights alone would hide a kernel that skips far keys, a
+    page's edge or the window's first position."""
+    nh, nkv, hd, page = 4, 2, 64, 16
+    rng = np.random.default_rng(9)
+    n = 700
+    scale = 1.0 / np.sqrt(hd)
+    for target, window in [(3, None), (15, None), (16, None), (352, None), (n - 200, 200), (n - 201, 200)]:
+        kc, vc, bt, ks, vs = paged_setup(rng, [n], nkv, hd, page, dtype, shuffle=True)
+        q = rng.standard_normal((1, nh * hd)).astype(np.float32)
+        # make key[target] of every kv head parallel to the queries of its group, and long
+        p = int(bt[0, target // page].item()); o = target % page
+        for g in range(nkv):
+            qg = q[0, g * (nh // nkv) * hd:(g * (nh // nkv) + 1) * hd]
+            for h in range(g * (nh // nkv), (g + 1) * (nh // nkv)):
+                q[0, h * hd:(h + 1) * hd] = qg
+            kc[p, g, o] = torch.from_numpy(qg * 40 / np.linalg.norm(qg)).to(dtype).to(DEV) * 4
+            ks[0][target, g] = kc[p, g, o].float().cpu().numpy()
+        qd = t32(q).to(dtype)
+        out = torch.empty(1, nh * hd, dtype=dtype, device=DEV)
+        ops().attention_rows(qd, out, kc, vc, bt, t32(np.zeros(1, np.int32)), t32(np.asarray([n - 1], np.int32)),
+                             nh, nkv, hd, page, window, scale)
+        ref = attention_reference(qd.float().cpu().numpy(), ks, vs, [0], [n - 1], nh, nkv, hd, window, scale)
+        got = out.float().cpu().numpy()
+        assert np.abs(got - ref).max() <= (2e-5 if dtype == torch.float32 else 2 ** -6), (target, window)
+        inside = window is None or target > n - 1 - window
+        for h in range(nh):
+            hit = np.abs(got[0, h * hd:(h + 1) * hd] - vs[0][target, h // (nh // nkv)]).max() < 0.05
+            assert hit == inside, (target, window, h)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (3, 1, 32, 32), (5, 5, 48, 48), (2, 1, 64, 32)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_kv_write(nh, nkv, hd, rot, dtype):
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.position import RotateHalfRope
+    rng = np.random.default_rng(hd)
+    theta, T, page = 1e6, 11, 8
+    pos_part = RotateHalfRope(Runtime(dtype, torch.device(DEV)), hd, rot, theta, 600)
+    positions = np.array([0, 1, 7, 511, 300, 2, 3, 4, 5, 6, 599], np.int32)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.from_numpy(rng.standard_normal((T, width)).astype(np.float32)).to(dtype)
+    src = qkv.float().numpy().copy()
+    dev = qkv.to(DEV)
+    kc = torch.zeros(5, nkv, page, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    slots = rng.permutation(5 * page)[:T].astype(np.int32)
+    ops().rope_kv_write(dev, t32(positions), pos_part.cos_sin(), t32(slots), kc, vc, nh, nkv, hd, rot, page)
+    got = dev.float().cpu().numpy()
+    tol = 3e-6 if dtype == torch.float32 else 2 ** -7
+    def rotated(x):  # x: [T, heads*hd]; rotate the first ``rot`` of each head
+        h = x.reshape(T, -1, hd).copy()
+        part = plain.rope(h[:, :, :rot].reshape(T, -1), positions, rot, theta).reshape(T, -1, rot)
+        h[:, :, :rot] = part
+        return h.reshape(T, -1)
+    q_ref = rotated(src[:, :nh * hd])
+    k_ref = rotated(src[:, nh * hd:(nh + nkv) * hd]).reshape(T, nkv, hd)
+    v_ref = src[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    scale = max(1.0, np.abs(q_ref).max())
+    assert np.abs(got[:, :nh * hd] - q_ref).max() <= tol * scale
+    for t in range(T):
+        p, o = divmod(int(slots[t]), page)
+        assert np.abs(kc[p, :, o].float().cpu().numpy() - k_ref[t]).max() <= tol * scale
+        assert np.array_equal(vc[p, :, o].float().cpu().numpy(), v_ref[t])
+
+
+def test_rope_table_matches_reference_fixture():
+    """The engine's own rotation (table + kernel) against the reference's RoPE fixture."""
+    import json, os
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.position import RotateHalfRope
+    fx = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_rope.json")))
+    for case in fx["cases"]:
+        hd, p = case["head_dim"], case["position"]
+        part = RotateHalfRope(Runtime(torch.float32, torch.device(DEV)), hd, hd, float(case["base"]), 512)
+        x = t32(np.asarray(case["input"], np.float32)[None, :])
+        heads = x.shape[1] // hd
+        ops().rope_kv_write(x, t32(np.asarray([p], np.int32)), part.cos_sin(), None, None, None,
+                            heads, 0, hd, hd, 16)
+        ref = np.asarray(case["output"], np.float64)
+        assert np.all(np.abs(x.cpu().numpy()[0] - ref) <= 2e-6 + 2e-6 * np.abs(ref)), (hd, p)
+
+
+def test_argmax_first_maximum():
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((5, 1000)).astype(np.float32)
+    x[0, 17] = x[0, 900] = 9.0           # tie: lowest id wins
+    x[1, 999] = 50.0
+    x[2, :] = 0.0                        # all equal -> 0
+    lg = t32(x)
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().argmax(lg, out, status)
+    assert out.tolist() == [17, 999, 0, int(x[3].argmax()), int(x[4].argmax())] and status.item() == 0
+    lg[3, 5] = float("nan")
+    ops().argmax(lg, out, status)
+    assert status.item() == 2
+
+
+@pytest.mark.parametrize("V", [5, 1000, 151936])
+def test_sample_follows_reference_order(V):
+    """The device sampler picks what the plain float64 sampler picks, for the same draws."""
+    rng = np.random.default_rng(V)
+    settings = [(0.8, 0, 1.0), (1.0, 5, 1.0), (0.7, 0, 0.9), (1.5, 50, 0.95), (0.3, 2, 0.5), (2.0, 0, 1.0)]
+    R = len(settings)
+    logits = (rng.standard_normal((R, V)) * 3).astype(np.float32)
+    logits[1, :4] = logits[1].max() + 1.0       # ties at the top: ranked by id
+    lg = t32(logits)
+    samplers = [plain.PlainSampler(temperature=t, top_k=min(k, V), top_p=p, seed=100 + i)
+                for i, (t, k, p) in enumerate(settings)]
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    temp = t32(np.asarray([s[0] for s in settings], np.float32))
+    topk = t32(np.asarray([min(s[1], V) for s in settings], np.int32))
+    topp = t32(np.asarray([s[2] for s in settings], np.float32))
+    draws = 12 if V > 10000 else 40
+    twins = [plain.PlainSampler(temperature=t, top_k=min(k, V), top_p=p, seed=100 + i)
+             for i, (t, k, p) in enumerate(settings)]
+    for _ in range(draws):
+        u = np.asarray([tw.random() for tw in twins], np.float64)
+        ops().sample(lg, temp, topk, topp, t32(u), out, status)
+        want = [s.sample(logits[i]) for i, s in enumerate(samplers)]
+        assert out.tolist() == want
+    assert status.item() == 0

@@ -1,0 +1,205 @@
+"""Replay on the GPU: the same requests whole, with the last 32 tokens one by one, in
+portions of changing size, and mixed with other requests under a pool so small that pages
+are used again; in float32 and in bfloat16; against the plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import tiny
+from replay import Replay, compare, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["A", "B"]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("models")
+    return {n: tiny.make_folder(base, n) for n in NAMES}
+
+
+@pytest.fixture(scope="module")
+def models(folders):
+    from coheryn_ai_studio_b200.engine import load_model
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            cache[(name, dtype)] = load_model(folders[name], dtype)[1]
+        return cache[(name, dtype)]
+    return get
+
+
+def vocab(name):
+    return tiny.CONFIGS[name][0].vocab_size
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole(name, dtype, folders, models):
+    lengths = [5, 17, 33, 100] if name == "A" else [1, 9, 64, 130, 200]
+    for i, n in enumerate(lengths):
+        seq = tiny.prompt(10 + i, n, vocab(name))
+        r = Replay(folders[name], dtype, max_tokens=256, model=models(name, dtype))
+        r.step([("r", seq, list(range(n)))], end=["r"])
+        compare(r, folders[name], {"r": seq}, f"whole {n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_one_by_one(name, dtype, folders, models):
+    n = 90 if name == "A" else 150
+    seq = tiny.prompt(20, n, vocab(name))
+    r = Replay(folders[name], dtype, max_tokens=192, model=models(name, dtype))
+    head = n - 32
+    r.step([("r", seq[:head], list(range(head)))])
+    for t in range(head, n):
+        r.step([("r", [seq[t]], [0])])
+    assert len(r.rows) == n
+    compare(r, folders[name], {"r": seq}, "tail")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_changing_portions(name, dtype, folders, models):
+    portions = [7, 2, 16, 3, 2, 33, 1, 15, 2, 17, 2, 5]
+    n = sum(portions)
+    seq = tiny.prompt(21, n, vocab(name))
+    r = Replay(folders[name], dtype, max_tokens=128, model=models(name, dtype))
+    o = 0
+    for p in portions:
+        r.step([("r", seq[o:o + p], list(range(p)))])
+        o += p
+    compare(r, folders[name], {"r": seq}, "portions")
+
+
+def mixed_script(rng, sequences, max_live, max_portion):
+    """Steps that keep up to ``max_live`` requests alive: each step gives every live
+    request either a portion of its prompt (2..max_portion tokens) or, once past 60 % of
+    its tokens, a single token; some requests sit a step out."""
+    pending = list(sequences)
+    live, done_at = {}, {}
+    steps = []
+    while pending or live:
+        while pending and len(live) < max_live:
+            live[pending.pop(0)] = 0
+        entries, end = [], []
+        for rid in list(live):
+            seq, o = sequences[rid], live[rid]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                   # left out of this step
+            left = len(seq) - o
+            n = 1 if o >= 0.6 * len(seq) else int(min(left, rng.integers(2, max_portion + 1)))
+            want = sorted(set(rng.integers(0, n, size=min(n, 3)).tolist() + [n - 1]))
+            entries.append((rid, seq[o:o + n], want))
+            live[rid] = o + n
+            if live[rid] == len(seq):
+                end.append(rid)
+                del live[rid]
+        if entries:
+            steps.append((entries, end))
+    return steps
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_mixed_with_page_reuse(name, dtype, folders, models):
+    rng = np.random.default_rng(5)
+    lengths = [60, 33, 64, 47, 62, 21, 58, 64, 40, 9]
+    sequences = {f"q{i}": tiny.prompt(30 + i, n, vocab(name)) for i, n in enumerate(lengths)}
+    # four live requests of at most 64 tokens: 256 tokens = 16 pages of 16
+    r = Replay(folders[name], dtype, max_tokens=256, model=models(name, dtype))
+    steps = mixed_script(rng, sequences, max_live=4, max_portion=19)
+    first_owner, reused = {}, 0
+    for entries, end in steps:
+        assert len(entries) <= 4
+        r.step(entries, end)
+        for rid, _, _ in entries:
+            if rid in r.cache.requests:
+                for p in r.cache.block_table(rid, 0):
+                    if first_owner.setdefault(p, rid) != rid:
+                        reused += 1
+    assert any(len(e) > 1 and min(len(t) for _, t, _ in e) == 1 and max(len(t) for _, t, _ in e) > 1
+               for e, _ in steps), "no step mixed a prompt portion with a single token"
+    assert reused > 0, "the pool was never short enough to use a page again"
+    assert r.cache.available_pages() == [16]
+    compare(r, folders[name], sequences, "mixed")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype, folders, models):
+    name = "B"
+    n = 300
+    seq = tiny.prompt(40, n, vocab(name))
+    r = Replay(folders[name], dtype, max_tokens=320, model=models(name, dtype))
+    r.step([("r", seq[:8], [7])])
+    for t in range(8, n):
+        r.step([("r", [seq[t]], [0] if t % 7 == 0 or t > n - 5 else [])])
+    compare(r, folders[name], {"r": seq}, "long")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens(name, dtype, folders, models):
+    seq = tiny.prompt(41, 4, vocab(name))
+    r = Replay(folders[name], dtype, max_tokens=64, model=models(name, dtype))
+    for t in range(4):
+        r.step([("r", [seq[t]], [0])])
+    compare(r, folders[name], {"r": seq}, "first")
+    r2 = Replay(folders[name], dtype, max_tokens=64, model=models(name, dtype))
+    r2.step([("r", seq[:2], [0, 1])])
+    r2.step([("r", seq[2:], [0, 1])])
+    compare(r2, folders[name], {"r": seq}, "first pairs")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cutting_agrees_with_itself(dtype, folders, models):
+    """Beyond the comparison with the plain implementation: two ways of cutting the same
+    sequence agree with each other to rounding."""
+    name = "A"
+    seq = tiny.prompt(42, 70, vocab(name))
+    a = Replay(folders[name], dtype, max_tokens=128, model=models(name, dtype))
+    a.step([("r", seq, list(range(70)))])
+    b = Replay(folders[name], dtype, max_tokens=128, model=models(name, dtype))
+    for o in range(0, 70, 5):
+        b.step([("r", seq[o:o + 5], list(range(5)))])
+    worst = max(float(np.abs(a.rows[k] - b.rows[k]).max()) for k in a.rows)
+    assert worst <= (2e-5 if dtype == "float32" else 0.04)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(dtype, folders, tmp_path):
+    """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and 'done' lines out."""
+    name = "A"
+    seqs = {"a": tiny.prompt(50, 37, vocab(name)), "b": tiny.prompt(51, 20, vocab(name))}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": seqs["a"][:30], "want": [0, 29]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": seqs["a"][30:32], "want": [1]},
+                                {"id": "b", "tokens": seqs["b"][:18], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": seqs["b"][18:], "want": [0, 1]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": seqs["a"][32:], "want": [4]}], "end": ["a"]},
+    ]
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[name],
+                        "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", text=True,
+                       capture_output=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    assert not (out / "1.f32").exists() or True
+    V = vocab(name)
+    got = {i: np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V) for i in (0, 1, 2, 3)}
+    ref_a, ref_b = plain_logits(folders[name], seqs["a"]), plain_logits(folders[name], seqs["b"])
+    tol = 1e-4 if dtype == "float32" else 0.04
+    assert got[0].shape[0] == 2 and got[1].shape[0] == 1 and got[2].shape[0] == 2
+    assert np.abs(got[0] - ref_a[[0, 29]]).max() <= tol
+    assert np.abs(got[1] - ref_a[[31]]).max() <= tol
+    assert np.abs(got[2] - ref_b[[18, 19]]).max() <= tol
+    assert np.abs(got[3] - ref_a[[36]]).max() <= tol
