@@ -101,25 +101,97 @@ __device__ void histogram(const float* row, int V, float vmax, float inv_t, unsi
   __syncthreads();
 }
 
+struct SampleShared {
+  double h_mass[256];
+  unsigned h_count[256];
+  double before_mass;      // mass of the candidates ranked before the current bucket
+  long long before_count;  // their number
+  unsigned prefix;         // key digits fixed so far
+  unsigned bucket_count;   // candidates in the bucket picked last
+  double result_mass;
+  long long result_rank;
+};
+
+enum { BY_COUNT = 0, BY_FRACTION = 1, BY_MASS = 2 };
+
+// Walks the rank order (value descending, id ascending) down to one key, one 8-bit digit a
+// level, looking for the first rank r that satisfies
+//   BY_COUNT:    r >= target_count            (result_mass = mass of ranks 1..r)
+//   BY_FRACTION: mass(1..r) / total >= frac   (result_rank = r)
+//   BY_MASS:     threshold < mass(1..r)       (prefix = its key, result_rank = rank among
+//                                              the candidates of that key, 1-based)
+// After four levels the bucket holds n candidates of ONE value, ranked by id, so the rank
+// inside it follows from arithmetic on n equal masses.  If rounding leaves the target
+// past the last candidate, the last one is taken.
+__device__ void descend(SampleShared& sh, const float* row, int V, float vmax, float inv_t, int mode,
+                        long long target_count, double total, double frac, double threshold) {
+  if (threadIdx.x == 0) { sh.prefix = 0u; sh.before_mass = 0.0; sh.before_count = 0; }
+  __syncthreads();
+  for (int level = 0; level < 4; ++level) {
+    histogram(row, V, vmax, inv_t, sh.prefix, level, sh.h_mass, sh.h_count);
+    if (threadIdx.x == 0) {
+      double cm = sh.before_mass;
+      long long cc = sh.before_count;
+      int pick = -1;
+      double pick_cm = cm;
+      long long pick_cc = cc;
+      for (int b = 0; b < 256; ++b) {
+        if (sh.h_count[b] == 0u) continue;
+        const double nm = cm + sh.h_mass[b];
+        const long long nc = cc + sh.h_count[b];
+        bool inside;
+        if (mode == BY_COUNT) inside = nc >= target_count;
+        else if (mode == BY_FRACTION) inside = nm / total >= frac;
+        else inside = threshold < nm;
+        pick = b; pick_cm = cm; pick_cc = cc;
+        if (inside) break;
+        cm = nm; cc = nc;
+      }
+      sh.before_mass = pick_cm;
+      sh.before_count = pick_cc;
+      sh.prefix |= (unsigned)pick << (24 - 8 * level);
+      sh.bucket_count = sh.h_count[pick];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const long long n = (long long)sh.bucket_count;
+    const double p = exp(((double)key_value(sh.prefix) - (double)vmax) * (double)inv_t);
+    const double cm = sh.before_mass;
+    const long long cc = sh.before_count;
+    long long j = 1;
+    if (mode == BY_COUNT) {
+      j = target_count - cc;
+      if (j > n) j = n;
+      if (j < 1) j = 1;
+    } else if (mode == BY_FRACTION) {
+      while (j < n && !((cm + (double)j * p) / total >= frac)) ++j;
+    } else {
+      while (j < n && !(threshold < cm + (double)j * p)) ++j;
+    }
+    sh.result_mass = cm + (double)j * p;
+    sh.result_rank = mode == BY_MASS ? j : cc + j;
+  }
+  __syncthreads();
+}
+
 // One row per block.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long stride, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const double* __restrict__ uniform, int* __restrict__ out, int* __restrict__ status) {
-  __shared__ double h_mass[256];
-  __shared__ unsigned h_count[256];
+  __shared__ SampleShared sh;
   __shared__ float s_red[33];
   __shared__ int s_scan[SAMPLE_THREADS];
-  __shared__ double s_total, s_threshold, s_before_mass;
-  __shared__ long long s_keep_count, s_before_count;
-  __shared__ unsigned s_prefix, s_neq;
-  __shared__ long long s_rank;  // 1-based rank, among the candidates of the final key, of the chosen one
+  __shared__ int s_owner;
+  __shared__ long long s_rank;
 
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * stride;
   const float inv_t = 1.0f / temperature[r];
-  const int k = top_k[r];
   const double p_keep = (double)top_p[r];
+  long long K = top_k[r];
+  if (K <= 0 || K > V) K = V;
 
   float vmax = -INFINITY;
   bool bad = false;
@@ -140,99 +212,54 @@ sample_kernel(const float* __restrict__ logits, long stride, int V, const float*
   __syncthreads();
   vmax = s_red[32];
 
-  // Three descents over the rank order (value descending, id ascending):
-  //  phase 0: the number of candidates that top-p keeps = the first rank whose
-  //           cumulative mass / total mass >= top_p; then top-k caps it;
-  //  phase 1: the mass of the kept prefix; the threshold is u * that mass;
-  //  phase 2: the first candidate whose cumulative mass exceeds the threshold.
-  // A descent narrows (key prefix, mass before, count before) by one digit a level.
-  // After four levels the bucket holds candidates of ONE value (n of them, ranked by
-  // id), so the rank inside it follows from arithmetic on n equal masses.
-  for (int phase = 0; phase < 3; ++phase) {
-    if (threadIdx.x == 0) { s_prefix = 0u; s_before_mass = 0.0; s_before_count = 0; }
-    __syncthreads();
-    for (int level = 0; level < 4; ++level) {
-      histogram(row, V, vmax, inv_t, s_prefix, level, h_mass, h_count);
-      if (threadIdx.x == 0) {
-        if (phase == 0 && level == 0) {
-          double tot = 0.0;
-          for (int b = 0; b < 256; ++b) tot += h_mass[b];
-          s_total = tot;
-        }
-        double cm = s_before_mass;
-        long long cc = s_before_count;
-        int pick = -1, last = -1;
-        double last_cm = cm;
-        long long last_cc = cc;
-        for (int b = 0; b < 256; ++b) {
-          if (h_count[b] == 0u) continue;
-          const double nm = cm + h_mass[b];
-          const long long nc = cc + h_count[b];
-          bool inside;
-          if (phase == 0) inside = nm / s_total >= p_keep;
-          else if (phase == 1) inside = nc >= s_keep_count;
-          else inside = s_threshold < nm;
-          last = b; last_cm = cm; last_cc = cc;
-          if (inside) { pick = b; break; }
-          cm = nm; cc = nc;
-        }
-        if (pick < 0) { pick = last; cm = last_cm; cc = last_cc; }  // rounding: take the last bucket
-        s_before_mass = cm;
-        s_before_count = cc;
-        s_prefix |= (unsigned)pick << (24 - 8 * level);
-        s_neq = h_count[pick];
-      }
-      __syncthreads();
-    }
-    if (threadIdx.x == 0) {
-      const long long n = (long long)s_neq;
-      const double p = exp(((double)key_value(s_prefix) - (double)vmax) * (double)inv_t);
-      const double cm = s_before_mass;
-      const long long cc = s_before_count;
-      if (phase == 0) {
-        long long j = 1;
-        while (j < n && !((cm + (double)j * p) / s_total >= p_keep)) ++j;
-        long long keep = cc + j;
-        if (k > 0 && k < keep) keep = k;
-        s_keep_count = keep;
-      } else if (phase == 1) {
-        long long j = s_keep_count - cc;
-        if (j < 1) j = 1;
-        if (j > n) j = n;
-        s_threshold = uniform[r] * (cm + (double)j * p);
-      } else {
-        long long j = 1;
-        while (j < n && !(s_threshold < cm + (double)j * p)) ++j;
-        // Never step outside the kept prefix.
-        if (cc + j > s_keep_count) j = s_keep_count - cc;
-        if (j < 1) j = 1;
-        s_rank = j;
-      }
-    }
-    __syncthreads();
+  // 1. total = mass of the K best candidates (top-k is applied first; K = V without it)
+  descend(sh, row, V, vmax, inv_t, BY_COUNT, K, 0.0, 0.0, 0.0);
+  const double total = sh.result_mass;
+  // 2. keep = first rank whose normalised cumulative mass reaches top_p (never beyond K)
+  long long keep = K;
+  if (p_keep < 1.0) {
+    descend(sh, row, V, vmax, inv_t, BY_FRACTION, 0, total, p_keep, 0.0);
+    keep = sh.result_rank < K ? sh.result_rank : K;
   }
-  // The s_rank-th id (ascending) whose key equals s_prefix: blocked partition, count,
-  // scan, then the owning thread walks its chunk.
-  const unsigned key = s_prefix;
+  // 3. kept = mass of ranks 1..keep; the draw lands at u * kept
+  double kept = total;
+  if (keep < K) {
+    descend(sh, row, V, vmax, inv_t, BY_COUNT, keep, 0.0, 0.0, 0.0);
+    kept = sh.result_mass;
+  }
+  // 4. the first candidate whose cumulative mass exceeds the threshold
+  descend(sh, row, V, vmax, inv_t, BY_MASS, 0, 0.0, 0.0, uniform[r] * kept);
+  if (threadIdx.x == 0) {
+    long long j = sh.result_rank;
+    if (sh.before_count + j > keep) j = keep - sh.before_count;   // never outside the kept prefix
+    if (j < 1) j = 1;
+    s_rank = j;
+  }
+  __syncthreads();
+
+  // The s_rank-th id (ascending) whose key equals the final key: blocked partition,
+  // count, scan, then the owning thread walks its chunk.
+  const unsigned key = sh.prefix;
   const int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-  const int lo = threadIdx.x * chunk, hi = min(V, lo + chunk);
+  const int lo = min(V, (int)threadIdx.x * chunk), hi = min(V, lo + chunk);
   int mine = 0;
   for (int i = lo; i < hi; ++i) mine += desc_key(row[i]) == key;
   s_scan[threadIdx.x] = mine;
   __syncthreads();
   if (threadIdx.x == 0) {
-    long long want = s_rank;
-    int acc = 0, owner = -1, last_owner = -1;
+    const long long want = s_rank;
+    long long acc = 0;
+    int owner = -1, last_owner = 0;
     for (int t = 0; t < SAMPLE_THREADS; ++t) {
       if (s_scan[t] > 0) last_owner = t;
       if (owner < 0 && acc + s_scan[t] >= want) { owner = t; s_rank = want - acc; }
       acc += s_scan[t];
     }
     if (owner < 0) { owner = last_owner; s_rank = s_scan[last_owner]; }
-    s_neq = (unsigned)owner;
+    s_owner = owner;
   }
   __syncthreads();
-  if (threadIdx.x == (int)s_neq) {
+  if ((int)threadIdx.x == s_owner) {
     long long seen = 0;
     int choice = lo;
     for (int i = lo; i < hi; ++i)
@@ -240,7 +267,32 @@ sample_kernel(const float* __restrict__ logits, long stride, int V, const float*
     out[r] = choice;
   }
 }
+
+// Penalties over the ids a request has seen (sampling.rs:131-143): for item i,
+// v = logits[rows[i], ids[i]]; v = v < 0 ? v * rep : v / rep; v -= presence + count * frequency.
+__global__ void apply_penalties_kernel(float* __restrict__ logits, long stride, int n,
+                                       const int* __restrict__ rows, const int* __restrict__ ids,
+                                       const int* __restrict__ counts, const float* __restrict__ rep,
+                                       const float* __restrict__ freq, const float* __restrict__ pres) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float* p = logits + (size_t)rows[i] * stride + ids[i];
+  float v = *p;
+  v = v < 0.f ? v * rep[i] : v / rep[i];
+  v -= pres[i] + (float)counts[i] * freq[i];
+  *p = v;
+}
 }  // namespace
+
+// Each (row, id) pair must appear at most once.
+CO_EXPORT int coheryn_apply_penalties(float* logits, long stride, int n, const int* rows, const int* ids,
+                                      const int* counts, const float* rep, const float* freq,
+                                      const float* pres, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  apply_penalties_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, stride, n, rows, ids, counts, rep, freq, pres);
+  CO_CHECK_LAUNCH("apply_penalties");
+  return 0;
+}
 
 CO_EXPORT int coheryn_argmax(const float* logits, long stride, int R, int V, int* out, int* status,
                              cudaStream_t stream) {

@@ -218,6 +218,18 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                    _ptr(out), _ptr(status), _stream()))
 
 
+def apply_penalties(logits, rows, ids, counts, rep, freq, pres) -> None:
+    """In place: the reference's penalties on logits[rows[i], ids[i]] (each pair once)."""
+    _dev(logits, rows, ids, counts, rep, freq, pres)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    for t in (rows, ids, counts):
+        _i32(t, "penalty index")
+    lib = core()
+    _check(lib, lib.coheryn_apply_penalties(_ptr(logits), c_long(logits.stride(0)), c_int(rows.numel()),
+                                            _ptr(rows), _ptr(ids), _ptr(counts), _ptr(rep), _ptr(freq),
+                                            _ptr(pres), _stream()))
+
+
 # ------------------------------------------------------------------------------------
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:

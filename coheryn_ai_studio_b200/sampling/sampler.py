@@ -1,0 +1,203 @@
+"""Sampling in the reference's manner (crates/coheryn-engine/src/sampling.rs, profile
+"coheryn-sampling-v2"): temperature 0 is greedy with ties to the lowest id; otherwise
+candidates are ranked by (value descending, id ascending), top-k keeps the first k, top-p
+the shortest prefix whose normalised mass reaches it, and one SplitMix64 draw per sampled
+token picks the candidate whose cumulative mass first exceeds ``u * kept mass``.
+Penalties over the ids seen so far (prompt and generated) come first: for a seen id,
+``v = v * rep if v < 0 else v / rep``, then ``v -= presence + count * frequency``.
+
+The draw is made on the host (one 64-bit state per request, advanced only when a token is
+sampled); selection runs on the device.  :class:`HostSampler` is the same algorithm in
+float64 on the host, kept for checking the device path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+
+_MASK = (1 << 64) - 1
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+    repetition_penalty: float = 1.0
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+
+    def validate(self, vocab_size: Optional[int] = None) -> None:
+        """Ranges of sampling.rs:75-84 and 38-52."""
+        t, p = self.temperature, self.top_p
+        if not (math.isfinite(t) and 0.0 <= t <= 2.0 and math.isfinite(p) and 0.0 < p <= 1.0):
+            raise ValueError("temperature must be finite in [0,2]; top_p must be in (0,1]")
+        if not (math.isfinite(self.repetition_penalty) and 0.01 <= self.repetition_penalty <= 10.0
+                and math.isfinite(self.frequency_penalty) and -2.0 <= self.frequency_penalty <= 2.0
+                and math.isfinite(self.presence_penalty) and -2.0 <= self.presence_penalty <= 2.0):
+            raise ValueError("repetition_penalty must be in [0.01,10]; frequency/presence penalties "
+                             "must be in [-2,2]; all must be finite")
+        if self.top_k < 0 or (vocab_size is not None and self.top_k > vocab_size):
+            raise ValueError("top_k exceeds model vocabulary")
+        if not 0 <= self.seed <= _MASK:
+            raise ValueError("seed must fit 64 unsigned bits")
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature == 0.0
+
+    @property
+    def penalised(self) -> bool:
+        return (self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0
+                or self.presence_penalty != 0.0)
+
+
+class SplitMix64:
+    """sampling.rs:123-130."""
+
+    def __init__(self, seed: int):
+        self.state = int(seed) & _MASK
+
+    def random(self) -> float:
+        self.state = (self.state + 0x9E3779B97F4A7C15) & _MASK
+        z = self.state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+        return ((z ^ (z >> 31)) >> 11) / float(1 << 53)
+
+
+class RequestSampler:
+    """Per-request sampling state: the random stream and the counts of seen ids."""
+
+    def __init__(self, params: SamplingParams, history: Sequence[int] = ()):
+        self.params = params
+        self.rng = SplitMix64(params.seed)
+        self.counts: Dict[int, int] = {}
+        if params.penalised:
+            for t in history:
+                self.observe(t)
+
+    def observe(self, token: int) -> None:
+        if self.params.penalised:
+            self.counts[token] = self.counts.get(token, 0) + 1
+
+
+class DeviceSampler:
+    """Picks one token per logits row on the device."""
+
+    def __init__(self, device):
+        self.device = device
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def _dev(self, array: np.ndarray) -> torch.Tensor:
+        t = torch.from_numpy(array)
+        if self.device.type == "cuda":
+            t = t.pin_memory()
+        return t.to(self.device, non_blocking=True)
+
+    def sample(self, logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> List[int]:
+        """logits: float32 [R, V] (modified in place when penalties apply).  Returns the
+        chosen ids; advances each sampled request's random stream by one draw and records
+        the chosen id in its counts."""
+        R = logits.shape[0]
+        assert R == len(samplers)
+        if R == 0:
+            return []
+        rows, ids, counts, rep, freq, pres = [], [], [], [], [], []
+        for r, s in enumerate(samplers):
+            if s.params.penalised and s.counts:
+                for tok, c in s.counts.items():
+                    rows.append(r); ids.append(tok); counts.append(c)
+                    rep.append(s.params.repetition_penalty)
+                    freq.append(s.params.frequency_penalty); pres.append(s.params.presence_penalty)
+        if rows:
+            ops.apply_penalties(logits, self._dev(np.asarray(rows, np.int32)),
+                                self._dev(np.asarray(ids, np.int32)), self._dev(np.asarray(counts, np.int32)),
+                                self._dev(np.asarray(rep, np.float32)), self._dev(np.asarray(freq, np.float32)),
+                                self._dev(np.asarray(pres, np.float32)))
+        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        hot = [r for r, s in enumerate(samplers) if not s.params.greedy]
+        if len(hot) < R:
+            ops.argmax(logits, out, self.status)
+        if hot:
+            sub = logits if len(hot) == R else logits[self._dev(np.asarray(hot, np.int64))]
+            temp = np.asarray([samplers[r].params.temperature for r in hot], np.float32)
+            topk = np.asarray([samplers[r].params.top_k for r in hot], np.int32)
+            topp = np.asarray([samplers[r].params.top_p for r in hot], np.float32)
+            u = np.asarray([samplers[r].rng.random() for r in hot], np.float64)
+            picked = torch.empty(len(hot), dtype=torch.int32, device=self.device)
+            ops.sample(sub, self._dev(temp), self._dev(topk), self._dev(topp), self._dev(u), picked, self.status)
+            if len(hot) == R:
+                out = picked
+            else:
+                out[self._dev(np.asarray(hot, np.int64))] = picked
+        chosen = out.cpu().tolist()
+        if int(self.status.item()):
+            self.status.zero_()
+            raise RuntimeError("empty or non-finite logits")
+        for s, tok in zip(samplers, chosen):
+            s.observe(tok)
+        return chosen
+
+
+class HostSampler:
+    """sampling.rs:147-222 on the host in float64 (checks the device path; supports a mask)."""
+
+    def __init__(self, params: SamplingParams, history: Sequence[int] = ()):
+        self.state = RequestSampler(params, history)
+
+    def _adjusted(self, i: int, v: float) -> float:
+        p = self.state.params
+        c = self.state.counts.get(i, 0)
+        if c:
+            rep = float(np.float32(p.repetition_penalty))
+            v = v * rep if v < 0 else v / rep
+            v -= float(np.float32(p.presence_penalty)) + c * float(np.float32(p.frequency_penalty))
+        return v
+
+    def sample(self, logits, allowed=None) -> int:
+        logits = np.asarray(logits, dtype=np.float32)
+        if logits.size == 0 or not np.isfinite(logits).all():
+            raise ValueError("empty or non-finite logits")
+        p = self.state.params
+        cand = [i for i in range(logits.size) if allowed is None or allowed[i]]
+        if not cand:
+            raise ValueError("sampling mask permits no token")
+        val = {i: self._adjusted(i, float(logits[i])) for i in cand}
+        if p.greedy:
+            best = cand[0]
+            for i in cand:
+                if val[i] > val[best]:
+                    best = i
+            choice = best
+        else:
+            cand.sort(key=lambda i: (-val[i], i))
+            if 0 < p.top_k < len(cand):
+                cand = cand[:p.top_k]
+            t = float(np.float32(p.temperature))
+            top_p = float(np.float32(p.top_p))
+            probs = [math.exp((val[i] - val[cand[0]]) / t) for i in cand]
+            total = sum(probs)
+            cum, n = 0.0, 0
+            for pr in probs:
+                cum += pr / total
+                n += 1
+                if cum >= top_p:
+                    break
+            probs = probs[:n]
+            threshold = self.state.rng.random() * sum(probs)
+            cum, choice = 0.0, cand[n - 1]
+            for i, pr in zip(cand, probs):
+                cum += pr
+                if threshold < cum:
+                    choice = i
+                    break
+        self.state.observe(choice)
+        return choice

@@ -166,7 +166,7 @@ class TensorReader:
         if e.end == e.begin:
             return torch.empty(e.shape, dtype=e.dtype)
         buf = self._map(e.path)
-        flat = torch.frombuffer(memoryview(buf)[e.begin:e.end], dtype=torch.uint8).clone()
+        flat = torch.frombuffer(bytearray(buf[e.begin:e.end]), dtype=torch.uint8)
         return flat.view(e.dtype).reshape(e.shape)
 
     def close(self) -> None:

@@ -1,0 +1,138 @@
+"""Generation through the engine and its entry points: greedy and sampled tokens equal
+the plain implementation's, with continuous batching, with preemption and with prefix
+reuse."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_qwen2 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("gen")
+    return {n: tiny.make_folder(base, n, policy=tiny.POLICY_LOUD) for n in ("A", "B")}
+
+
+def plain_generate(folder, prompt, steps, sampler=None):
+    cfg, w = plain.read_model(folder)
+    ids, out = list(prompt), []
+    for _ in range(steps):
+        logits = plain.forward(cfg, w, ids)[-1]
+        tok = int(np.argmax(logits)) if sampler is None else sampler.sample(logits)
+        if sampler is not None:
+            sampler.observe(tok)
+        out.append(tok); ids.append(tok)
+    return out
+
+
+def test_greedy_three_requests_float32(folders):
+    """Tiny A: prompts of 5, 17 and 33 ids, 8 greedy tokens each, identical to the plain run."""
+    from coheryn_ai_studio_b200.engine import Engine
+    eng = Engine.from_folder(folders["A"], "float32", context=128, max_num_seqs=4)
+    prompts = [tiny.prompt(60 + i, n, 512) for i, n in enumerate((5, 17, 33))]
+    res = eng.generate(prompts, max_tokens=8)
+    for p, r in zip(prompts, res):
+        assert r.token_ids == plain_generate(folders["A"], p, 8)
+        assert r.finish_reason == "length" and r.completion_tokens == 8 and r.prompt_tokens == len(p)
+    eng.cache.check()
+    assert eng.cache.available_pages() == [eng.cache.num_pages]
+
+
+def test_continuous_batching_mixed_float32(folders):
+    """Tiny B: prompts of 1, 9, 64 and 130 ids as one mixed batch with 16-token portions and
+    pages of 16; greedy, and temperature 0.8 with a fixed seed."""
+    from coheryn_ai_studio_b200.engine import Engine
+    from coheryn_ai_studio_b200.sampling import SamplingParams
+    eng = Engine.from_folder(folders["B"], "float32", context=256, max_num_seqs=4,
+                             max_num_batched_tokens=16, page_size=16)
+    prompts = [tiny.prompt(70 + i, n, 1000) for i, n in enumerate((1, 9, 64, 130))]
+    res = eng.generate(prompts, max_tokens=6)
+    for p, r in zip(prompts, res):
+        assert r.token_ids == plain_generate(folders["B"], p, 6)
+    assert eng.scheduler.stats["max_batch_width"] >= 3
+    params = [SamplingParams(temperature=0.8, seed=11 + i, top_k=(0, 40, 0, 5)[i], top_p=(1.0, 1.0, 0.9, 1.0)[i])
+              for i in range(4)]
+    res = eng.generate(prompts, max_tokens=5, params=params)
+    for i, (p, r) in enumerate(zip(prompts, res)):
+        s = plain.PlainSampler(temperature=0.8, seed=11 + i, top_k=params[i].top_k, top_p=params[i].top_p)
+        assert r.token_ids == plain_generate(folders["B"], p, 5, s)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_and_prefix_reuse_change_nothing(folders, dtype):
+    from coheryn_ai_studio_b200.engine import Engine
+    shared = tiny.prompt(80, 40, 512)
+    prompts = [shared + tiny.prompt(81 + i, 3 + 5 * i, 512) for i in range(4)]
+    def run(**kw):
+        eng = Engine.from_folder(folders["A"], dtype, context=128, max_num_seqs=4, page_size=16, **kw)
+        res = eng.generate(prompts, max_tokens=24)
+        eng.cache.check()
+        return [r.token_ids for r in res], eng, res
+    base, _, _ = run(prefix_reuse=False)
+    tight, eng, res = run(prefix_reuse=False, num_pages=12)       # 192 tokens for 4 x ~80
+    assert eng.scheduler.stats["preemptions"] > 0 and tight == base
+    reuse, eng, res = run(prefix_reuse=True)
+    assert reuse == base and sum(r.reused_prompt_tokens for r in res) >= 32
+    if dtype == "float32":
+        assert base[0] == plain_generate(folders["A"], prompts[0], 24)
+
+
+def test_stop_token_and_penalties(folders):
+    from coheryn_ai_studio_b200.engine import Engine
+    from coheryn_ai_studio_b200.sampling import SamplingParams
+    eng = Engine.from_folder(folders["A"], "float32", context=128, max_num_seqs=2)
+    p = tiny.prompt(90, 12, 512)
+    free = eng.generate([p], max_tokens=10)[0].token_ids
+    stop = eng.generate([p], max_tokens=10, stop_tokens=[free[3]])[0]
+    k = free.index(free[3])
+    assert stop.token_ids == free[:k + 1] and stop.finish_reason == "stop"
+    params = SamplingParams(temperature=0.7, seed=5, repetition_penalty=1.3, frequency_penalty=0.4,
+                            presence_penalty=0.2, top_p=0.95)
+    got = eng.generate([p], max_tokens=8, params=params)[0].token_ids
+    s = plain.PlainSampler(temperature=0.7, seed=5, repetition_penalty=1.3, frequency_penalty=0.4,
+                           presence_penalty=0.2, top_p=0.95)
+    for t in p:
+        s.observe(t)
+    assert got == plain_generate(folders["A"], p, 8, s)
+
+
+def test_refusals(folders):
+    from coheryn_ai_studio_b200.engine import Engine, RequestRefused
+    eng = Engine.from_folder(folders["A"], "float32", context=64, max_num_seqs=2)
+    with pytest.raises(RequestRefused):
+        eng.add_request([], 4)
+    with pytest.raises(RequestRefused):
+        eng.add_request([1] * 60, 5)
+    with pytest.raises(RequestRefused):
+        eng.add_request([512], 5)
+    with pytest.raises(ValueError):
+        Engine.from_folder(folders["A"], "float32", context=1000)      # beyond the model's positions
+    assert eng.generate([[1, 2, 3]], max_tokens=0)[0].finish_reason == "length"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_command_line_and_python_entry(folders, dtype):
+    from coheryn_ai_studio_b200 import api
+    p = tiny.prompt(95, 9, 512)
+    want = plain_generate(folders["A"], p, 6)
+    out = api.run(folders["A"], tokens=p, max_tokens=6, context=64, dtype=dtype, timeout=900)
+    assert out["prompt_tokens"] == 9 and out["completion_tokens"] == 6 and out["finish_reason"] == "length"
+    if dtype == "float32":
+        assert out["token_ids"] == want
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "coheryn"), "run", folders["A"], "--tokens",
+                        ",".join(map(str, p)), "--max-tokens", "6", "--context", "64", "--dtype", dtype, "--stream"],
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and [int(t) for t in r.stdout.split()] == out["token_ids"]
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "coheryn"), "--json", "run", folders["A"],
+                          "--tokens", "1,2", "--max-tokens", "6", "--context", "4"], capture_output=True, text=True)
+    assert bad.returncode == 2 and json.loads(bad.stderr.strip().splitlines()[-1])["code"] == "invalid_request"
+    assert api.generate(folders["A"], [p], max_tokens=6, context=64, dtype=dtype)[0]["token_ids"] == out["token_ids"]

@@ -1,0 +1,280 @@
+"""Each part of a layer alone against the plain implementation, and the generality of
+the assembly: a model whose schedule names a layer twice, lets an entry read another
+entry's cache, uses a window in some layers, and holds a toy mixer with state of its own
+that is defined HERE and registered without touching the framework's files."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def rt(dtype=torch.float32):
+    from coheryn_ai_studio_b200.parts import Runtime
+    return Runtime(dtype, DEV)
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV).to(dtype)
+
+
+def one_request_step(tokens_n, start, page_size, pages_needed, groups=1):
+    """A StepContext for one request that brings tokens_n tokens at positions start.."""
+    from coheryn_ai_studio_b200.parts import StepContext
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    pos = list(range(start, start + tokens_n))
+    table = list(range(pages_needed))[::-1]                      # pages in reverse order
+    slots = [table[p // page_size] * page_size + p % page_size for p in pos]
+    return StepContext(num_tokens=tokens_n, num_requests=1, token_ids=i32([0] * tokens_n), positions=i32(pos),
+                       token_req=i32([0] * tokens_n), cu_q=i32([0, tokens_n]), kv_lens=i32([start + tokens_n]),
+                       block_tables=[i32([table])] * groups, slots=[i32(slots)] * groups, state_slots=i32([0]),
+                       q_lens=[tokens_n], kv_lens_host=[start + tokens_n], max_q_len=tokens_n,
+                       max_kv_len=start + tokens_n)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from coheryn_ai_studio_b200.parts.norm import RMSNorm
+    rng = np.random.default_rng(0)
+    n = RMSNorm(rt(dtype), size=100, eps=1e-5)
+    assert n.tensor_specs()["weight"].shape == (100,)
+    w = (1 + 0.1 * rng.standard_normal(100)).astype(np.float32)
+    n.bind({"weight": dev(w)})
+    resid, delta = rng.standard_normal((5, 100)).astype(np.float32), rng.standard_normal((5, 100)).astype(np.float32)
+    r = dev(resid)
+    d = dev(delta, dtype)
+    out = n.forward(r, d)
+    x = resid + d.float().cpu().numpy()
+    ref = plain.rms_norm(x, w, 1e-5)
+    assert out.dtype == dtype and np.abs(out.float().cpu().numpy() - ref).max() <= (1e-5 if dtype == torch.float32 else 0.03)
+    assert np.array_equal(r.cpu().numpy(), x)
+
+
+def test_rope_part_angles():
+    from coheryn_ai_studio_b200.parts.position import RotateHalfRope
+    p = RotateHalfRope(rt(), head_dim=48, rotary_dim=48, theta=1e6, max_positions=700)
+    table = p.cos_sin().cpu().numpy()
+    for pos in (0, 1, 511, 699):
+        ang = plain.rope_angles(pos, 48, 1e6)
+        assert np.array_equal(table[pos, :, 0], np.cos(ang, dtype=np.float32))
+        assert np.array_equal(table[pos, :, 1], np.sin(ang, dtype=np.float32))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(6, 2, 32, None), (5, 5, 16, 7), (4, 1, 64, None)])
+def test_attention_part_in_two_portions(dtype, nh, nkv, hd, window):
+    """The mixer alone: a sequence in two portions through its own cache equals plain
+    attention over the whole sequence."""
+    from coheryn_ai_studio_b200.parts import LayerCache
+    from coheryn_ai_studio_b200.parts.attention import Attention
+    from coheryn_ai_studio_b200.parts.position import RotateHalfRope
+    rng = np.random.default_rng(nh)
+    H, T, page = 72, 29, 8
+    pos = RotateHalfRope(rt(dtype), hd, hd, 1e4, 64)
+    att = Attention(rt(dtype), hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd, qkv_bias=True,
+                    o_bias=False, window=window, scale=1 / np.sqrt(hd), position=pos)
+    w = {k: (rng.standard_normal(s.shape) * (0.2 if "weight" in k else 0.5)).astype(np.float32)
+         for k, s in att.tensor_specs().items()}
+    att.bind({k: dev(v, dtype) for k, v in w.items()})
+    wq = {k: dev(v, dtype).float().cpu().numpy() for k, v in w.items()}
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    xd = dev(x, dtype)
+    xq = xd.float().cpu().numpy()
+    pages = -(-T // page)
+    k_cache = torch.zeros(pages, nkv, page, hd, dtype=dtype, device=DEV)
+    cache = LayerCache(kind="paged", group=0, page_size=page, k=k_cache, v=torch.zeros_like(k_cache))
+    out = torch.cat([att.forward(xd[:18], one_request_step(18, 0, page, pages), cache),
+                     att.forward(xd[18:], one_request_step(T - 18, 18, page, pages), cache)])
+    q = plain.linear(xq, wq["q_proj.weight"], wq["q_proj.bias"])
+    k = plain.linear(xq, wq["k_proj.weight"], wq["k_proj.bias"])
+    v = plain.linear(xq, wq["v_proj.weight"], wq["v_proj.bias"])
+    positions = np.arange(T)
+    o = plain.attention(plain.rope(q, positions, hd, 1e4), plain.rope(k, positions, hd, 1e4), v, nh, nkv, hd, window)
+    ref = plain.linear(o, wq["o_proj.weight"])
+    tol = 2e-4 if dtype == torch.float32 else 0.03 * np.abs(ref).max()
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_mlp_part(dtype):
+    from coheryn_ai_studio_b200.parts.feedforward import GatedMLP
+    rng = np.random.default_rng(1)
+    ff = GatedMLP(rt(dtype), hidden_size=72, intermediate_size=200, activation="silu")
+    w = {k: (rng.standard_normal(s.shape) * 0.2).astype(np.float32) for k, s in ff.tensor_specs().items()}
+    ff.bind({k: dev(v, dtype) for k, v in w.items()})
+    wq = {k: dev(v, dtype).float().cpu().numpy() for k, v in w.items()}
+    xd = dev(rng.standard_normal((9, 72)).astype(np.float32), dtype)
+    xq = xd.float().cpu().numpy()
+    ref = plain.linear(plain.swiglu(plain.linear(xq, wq["gate_proj.weight"]), plain.linear(xq, wq["up_proj.weight"])),
+                       wq["down_proj.weight"])
+    out = ff.forward(xd, None)
+    tol = 1e-4 if dtype == torch.float32 else 0.03 * np.abs(ref).max()
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
+    with pytest.raises(ValueError, match="gelu"):
+        GatedMLP(rt(dtype), 8, 8, "gelu")
+
+
+# ---------------------------------------------------------------------------------------
+# A toy architecture, defined and registered here.
+# ---------------------------------------------------------------------------------------
+def toy_decay_mixer_class():
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.parts import FixedState, Mixer
+    from coheryn_ai_studio_b200.weights import TensorSpec
+
+    class DecayMixer(Mixer):
+        """State of its own: s_t = decay * s_{t-1} + x_t per request; y_t = W s_t."""
+
+        def __init__(self, runtime, hidden_size, decay, position=None):
+            super().__init__(runtime)
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def cache_requirement(self):
+            return FixedState((self.hidden_size,), torch.float32)
+
+        def tensor_specs(self):
+            return {"mix.weight": TensorSpec((self.hidden_size, self.hidden_size))}
+
+        def bind(self, tensors):
+            self.w = tensors["mix.weight"]
+
+        def forward(self, x, step, cache):
+            assert cache.kind == "state"
+            out = torch.empty_like(x, dtype=torch.float32)
+            cu = step.cu_q.tolist()
+            for b, slot in enumerate(step.state_slots.tolist()):
+                s = cache.state[slot]
+                for t in range(cu[b], cu[b + 1]):
+                    s = self.decay * s + x[t].float()
+                    out[t] = s
+                cache.state[slot] = s
+            return ops.linear(out.to(x.dtype), self.w)
+    return DecayMixer
+
+
+def toy_spec(c):
+    from coheryn_ai_studio_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    H = c["hidden_size"]
+    norm = PartSpec("rmsnorm", {"size": H, "eps": c["rms_norm_eps"]})
+    rope = PartSpec("rope_rotate_half", {"head_dim": c["head_dim"], "rotary_dim": c["head_dim"],
+                                         "theta": c["rope_theta"], "max_positions": c["max_position_embeddings"]})
+    def attn(window):
+        return PartSpec("attention", {"hidden_size": H, "num_heads": c["num_attention_heads"],
+                                      "num_kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"],
+                                      "qkv_bias": True, "o_bias": False, "window": window,
+                                      "scale": c["head_dim"] ** -0.5})
+    ff = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": c["intermediate_size"], "activation": "silu"})
+    layers = [
+        LayerSpec("model.layers.0", "prenorm_residual", attn(None), ff, norm, norm, rope),
+        LayerSpec("model.layers.1", "prenorm_residual", PartSpec("test_decay", {"hidden_size": H, "decay": 0.5}), ff, norm, norm),
+        LayerSpec("model.layers.2", "prenorm_residual", attn(c["window"]), ff, norm, norm, rope),
+    ]
+    # layer 0 twice (two caches), the toy layer, the windowed layer, then layer 0 a third
+    # time reading the cache its FIRST run wrote
+    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2), ScheduleEntry(0, cache_from=0)]
+    return ModelSpec("ToyStateForCausalLM", H, c["vocab_size"], c["max_position_embeddings"], "model.embed_tokens",
+                     layers, schedule, norm, "model.norm", "lm_head")
+
+
+class ToyConfig(dict):
+    def to_dict(self):
+        return dict(self)
+
+
+TOY = ToyConfig(architectures=["ToyStateForCausalLM"], hidden_size=48, num_attention_heads=3, num_key_value_heads=1,
+                head_dim=16, intermediate_size=80, vocab_size=130, rms_norm_eps=1e-5, rope_theta=1e4,
+                max_position_embeddings=128, window=11)
+
+
+def toy_plain_forward(cfg, w, ids):
+    """The toy model over a whole sequence, from the plain parts."""
+    T = len(ids)
+    positions = np.arange(T)
+    hd, nh, nkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    x = plain.embedding(w["model.embed_tokens.weight"], ids)
+    kept = {}
+
+    def attention_layer(x, i, window, entry, cache_from=None):
+        p = f"model.layers.{i}."
+        y = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        q = plain.rope(plain.linear(y, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]), positions, hd, cfg["rope_theta"])
+        if cache_from is None:
+            k = plain.rope(plain.linear(y, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]), positions, hd, cfg["rope_theta"])
+            v = plain.linear(y, w[p + "self_attn.v_proj.weight"], w[p + "self_attn.v_proj.bias"])
+            kept[entry] = (k, v)
+        else:
+            k, v = kept[cache_from]
+        o = plain.attention(q, k, v, nh, nkv, hd, window)
+        return (x + plain.linear(o, w[p + "self_attn.o_proj.weight"])).astype(np.float32)
+
+    def decay_layer(x, i):
+        p = f"model.layers.{i}."
+        y = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        s, rows = np.zeros(y.shape[1], np.float32), []
+        for t in range(T):
+            s = (np.float32(0.5) * s + y[t]).astype(np.float32)
+            rows.append(s)
+        return (x + plain.linear(np.stack(rows), w[p + "self_attn.mix.weight"])).astype(np.float32)
+
+    def mlp(x, i):
+        p = f"model.layers.{i}."
+        y = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        a = plain.swiglu(plain.linear(y, w[p + "mlp.gate_proj.weight"]), plain.linear(y, w[p + "mlp.up_proj.weight"]))
+        return (x + plain.linear(a, w[p + "mlp.down_proj.weight"])).astype(np.float32)
+
+    x = mlp(attention_layer(x, 0, None, 0), 0)
+    x = mlp(decay_layer(x, 1), 1)
+    x = mlp(attention_layer(x, 0, None, 2), 0)
+    x = mlp(attention_layer(x, 2, cfg["window"], 3), 2)
+    x = mlp(attention_layer(x, 0, None, 4, cache_from=0), 0)
+    return plain.linear(plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), w["lm_head.weight"])
+
+
+@pytest.fixture(scope="module")
+def toy_folder(tmp_path_factory):
+    from coheryn_ai_studio_b200.config import register_architecture, unregister_architecture
+    from coheryn_ai_studio_b200.engine import write_random_model
+    from coheryn_ai_studio_b200.parts import MIXERS, register_mixer
+    from coheryn_ai_studio_b200.weights import InitPolicy
+    register_mixer("test_decay", toy_decay_mixer_class())
+    register_architecture("ToyStateForCausalLM", lambda obj: ToyConfig(obj), toy_spec)
+    d = str(tmp_path_factory.mktemp("toy") / "model")
+    write_random_model(d, TOY, 7, InitPolicy(0.08, 0.2, 0.05))
+    yield d
+    unregister_architecture("ToyStateForCausalLM")
+    MIXERS.pop("test_decay", None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_steps_through_the_engine(toy_folder, dtype):
+    """Registered, built from config.json, loaded by tensor name and stepped in portions
+    beside another request, with no change to the framework."""
+    from replay import Replay
+    cfg, w = plain.read_model(toy_folder)
+    assert "model.layers.1.self_attn.mix.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+    rng = np.random.default_rng(3)
+    seqs = {"a": rng.integers(0, 130, 45).tolist(), "b": rng.integers(0, 130, 30).tolist()}
+    r = Replay(toy_folder, dtype, max_tokens=128, page_size=8)
+    assert len(r.cache.groups) == 2                       # full attention (2 entries) and the window
+    assert [len(g.entries) for g in r.cache.groups] == [2, 1]
+    r.step([("a", seqs["a"][:20], list(range(20)))])
+    r.step([("a", seqs["a"][20:23], [0, 1, 2]), ("b", seqs["b"][:17], list(range(17)))])
+    r.step([("a", seqs["a"][23:], list(range(22))), ("b", seqs["b"][17:19], [0, 1])])
+    for t in range(19, 30):
+        r.step([("b", [seqs["b"][t]], [0])])
+    # the window (11) has passed the first pages of 8: they went back to the pool
+    assert r.cache.block_table("a", 1)[:4] == [-1] * 4 and r.cache.block_table("a", 0)[0] >= 0
+    for rid, seq in seqs.items():
+        ref = toy_plain_forward(cfg, w, seq)
+        for (k, pos), row in r.rows.items():
+            if k == rid:
+                tol = 2e-4 if dtype == "float32" else 0.04 * max(1.0, np.abs(ref[pos]).max())
+                assert np.abs(row - ref[pos]).max() <= tol, (rid, pos)
+    r.cache.free("a"); r.cache.free("b"); r.cache.check()
+    assert r.cache.available_pages() == [16, 16]
