@@ -1,0 +1,327 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode throughput at the layer sizes of
+Qwen2.5-1.5B (random bfloat16 weights, batch 8, context 4,096), plus prefill of a
+2,048-token prompt, decode at batch 1 and 64, and the achieved fraction of the roofline.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  ``value`` is decoded tokens per second
+from CUDA events around K back-to-back decode steps (inputs of every step copied from
+pinned host memory, no host synchronisation inside the timed region).  ``e2e`` is the
+same workload through ``Engine.step()``, the call a user makes: host token ids in, host
+token ids out, every step.
+
+The cache of the timed requests is filled with random keys and values (their prompts are
+not run); weights and caches are far larger than the 126 MB L2, so every step streams
+them from HBM.  One JSON line is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen2.5-1.5B layer sizes.
+SIZES = dict(vocab_size=151936, hidden_size=1536, intermediate_size=8960, num_hidden_layers=28,
+             num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+             max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6,
+             tie_word_embeddings=True)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    src = "fallback"
+    p = dict(FALLBACK_PEAKS)
+    if os.path.isfile(path):
+        try:
+            obj = json.load(open(path))
+            flat = {}
+
+            def walk(o):
+                if isinstance(o, dict):
+                    for k, v in o.items():
+                        if isinstance(v, (int, float)) and not isinstance(v, bool):
+                            flat.setdefault(k, float(v))
+                        else:
+                            walk(v)
+            walk(obj)
+            if "hbm_gbs" in flat:
+                p["hbm_gbs"] = flat["hbm_gbs"]
+            if "bf16_tflops" in flat:
+                p["bf16_tflops"] = flat["bf16_tflops"]
+            if "bf16_tflops_sustained" in flat:
+                p["bf16_tflops_sustained"] = flat["bf16_tflops_sustained"]
+            src = "measured"
+        except Exception:
+            pass
+    p["source"] = src
+    return p
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def window(self, t0, t1):
+        rows = [l.split(", ") for t, l in self.lines if t0 <= t <= t1 + 0.15 and l]
+        if not rows:
+            rows = [l.split(", ") for _, l in self.lines[-3:] if l]
+        return rows
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    @staticmethod
+    def summary(rows):
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                mhz.append(int(r[0])); mx = max(mx, int(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"],
+                    help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace (no setup.py/pyproject.toml, pip reports "
+                          "'not installable') and this image has no cargo/rustc; it is CPU-only"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.engine import Engine, StepEntry, random_model_on_device
+    from coheryn_ai_studio_b200.engine.scheduler import Request
+    from coheryn_ai_studio_b200.sampling import RequestSampler, SamplingParams
+
+    pk = peaks()
+    sizes = dict(SIZES, num_hidden_layers=args.layers)
+    cfg = Qwen2Config(**sizes)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    model = random_model_on_device(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    V, H, I, L = cfg.vocab_size, cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
+    nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    layer_params = (nh + 2 * nkv) * hd * H + H * nh * hd + 3 * H * I
+    weight_bytes = 2 * (L * layer_params + V * H) + 2 * L * ((nh + 2 * nkv) * hd + 2 * H) + 4 * H
+    kv_bytes_per_token = 2 * L * nkv * hd * 2
+    total_steps = args.warmup + args.steps
+
+    sampler = ClockSampler()
+    sampler.start()
+
+    def make_engine(batch):
+        margin = 2 * total_steps + 8
+        eng = Engine(model, dtype="bfloat16", context=args.context, max_num_seqs=batch,
+                     max_num_batched_tokens=max(2048, args.prefill_tokens), page_size=args.page_size,
+                     kv_cache_tokens=batch * (args.context + 64), prefix_reuse=False,
+                     use_graphs=not args.no_graphs)
+        for g in eng.cache.groups:
+            g.tensor.normal_(0.0, 1.0)
+        rng = np.random.default_rng(1234 + batch)
+        lens = np.minimum(rng.integers(512, args.context + 1, size=batch), args.context - margin)
+        return eng, [int(x) for x in lens], rng
+
+    def inject(eng, lens, rng):
+        """Requests that have 'run' their prompts: pages reserved and committed, contents
+        random.  Returns the Request objects (already in the scheduler's running list)."""
+        reqs = []
+        for i, n in enumerate(lens):
+            prompt = rng.integers(0, V, size=n).tolist()
+            req = Request(f"bench-{i}", prompt, max_tokens=4 * total_steps + 64, params=SamplingParams())
+            req.sampler = RequestSampler(req.params)
+            req.arrival = i
+            assert eng.cache.admit(req.request_id) is not None
+            assert eng.cache.reserve(req.request_id, prompt[:-1])
+            eng.cache.commit(req.request_id)
+            req.num_computed = n - 1
+            eng.scheduler.running.append(req)
+            eng._requests[req.request_id] = req
+            from coheryn_ai_studio_b200.engine.engine import _Timing
+            eng._timing[req.request_id] = _Timing(time.perf_counter())
+            reqs.append(req)
+        return reqs
+
+    def decode_device_timed(batch, steps, warmup):
+        """K decode steps back to back, timed on the device."""
+        eng, lens, rng = make_engine(batch)
+        ids = [f"d{i}" for i in range(batch)]
+        for rid, n in zip(ids, lens):
+            assert eng.cache.admit(rid) is not None
+            assert eng.cache.reserve(rid, [0] * n)
+            eng.cache.commit(rid)
+        out = torch.empty(batch, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        toks = rng.integers(0, V, size=(warmup + steps, batch))
+
+        def one(k):
+            logits = eng.runner.step([StepEntry(rid, [int(toks[k, b])], [0]) for b, rid in enumerate(ids)])
+            ops.argmax(logits, out, status)
+        for k in range(warmup):
+            one(k)
+        torch.cuda.synchronize()
+        l0 = ops.total_launch_count() + eng.runner.graph_launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record()
+        for k in range(warmup, warmup + steps):
+            one(k)
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        ms = e0.elapsed_time(e1)
+        launches = ops.total_launch_count() + eng.runner.graph_launches - l0
+        mean_ctx = float(np.mean(lens)) + warmup + steps / 2
+        step_bytes = weight_bytes + batch * mean_ctx * kv_bytes_per_token
+        del eng
+        torch.cuda.empty_cache()
+        return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches,
+                "bytes_per_step": step_bytes, "window": (t0, t1), "mean_ctx": mean_ctx}
+
+    def decode_end_to_end(batch, steps, warmup):
+        eng, lens, rng = make_engine(batch)
+        inject(eng, lens, rng)
+        for _ in range(warmup):
+            eng.step()
+        torch.cuda.synchronize()
+        h2d = d2h = 0
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            events = eng.step()
+            h2d += eng.runner.h2d_bytes
+            d2h += 4 * len(events) + 8        # sampled ids and the two status words
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        del eng
+        torch.cuda.empty_cache()
+        return {"value": batch * steps / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d // steps,
+                "d2h_bytes_per_step": d2h // steps, "ms_per_step": dt / steps * 1e3}
+
+    def prefill_timed(tokens, repeats=3):
+        eng, _, rng = make_engine(1)
+        best = None
+        for r in range(repeats + 1):            # the first run is the warm-up
+            rid = f"p{r}"
+            prompt = rng.integers(0, V, size=tokens).tolist()
+            eng.cache.admit(rid)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.runner.step([StepEntry(rid, prompt, [tokens - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            eng.cache.free(rid)
+            if r > 0:
+                best = ms if best is None else min(best, ms)
+        flops = 2.0 * tokens * L * layer_params + 2.0 * V * H + L * 4.0 * nh * hd * tokens * (tokens + 1) / 2
+        peak = pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]) * 1e12
+        del eng
+        torch.cuda.empty_cache()
+        return {"value": tokens / (best / 1e3), "tokens": tokens, "ms": best, "frac": flops / (best / 1e3) / peak,
+                "tflops": flops / (best / 1e3) / 1e12}
+
+    main_run = decode_device_timed(args.batch, args.steps, args.warmup)
+    clocks = ClockSampler.summary(sampler.window(*main_run["window"]))
+    e2e = decode_end_to_end(args.batch, args.steps, args.warmup)
+    prefill = prefill_timed(args.prefill_tokens)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = decode_device_timed(b, max(16, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(r["bytes_per_step"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+    sampler.stop()
+
+    achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode_tokens_per_s", "value": round(main_run["tok_s"], 1), "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-1.5B layer sizes, random weights", "global_batch": args.batch,
+            "seq_len": args.context, "parallelism": "single-gpu", "layers": L,
+            "layers_of_config": SIZES["num_hidden_layers"], "hidden": H, "heads": nh, "kv_heads": nkv,
+            "head_dim": hd, "intermediate": I, "vocab": V, "tied_embeddings": True,
+            "context_per_request": "uniform[512,4096]", "mean_context": round(main_run["mean_ctx"], 1),
+            "page_size": args.page_size, "cuda_graphs": not args.no_graphs,
+            "l2": "weights+cache per step exceed L2 (126 MB)", "peaks": pk["source"],
+        },
+        "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": int(main_run["launches"]),
+        "clocks": clocks,
+        "prefill": {"value": round(prefill["value"], 1), "tokens": prefill["tokens"], "ms": round(prefill["ms"], 3),
+                    "frac": round(prefill["frac"], 4), "tflops": round(prefill["tflops"], 1)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

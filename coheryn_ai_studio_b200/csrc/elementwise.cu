@@ -91,7 +91,8 @@ CO_EXPORT int coheryn_add_rmsnorm(float* resid, const void* delta, int delta_dty
 }
 
 // ---------------------------------------------------------------------------------
-// Gated activation: out[m, j] = silu(in[m, j]) * in[m, I + j], in is [M, 2I].
+// Gated activation over interleaved columns: out[m, j] = silu(in[m, 2j]) * in[m, 2j+1],
+// in is [M, 2I] (column 2j = gate_j, column 2j+1 = up_j).
 // silu(g) = g / (1 + exp(-g)) in float32.
 // ---------------------------------------------------------------------------------
 template <typename T>
@@ -99,8 +100,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const size_t m = i / I, j = i % I;
-    const float g = co_to_float(in[m * 2 * I + j]);
-    const float u = co_to_float(in[m * 2 * I + I + j]);
+    const float g = co_to_float(in[m * 2 * I + 2 * j]);
+    const float u = co_to_float(in[m * 2 * I + 2 * j + 1]);
     out[i] = co_from_float<T>((g / (1.0f + expf(-g))) * u);
   }
 }

@@ -1,0 +1,183 @@
+// out[M, N] = x[M, K] . W[N, K]^T (+ bias) for few rows (M <= 64), bfloat16 operands,
+// float32 accumulation on the tensor cores (mma.sync m16n8k16).  This is the matrix
+// product of decode steps: it is bound by reading W once from HBM, so the kernel is
+// shaped around the weight stream, not around the arithmetic.
+//
+// A CTA owns NT*8 consecutive rows of W (output features) for ALL tokens; its warps
+// split K in interleaved blocks of 32 (warp w takes blocks w, w+W, ...), each thread
+// fetching 16 contiguous bytes of a W row per block with a streaming load.  Tokens sit
+// on the M axis of the MMA (tiles of 16, zero padded), features on the N axis (tiles of
+// 8).  The k order inside a block is permuted identically for both operands so that a
+// thread's 16 bytes feed two MMAs without a shuffle.  Per-warp partial sums are combined
+// through shared memory in warp order.  An output element is therefore always summed in
+// the same order, whatever M is: a row's result does not depend on the batch around it.
+//
+// Epilogues: bias; or gated SiLU over interleaved rows (row 2j = gate_j, row 2j+1 = up_j:
+// out[m, j] = silu(acc[2j]) * acc[2j+1]), which keeps a gate/up pair in one thread.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int EPI_PLAIN = 0, EPI_GATED_SILU = 1;
+
+template <int MT, int NT>
+__global__ void __launch_bounds__(256)
+gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                  const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype,
+                  int M, int N, int K, long ldx, long ldo, int epilogue) {
+  extern __shared__ float red[];  // [warps][MT][NT][4][32]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_base = blockIdx.x * NT * 8;
+
+  const __nv_bfloat16* wrow[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) wrow[nt] = w + (size_t)min(n_base + nt * 8 + g, N - 1) * K;
+  const __nv_bfloat16* xrow[MT][2];
+  bool xok[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = mt * 16 + h * 8 + g;
+      xok[mt][h] = m < M;
+      xrow[mt][h] = x + (size_t)min(m, M - 1) * ldx;
+    }
+
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+
+  const int nblk = (K + 31) >> 5;
+#pragma unroll 4
+  for (int blk = warp; blk < nblk; blk += warps) {
+    const int k = (blk << 5) + (t << 3);
+    const bool valid = k < K;  // K is a multiple of 8: a 16-byte piece is whole or absent
+    uint4 wv[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) wv[nt] = valid ? ld_stream(wrow[nt] + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const uint4 xa = (valid && xok[mt][0]) ? __ldg((const uint4*)(xrow[mt][0] + k)) : make_uint4(0, 0, 0, 0);
+      const uint4 xb = (valid && xok[mt][1]) ? __ldg((const uint4*)(xrow[mt][1] + k)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        mma_bf16(acc[mt][nt], xa.x, xb.x, xa.y, xb.y, wv[nt].x, wv[nt].y);
+        mma_bf16(acc[mt][nt], xa.z, xb.z, xa.w, xb.w, wv[nt].z, wv[nt].w);
+      }
+    }
+  }
+
+  // Partial sums of every warp, laid out so that lanes write consecutive words.
+  constexpr int E = MT * NT * 4 * 32;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[warp * E + ((mt * NT + nt) * 4 + i) * 32 + lane] = acc[mt][nt][i];
+  __syncthreads();
+
+  // One thread per pair of neighbouring features (i = 0,1 or 2,3 of a fragment).
+  constexpr int PAIRS = MT * NT * 2 * 32;
+  for (int e = threadIdx.x; e < PAIRS; e += blockDim.x) {
+    const int l = e & 31, half = (e >> 5) & 1, tile = e >> 6;
+    const int nt = tile % NT, mt = tile / NT;
+    const int m = mt * 16 + half * 8 + (l >> 2);
+    const int n = n_base + nt * 8 + (l & 3) * 2;
+    if (m >= M || n >= N) continue;
+    const int base = ((mt * NT + nt) * 4 + half * 2) * 32 + l;
+    float v0 = 0.f, v1 = 0.f;
+    for (int wi = 0; wi < warps; ++wi) {
+      v0 += red[wi * E + base];
+      v1 += red[wi * E + base + 32];
+    }
+    if (epilogue == EPI_GATED_SILU) {
+      // rows (n, n+1) = (gate_j, up_j), j = n / 2
+      const float r = (v0 / (1.0f + __expf(-v0))) * v1;
+      const size_t o = (size_t)m * ldo + (n >> 1);
+      if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
+      else ((float*)out)[o] = r;
+      continue;
+    }
+    const bool has1 = n + 1 < N;
+    if (bias) {
+      v0 += co_load_any(bias, bias_dtype, n);
+      if (has1) v1 += co_load_any(bias, bias_dtype, n + 1);
+    }
+    const size_t o = (size_t)m * ldo + n;
+    if (out_dtype == CO_BF16) {
+      __nv_bfloat16* p = (__nv_bfloat16*)out + o;
+      if (has1 && ((o & 1) == 0)) *(__nv_bfloat162*)p = __floats2bfloat162_rn(v0, v1);
+      else { p[0] = __float2bfloat16_rn(v0); if (has1) p[1] = __float2bfloat16_rn(v1); }
+    } else {
+      float* p = (float*)out + o;
+      p[0] = v0;
+      if (has1) p[1] = v1;
+    }
+  }
+}
+
+template <int MT, int NT>
+int launch_small(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                 int M, int N, int K, long ldx, long ldo, int epilogue, int warps, cudaStream_t stream) {
+  const size_t smem = (size_t)warps * MT * NT * 4 * 32 * sizeof(float);
+  auto kernel = gemm_small_kernel<MT, NT>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) CO_FAIL("gemm_small: shared memory %zu: %s", smem, cudaGetErrorString(e));
+  }
+  const int grid = (N + NT * 8 - 1) / (NT * 8);
+  kernel<<<grid, warps * 32, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype,
+                                             out, out_dtype, M, N, K, ldx, ldo, epilogue);
+  CO_CHECK_LAUNCH("gemm_small");
+  return 0;
+}
+}  // namespace
+
+// x: [M, K] bfloat16, row stride ldx (elements, a multiple of 8, base 16-byte aligned);
+// w: [N, K] bfloat16 contiguous; K a multiple of 8; M <= 64.
+// epilogue 0: out[M, N] (+ bias); 1: gated SiLU over interleaved rows, out[M, N/2].
+CO_EXPORT int coheryn_gemm_bf16_small(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
+                                      int out_dtype, int M, int N, int K, long ldx, long ldo, int epilogue,
+                                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64) CO_FAIL("gemm_bf16_small: M = %d exceeds 64", M);
+  if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_small: K = %d and the row stride %ld must be multiples of 8", K, ldx);
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_small: operands must be 16-byte aligned");
+  if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_small: gated epilogue needs an even number of rows");
+  if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_small: unknown epilogue %d", epilogue);
+  // Rows per CTA: as many as keep at least ~2 CTAs per SM (148 SMs); more rows per CTA
+  // mean fewer re-reads of x through L2.
+  const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
+  int nt = 8 / mt;  // MT * NT <= 8 bounds registers and the reduction buffer
+  while (nt > 1 && (N + nt * 8 - 1) / (nt * 8) < 296) nt >>= 1;
+  const int nblk = (K + 31) / 32;
+  const int warps = nblk >= 8 ? 8 : (nblk >= 4 ? 4 : (nblk >= 2 ? 2 : 1));
+#define GO(MT_, NT_) return launch_small<MT_, NT_>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, ldo, epilogue, warps, stream)
+  if (mt == 1) { if (nt == 8) GO(1, 8); if (nt == 4) GO(1, 4); if (nt == 2) GO(1, 2); GO(1, 1); }
+  if (mt == 2) { if (nt == 4) GO(2, 4); if (nt == 2) GO(2, 2); GO(2, 1); }
+  if (nt == 2) GO(4, 2);
+  GO(4, 1);
+#undef GO
+}

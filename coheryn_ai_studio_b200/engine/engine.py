@@ -51,10 +51,11 @@ class Engine:
     def __init__(self, model, *, dtype="bfloat16", context: int = 4096, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 2048, page_size: int = 16,
                  num_pages: Optional[int] = None, kv_cache_tokens: Optional[int] = None,
-                 prefix_reuse: bool = True, eos_token_ids: Sequence[int] = ()):
+                 prefix_reuse: bool = True, eos_token_ids: Sequence[int] = (), use_graphs: bool = True):
         """``model`` is a DecoderModel on the device.  The cache pool holds ``num_pages``
         pages per group, or enough for ``kv_cache_tokens`` tokens, or by default enough for
-        ``max_num_seqs`` requests of ``context`` tokens."""
+        ``max_num_seqs`` requests of ``context`` tokens.  ``use_graphs`` replays decode steps
+        from CUDA graphs (one per batch size, captured at first use)."""
         self.model = model
         spec = model.spec
         if context < 1 or context > spec.max_positions:
@@ -68,7 +69,7 @@ class Engine:
                                   parse_dtype(dtype), model.runtime.device, page_size=page_size,
                                   num_pages=num_pages, max_requests=max_num_seqs,
                                   prefix_reuse=prefix_reuse)
-        self.runner = StepRunner(model, self.cache)
+        self.runner = StepRunner(model, self.cache, use_graphs=use_graphs, graph_max_kv_len=context)
         self.scheduler = Scheduler(self.cache, context, max_num_seqs, max_num_batched_tokens)
         self.sampler = DeviceSampler(model.runtime.device)
         self.eos_token_ids = tuple(eos_token_ids)

@@ -7,15 +7,20 @@ exactly one token per lane (crates/coheryn-engine/src/inference/batch.rs:64-116)
 returns logits for every lane; here a lane carries any number of tokens and logits are
 computed for the wanted rows alone (the non-output shortcut of
 crates/coheryn-engine/src/inference.rs:481-485 taken further).
+
+Steps in which every request brings exactly one token and wants its logits (decoding) can
+be replayed from a CUDA graph: the launch sequence is captured once per batch size over
+static index buffers, and a step then costs one host-to-device copy and one graph launch.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager
 from ..parts.base import StepContext
 from ..parts.model import DecoderModel
@@ -32,22 +37,111 @@ class StepEntry:
     want: Sequence[int] = ()      # places among ``tokens`` whose logits are wanted
 
 
+@dataclass
+class _Layout:
+    """A batch as host arrays (all int32)."""
+    B: int
+    T: int
+    ids: np.ndarray
+    pos: np.ndarray
+    req: np.ndarray
+    cu: np.ndarray
+    kv_lens: np.ndarray
+    state_slots: np.ndarray
+    rows: np.ndarray
+    tables: List[List[List[int]]]     # per group, per request: pages
+    slots: List[np.ndarray]           # per group: [T]
+    q_lens: List[int]
+
+
+class _DecodeGraph:
+    """The captured launch sequence of a decode step for one batch size."""
+
+    def __init__(self, runner: "StepRunner", B: int):
+        self.B = B
+        groups = len(runner.cache.groups)
+        self.width = runner.graph_table_width
+        sizes = [("ids", B), ("pos", B), ("req", B), ("cu", B + 1), ("kv_lens", B), ("state_slots", B),
+                 ("rows", B)]
+        for g in range(groups):
+            sizes += [(f"table{g}", B * self.width), (f"slots{g}", B)]
+        total = sum(n for _, n in sizes)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=runner.device)
+        self.h: Dict[str, np.ndarray] = {}
+        self.d: Dict[str, torch.Tensor] = {}
+        o = 0
+        host_np = self.host.numpy()
+        for name, n in sizes:
+            self.h[name] = host_np[o:o + n]
+            self.d[name] = self.dev[o:o + n]
+            o += n
+        self.ctx = StepContext(
+            num_tokens=B, num_requests=B, token_ids=self.d["ids"], positions=self.d["pos"],
+            token_req=self.d["req"], cu_q=self.d["cu"], kv_lens=self.d["kv_lens"],
+            block_tables=[self.d[f"table{g}"].view(B, self.width) for g in range(groups)],
+            slots=[self.d[f"slots{g}"] for g in range(groups)], state_slots=self.d["state_slots"],
+            q_lens=[1] * B, kv_lens_host=[], max_q_len=1, max_kv_len=runner.graph_max_kv_len)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.launches = 0
+
+    def fill(self, lay: _Layout) -> None:
+        h = self.h
+        h["ids"][:] = lay.ids; h["pos"][:] = lay.pos; h["req"][:] = lay.req; h["cu"][:] = lay.cu
+        h["kv_lens"][:] = lay.kv_lens; h["state_slots"][:] = lay.state_slots; h["rows"][:] = lay.rows
+        for g, lists in enumerate(lay.tables):
+            tab = h[f"table{g}"].reshape(self.B, self.width)
+            for b, pages in enumerate(lists):
+                tab[b, :len(pages)] = pages
+            h[f"slots{g}"][:] = lay.slots[g]
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def run(self, runner: "StepRunner") -> torch.Tensor:
+        if self.graph is None:
+            side = torch.cuda.Stream(device=runner.device)
+            side.wait_stream(torch.cuda.current_stream(runner.device))
+            with torch.cuda.stream(side):
+                for _ in range(2):     # loads libraries and sets kernel attributes outside the capture
+                    runner.model.forward(self.ctx, runner.layer_caches, self.d["rows"])
+            torch.cuda.current_stream(runner.device).wait_stream(side)
+            before = ops.total_launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.logits = runner.model.forward(self.ctx, runner.layer_caches, self.d["rows"])
+            self.launches = ops.total_launch_count() - before
+            self.graph = graph
+        self.graph.replay()
+        runner.graph_launches += self.launches
+        return self.logits
+
+
 class StepRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager):
+    def __init__(self, model: DecoderModel, cache: CacheManager, use_graphs: bool = False,
+                 graph_max_kv_len: Optional[int] = None):
+        """``use_graphs`` replays decode steps from CUDA graphs; ``graph_max_kv_len`` bounds
+        the length a request can reach while graphs are used (default: the model's
+        positions)."""
         self.model, self.cache = model, cache
         self.device = model.runtime.device
         self.layer_caches = cache.layer_caches()
         self.steps_run = 0
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.graph_max_kv_len = int(graph_max_kv_len or model.spec.max_positions)
+        self.graph_table_width = max(1, -(-self.graph_max_kv_len // cache.page_size))
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self.graph_launches = 0       # kernel launches replayed from graphs
+        self.h2d_bytes = 0            # bytes copied to the device by the last step
 
     def _to_device(self, array: np.ndarray) -> torch.Tensor:
         t = torch.from_numpy(array)
+        self.h2d_bytes += array.nbytes
         if self.device.type == "cuda":
             t = t.pin_memory()
         return t.to(self.device, non_blocking=True)
 
-    def build_context(self, entries: Sequence[StepEntry]):
-        """Reserve pages and lay the batch out for the device.  Raises OutOfPages (with
-        every reservation of this step undone) when the pool is too small."""
+    # ------------------------------------------------------------------ host side
+    def _check(self, entries: Sequence[StepEntry]) -> None:
         cache, spec = self.cache, self.model.spec
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -69,19 +163,22 @@ class StepRunner:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.request_id!r} wants the logits of place {w} "
                                      f"of {len(e.tokens)} tokens")
+
+    def _reserve(self, entries: Sequence[StepEntry]) -> None:
         done: List[str] = []
         for e in entries:
-            if not cache.reserve(e.request_id, e.tokens):
+            if not self.cache.reserve(e.request_id, e.tokens):
                 for rid in done:
-                    cache.rollback(rid)
+                    self.cache.rollback(rid)
                 raise OutOfPages(f"no cache pages left for {len(e.tokens)} more tokens of request "
-                                 f"{e.request_id!r} (available per group: {cache.available_pages()})")
+                                 f"{e.request_id!r} (available per group: {self.cache.available_pages()})")
             done.append(e.request_id)
 
+    def _layout(self, entries: Sequence[StepEntry]) -> _Layout:
+        cache = self.cache
         B = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         starts = [cache.length(e.request_id) for e in entries]
-        kv_lens = [s + n for s, n in zip(starts, q_lens)]
         T = sum(q_lens)
         ids = np.empty(T, np.int32); pos = np.empty(T, np.int32); req = np.empty(T, np.int32)
         cu = np.zeros(B + 1, np.int32)
@@ -95,32 +192,65 @@ class StepRunner:
             rows.extend(o + int(w) for w in e.want)
             o += n
             cu[b + 1] = o
-        tables, slots = [], []
-        for gi in range(len(cache.groups)):
-            lists = [cache.block_table(e.request_id, gi) for e in entries]
+        groups = range(len(cache.groups))
+        return _Layout(
+            B=B, T=T, ids=ids, pos=pos, req=req, cu=cu,
+            kv_lens=np.asarray([s + n for s, n in zip(starts, q_lens)], np.int32),
+            state_slots=np.asarray([cache.state_slot(e.request_id) for e in entries], np.int32),
+            rows=np.asarray(rows, np.int32),
+            tables=[[cache.block_table(e.request_id, g) for e in entries] for g in groups],
+            slots=[np.concatenate([np.asarray(cache.slot_ids(e.request_id, g), np.int32) for e in entries])
+                   for g in groups],
+            q_lens=q_lens)
+
+    def _context(self, lay: _Layout):
+        tables = []
+        for lists in lay.tables:
             width = max(1, max(len(l) for l in lists))
-            bt = np.full((B, width), -1, np.int32)
+            bt = np.full((lay.B, width), -1, np.int32)
             for b, l in enumerate(lists):
                 bt[b, :len(l)] = l
             tables.append(self._to_device(bt))
-            sl = np.concatenate([np.asarray(cache.slot_ids(e.request_id, gi), np.int32) for e in entries])
-            slots.append(self._to_device(sl))
+        kv = lay.kv_lens.tolist()
         ctx = StepContext(
-            num_tokens=T, num_requests=B,
-            token_ids=self._to_device(ids), positions=self._to_device(pos),
-            token_req=self._to_device(req), cu_q=self._to_device(cu),
-            kv_lens=self._to_device(np.asarray(kv_lens, np.int32)),
-            block_tables=tables, slots=slots,
-            state_slots=self._to_device(np.asarray([cache.state_slot(e.request_id) for e in entries], np.int32)),
-            q_lens=q_lens, kv_lens_host=kv_lens, max_q_len=max(q_lens), max_kv_len=max(kv_lens))
-        return ctx, self._to_device(np.asarray(rows, np.int32))
+            num_tokens=lay.T, num_requests=lay.B, token_ids=self._to_device(lay.ids),
+            positions=self._to_device(lay.pos), token_req=self._to_device(lay.req),
+            cu_q=self._to_device(lay.cu), kv_lens=self._to_device(lay.kv_lens), block_tables=tables,
+            slots=[self._to_device(s) for s in lay.slots], state_slots=self._to_device(lay.state_slots),
+            q_lens=lay.q_lens, kv_lens_host=kv, max_q_len=max(lay.q_lens), max_kv_len=max(kv))
+        return ctx, self._to_device(lay.rows)
+
+    def build_context(self, entries: Sequence[StepEntry]):
+        """Check, reserve pages and lay the batch out on the device (no graph)."""
+        self._check(entries)
+        self._reserve(entries)
+        return self._context(self._layout(entries))
+
+    # ------------------------------------------------------------------ the step
+    def _graphable(self, entries: Sequence[StepEntry], lay: _Layout) -> bool:
+        return (self.use_graphs and all(n == 1 for n in lay.q_lens)
+                and all(list(e.want) == [0] for e in entries)
+                and int(lay.kv_lens.max()) <= self.graph_max_kv_len)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the batch; returns float32 logits ``[wanted, vocab]`` on the device, in the
-        order of the entries and of their ``want`` lists."""
-        ctx, rows = self.build_context(entries)
+        order of the entries and of their ``want`` lists.  (With graphs the tensor is a
+        static buffer that the next decode step of the same size overwrites.)"""
+        self._check(entries)
+        self._reserve(entries)
+        self.h2d_bytes = 0
         try:
-            logits = self.model.forward(ctx, self.layer_caches, rows)
+            lay = self._layout(entries)
+            if self._graphable(entries, lay):
+                g = self._graphs.get(lay.B)
+                if g is None:
+                    g = self._graphs[lay.B] = _DecodeGraph(self, lay.B)
+                g.fill(lay)
+                self.h2d_bytes += g.host.numel() * 4
+                logits = g.run(self)
+            else:
+                ctx, rows = self._context(lay)
+                logits = self.model.forward(ctx, self.layer_caches, rows)
         except Exception:
             for e in entries:
                 self.cache.rollback(e.request_id)

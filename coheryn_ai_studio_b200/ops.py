@@ -29,6 +29,7 @@ def require_gpu() -> None:
 
 
 _core = None
+_attn_libs = {}
 
 
 def core():
@@ -44,6 +45,14 @@ def core():
 def launch_count() -> int:
     """Kernel launches made through the core library since it was loaded."""
     return int(core().coheryn_launch_count())
+
+
+def total_launch_count() -> int:
+    """Kernel launches made through every library of this package that is loaded."""
+    n = launch_count()
+    for lib in _attn_libs.values():
+        n += int(lib.coheryn_launch_count())
+    return n
 
 
 def _code(t: torch.Tensor) -> int:
@@ -117,7 +126,7 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[m, j] = silu(gate_up[m, j]) * gate_up[m, I + j]."""
+    """out[m, j] = silu(gate_up[m, 2j]) * gate_up[m, 2j + 1] (gate and up interleaved)."""
     _dev(gate_up, out)
     M, I2 = gate_up.shape
     assert I2 % 2 == 0 and out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
@@ -231,6 +240,26 @@ def apply_penalties(logits, rows, ids, counts, rep, freq, pres) -> None:
 
 
 # ------------------------------------------------------------------------------------
+def gemm_bf16_small(x, w, bias, out, gated: bool = False) -> None:
+    """Tensor-core product for at most 64 rows (decode); see csrc/gemm_bf16_small.cu."""
+    _dev(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == K
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N // 2 if gated else N)
+    lib = core()
+    _check(lib, lib.coheryn_gemm_bf16_small(
+        _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
+        c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)),
+        c_int(1 if gated else 0), _stream()))
+
+
+def _small_ok(x, w) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= 64
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x @ w.T (+ bias), float32 accumulation.  float32 operands use FMA on the CUDA
@@ -241,7 +270,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     if M == 0:
         return out
-    gemm_simt(x, w, bias, out)
+    if _small_ok(x, w):
+        gemm_bf16_small(x, w, bias, out)
+    else:
+        gemm_simt(x, w, bias, out)
     return out
 
 
@@ -252,24 +284,70 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     (``step`` is a StepContext).  Chooses the kernel by dtype and shape."""
     attention_rows(q, out, k_cache, v_cache, step.block_tables[group], step.token_req,
                    step.positions, num_heads, num_kv_heads, head_dim, page_size, window, scale,
-                   cu_q=step.cu_q, kv_lens=step.kv_lens, q_lens=step.q_lens)
+                   cu_q=step.cu_q, kv_lens=step.kv_lens, q_lens=step.q_lens, max_kv_len=step.max_kv_len)
+
+
+def attention_lib(head_dim: int):
+    lib = _attn_libs.get(head_dim)
+    if lib is None:
+        lib = build.attention_library(head_dim)
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_attn_scratch_floats.restype = ctypes.c_long
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        if lib.coheryn_attn_head_dim() != head_dim:
+            raise KernelError(f"attention library was built for head size {lib.coheryn_attn_head_dim()}, not {head_dim}")
+        _attn_libs[head_dim] = lib
+    return lib
 
 
 def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads, num_kv_heads,
-                   head_dim, page_size, window, scale, cu_q=None, kv_lens=None, q_lens=None) -> None:
+                   head_dim, page_size, window, scale, cu_q=None, kv_lens=None, q_lens=None,
+                   max_kv_len=None, force_simple=False) -> None:
     """Attention of rows (request token_req[i] at position positions[i]) over cache pages.
-    When the rows are whole runs of consecutive positions per request (``cu_q``,
-    ``kv_lens``, host ``q_lens``), the bfloat16 tensor-core kernels can take them."""
-    attention_simple(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads,
-                     num_kv_heads, head_dim, page_size, window, scale)
+    bfloat16 rows that are whole runs of consecutive positions per request, ending at the
+    request's last position (``cu_q``, ``kv_lens`` on the device, ``q_lens`` and
+    ``max_kv_len`` on the host) go to the tensor-core kernels when the head size is a
+    multiple of 16 up to 256; everything else goes to the float32-arithmetic kernel."""
+    fast = (not force_simple and q.dtype == torch.bfloat16 and cu_q is not None and kv_lens is not None
+            and q_lens is not None and max_kv_len is not None and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0)
+    if not fast:
+        attention_simple(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads,
+                         num_kv_heads, head_dim, page_size, window, scale)
+        return
+    _dev(q, out, k_cache, v_cache, block_tables, cu_q, kv_lens)
+    _i32(block_tables, "block_tables"); _i32(cu_q, "cu_q"); _i32(kv_lens, "kv_lens")
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == q.dtype and k_cache.dtype == q.dtype
+    G = num_heads // num_kv_heads
+    B = len(q_lens)
+    rows = [n * G for n in q_lens]
+    any_small = any(r <= 16 for r in rows)
+    any_large = any(r > 16 for r in rows)
+    lib = attention_lib(head_dim)
+    scratch, floats = None, 0
+    if any_small and G <= 16:
+        floats = int(lib.coheryn_attn_scratch_floats(c_int(B), c_int(num_kv_heads), c_int(max_kv_len)))
+        scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
+    _check(lib, lib.coheryn_attention_bf16(
+        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_q), _ptr(kv_lens), c_int(B),
+        c_int(num_heads), c_int(num_kv_heads), c_int(page_size), c_int(window or 0), c_float(scale),
+        c_int(max(rows)), c_int(1 if any_small else 0), c_int(1 if any_large else 0), c_int(max_kv_len),
+        _ptr(scratch), c_long(floats), _stream()))
 
 
 def gated_silu_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(x @ Wg.T) * (x @ Wu.T) for w_gate_up = [Wg; Wu] stacked by rows."""
+    """silu(x @ Wg.T) * (x @ Wu.T) for w_gate_up with INTERLEAVED rows (row 2j = gate_j,
+    row 2j+1 = up_j), so that a gate/up pair lands in one thread of the epilogue."""
     M = x.shape[0]
     I = w_gate_up.shape[0] // 2
-    gu = linear(x, w_gate_up)
     out = torch.empty((M, I), dtype=x.dtype, device=x.device)
-    if M:
-        silu_mul(gu, out)
+    if M == 0:
+        return out
+    if _small_ok(x, w_gate_up):
+        gemm_bf16_small(x, w_gate_up, None, out, gated=True)
+        return out
+    gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
+    gemm_simt(x, w_gate_up, None, gu)
+    silu_mul(gu, out)
     return out

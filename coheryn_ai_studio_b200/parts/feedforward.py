@@ -27,8 +27,10 @@ class GatedMLP(FeedForward):
                 "down_proj.weight": TensorSpec((H, I))}
 
     def bind(self, tensors):
-        # One matrix product for gate and up: gate rows first, up rows after them.
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        # One matrix product for gate and up, rows interleaved (2j = gate_j, 2j+1 = up_j) so
+        # that the gated epilogue finds a pair in neighbouring output columns.
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:

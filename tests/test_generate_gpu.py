@@ -74,6 +74,8 @@ def test_preemption_and_prefix_reuse_change_nothing(folders, dtype):
     prompts = [shared + tiny.prompt(81 + i, 3 + 5 * i, 512) for i in range(4)]
     def run(**kw):
         eng = Engine.from_folder(folders["A"], dtype, context=128, max_num_seqs=4, page_size=16, **kw)
+        if kw.get("prefix_reuse"):
+            eng.generate(prompts[:1], max_tokens=2)      # leaves the shared prefix's pages behind
         res = eng.generate(prompts, max_tokens=24)
         eng.cache.check()
         return [r.token_ids for r in res], eng, res

@@ -85,6 +85,37 @@ def test_gemm_simt(shape, dtype):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("shape", [(1, 50, 40), (3, 129, 200), (8, 96, 1000), (16, 2048, 1536), (17, 300, 72),
+                                   (33, 1536, 8960), (64, 257, 96), (5, 151936, 64)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_gemm_bf16_small(shape, gated):
+    M, N, K = shape
+    if gated and N % 2:
+        N += 1
+    rng = np.random.default_rng(M + N)
+    x = t32(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
+    w = t32((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
+    acc = x.double().cpu() @ w.double().cpu().T
+    if gated:
+        g, u = acc[:, 0::2], acc[:, 1::2]
+        ref = g / (1 + torch.exp(-g)) * u
+        out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_small(x, w, None, out, gated=True)
+        assert (out.double().cpu() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max()) + 1e-3
+    else:
+        b = t32(rng.standard_normal(N).astype(np.float32))
+        ref = acc + b.double().cpu()
+        out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_small(x, w, b, out)
+        assert (out.double().cpu() - ref).abs().max() <= 2e-5 * max(1.0, ref.abs().max())
+        outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_small(x, w, b.to(torch.bfloat16), outb)
+        assert (outb.double().cpu() - ref).abs().max() <= 2 ** -7 * max(1.0, ref.abs().max())
+    with pytest.raises(Exception, match="multiples of 8"):
+        ops().gemm_bf16_small(x[:, :K - 4].contiguous(), w[:, :K - 4].contiguous(), None,
+                              torch.empty(M, N // 2 if gated else N, dtype=torch.float32, device=DEV), gated=gated)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_rows_do_not_depend_on_batch(dtype):
     """A row's product is the same alone and inside a larger batch (bitwise)."""
@@ -94,6 +125,10 @@ def test_rows_do_not_depend_on_batch(dtype):
     full = ops().linear(x, w)
     for r in (0, 13, 69):
         assert torch.equal(ops().linear(x[r:r + 1].contiguous(), w)[0], full[r])
+    if dtype == torch.bfloat16:     # the tensor-core kernel for few rows: 1, 9, 33 and 64 rows agree bitwise
+        big = ops().linear(x[:64].contiguous(), w)
+        for m in (1, 9, 33):
+            assert torch.equal(ops().linear(x[:m].contiguous(), w), big[:m])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -103,7 +138,7 @@ def test_silu_mul(dtype):
     out = torch.empty(9, 77, dtype=dtype, device=DEV)
     ops().silu_mul(gu, out)
     g = gu.float().cpu().numpy()
-    ref = plain.swiglu(g[:, :77], g[:, 77:])
+    ref = plain.swiglu(g[:, 0::2], g[:, 1::2])
     tol = 1e-6 if dtype == torch.float32 else 2 ** -8
     assert np.abs(out.float().cpu().numpy() - ref).max() <= tol * max(1, np.abs(ref).max())
 
@@ -162,11 +197,19 @@ def test_attention(nh, nkv, hd, page, dtype, window):
     q = torch.from_numpy(rng.standard_normal((T, nh * hd)).astype(np.float32)).to(dtype).to(DEV)
     out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
     scale = 1.0 / np.sqrt(hd)
-    ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
-                         nh, nkv, hd, page, window, scale)
     ref = attention_reference(q.float().cpu().numpy(), ks, vs, reqs, poss, nh, nkv, hd, window, scale)
-    tol = 2e-5 if dtype == torch.float32 else 2 ** -7
-    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
+    # bfloat16: the output is rounded to 8 bits (relative 2^-9, taken as 2^-8), and the
+    # tensor-core kernels also round the probabilities to bfloat16 before P V (absolute 2^-8
+    # for values of unit spread)
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -8 * np.abs(ref) + 2 ** -8
+    q_lens = [1, 30, 47, 1]
+    hints = dict(cu_q=t32(np.asarray([0, 1, 31, 78, 79], np.int32)), kv_lens=t32(np.asarray(lens, np.int32)),
+                 q_lens=q_lens, max_kv_len=max(lens))
+    for force_simple in (True, False):       # the plain kernel, then the one the engine picks
+        out.zero_()
+        ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
+                             nh, nkv, hd, page, window, scale, force_simple=force_simple, **hints)
+        assert np.all(np.abs(out.float().cpu().numpy() - ref) <= tol), force_simple
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -192,7 +235,8 @@ def test_attention_finds_a_far_key(dtype):
         qd = t32(q).to(dtype)
         out = torch.empty(1, nh * hd, dtype=dtype, device=DEV)
         ops().attention_rows(qd, out, kc, vc, bt, t32(np.zeros(1, np.int32)), t32(np.asarray([n - 1], np.int32)),
-                             nh, nkv, hd, page, window, scale)
+                             nh, nkv, hd, page, window, scale, cu_q=t32(np.asarray([0, 1], np.int32)),
+                             kv_lens=t32(np.asarray([n], np.int32)), q_lens=[1], max_kv_len=n)
         ref = attention_reference(qd.float().cpu().numpy(), ks, vs, [0], [n - 1], nh, nkv, hd, window, scale)
         got = out.float().cpu().numpy()
         assert np.abs(got - ref).max() <= (2e-5 if dtype == torch.float32 else 2 ** -6), (target, window)
