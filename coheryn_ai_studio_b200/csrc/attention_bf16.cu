@@ -65,23 +65,50 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
+// The pages that hold positions [key0, key0 + BN): each lane of a warp fetches up to two
+// block-table entries once per tile (entries lane and lane + 32 of the tile's page run);
+// page_of() then hands them out by shuffle, so that the copies below wait on no load.
+struct TilePages {
+  int e0, e1, first_block;
+};
+__device__ __forceinline__ TilePages tile_pages(const int* __restrict__ table, int page_size, int key0,
+                                                int kv_begin, int kv_end) {
+  const int lane = threadIdx.x & 31;
+  TilePages tp;
+  const int lo = max(key0, kv_begin), hi = min(key0 + BN, kv_end) - 1;   // positions really read
+  tp.first_block = lo / page_size;
+  const int last_block = hi >= lo ? hi / page_size : tp.first_block - 1;
+  tp.e0 = tp.first_block + lane <= last_block ? table[tp.first_block + lane] : 0;
+  tp.e1 = tp.first_block + lane + 32 <= last_block ? table[tp.first_block + lane + 32] : 0;
+  return tp;
+}
+__device__ __forceinline__ int page_of(const TilePages& tp, int block) {
+  const int i = block - tp.first_block;   // 0..63 for pages of at least one position
+  const int a = __shfl_sync(0xffffffffu, tp.e0, i & 31);
+  const int b = __shfl_sync(0xffffffffu, tp.e1, i & 31);
+  return i < 32 ? a : b;
+}
+
 // Copies key or value rows of positions [key0, key0 + BN) of one kv head from the pages
 // into a [BN][LDS] tile; positions outside [kv_begin, kv_end) are zero filled and their
 // pages are not touched (a window may already have given them back).  `nthreads` threads
-// with ids `tid` cooperate.
-__device__ __forceinline__ void load_tile(bf16* tile, const bf16* __restrict__ cache, const int* __restrict__ table,
+// with ids `tid` cooperate (whole warps; every lane runs every iteration).
+__device__ __forceinline__ void load_tile(bf16* tile, const bf16* __restrict__ cache, const TilePages& tp,
                                           int kvh, int nkv, int page_size, int key0, int kv_begin, int kv_end,
                                           int tid, int nthreads) {
-  for (int c = tid; c < BN * CHUNKS; c += nthreads) {
+  constexpr int TOTAL = BN * CHUNKS;
+  for (int c0 = 0; c0 < TOTAL; c0 += nthreads) {
+    const int c = c0 + tid;
     const int row = c / CHUNKS, piece = c % CHUNKS;
     const int pos = key0 + row;
-    const bool valid = pos >= kv_begin && pos < kv_end;
-    const bf16* src = cache;
-    if (valid) {
-      const int page = table[pos / page_size];
-      src = cache + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * HD + piece * 8;
+    const bool valid = c < TOTAL && pos >= kv_begin && pos < kv_end;
+    const int block = valid ? pos / page_size : tp.first_block;
+    const int page = page_of(tp, block);
+    if (c < TOTAL) {
+      const bf16* src = valid ? cache + (((size_t)page * nkv + kvh) * page_size + (pos - block * page_size)) * HD + piece * 8
+                              : cache;
+      cp_async16(tile + row * LDS + piece * 8, src, valid);
     }
-    cp_async16(tile + row * LDS + piece * 8, src, valid);
   }
 }
 
@@ -233,8 +260,11 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
   const int kv_end = pos_hi + 1;
 
   load_q_rows(Qs, q, q_stride, tok0, kvh, G, row_first, BM, rows, tid, 128);
-  load_tile(Ks, k_cache, table, kvh, nkv, page_size, tile_first * BN, key_first, kv_end, tid, 128);
-  load_tile(Vs, v_cache, table, kvh, nkv, page_size, tile_first * BN, key_first, kv_end, tid, 128);
+  {
+    const TilePages tp = tile_pages(table, page_size, tile_first * BN, key_first, kv_end);
+    load_tile(Ks, k_cache, tp, kvh, nkv, page_size, tile_first * BN, key_first, kv_end, tid, 128);
+    load_tile(Vs, v_cache, tp, kvh, nkv, page_size, tile_first * BN, key_first, kv_end, tid, 128);
+  }
   cp_async_commit();
 
   int lo[2], hi[2];
@@ -268,8 +298,9 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
   for (int tile = tile_first; tile <= tile_last; ++tile) {
     const int buf = (tile - tile_first) & 1;
     if (tile < tile_last) {
-      load_tile(Ks + (buf ^ 1) * BN * LDS, k_cache, table, kvh, nkv, page_size, (tile + 1) * BN, key_first, kv_end, tid, 128);
-      load_tile(Vs + (buf ^ 1) * BN * LDS, v_cache, table, kvh, nkv, page_size, (tile + 1) * BN, key_first, kv_end, tid, 128);
+      const TilePages tp = tile_pages(table, page_size, (tile + 1) * BN, key_first, kv_end);
+      load_tile(Ks + (buf ^ 1) * BN * LDS, k_cache, tp, kvh, nkv, page_size, (tile + 1) * BN, key_first, kv_end, tid, 128);
+      load_tile(Vs + (buf ^ 1) * BN * LDS, v_cache, tp, kvh, nkv, page_size, (tile + 1) * BN, key_first, kv_end, tid, 128);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -335,8 +366,9 @@ attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__
   const bool w_active = key0 <= pos_hi && key0 + BN > key_first;
   load_q_rows(Qs, q, q_stride, tok0, kvh, G, 0, 16, rows, tid, 128);
   if (w_active) {
-    load_tile(Kw, k_cache, table, kvh, nkv, page_size, key0, key_first, kv_end, lane, 32);
-    load_tile(Vw, v_cache, table, kvh, nkv, page_size, key0, key_first, kv_end, lane, 32);
+    const TilePages tp = tile_pages(table, page_size, key0, key_first, kv_end);
+    load_tile(Kw, k_cache, tp, kvh, nkv, page_size, key0, key_first, kv_end, lane, 32);
+    load_tile(Vw, v_cache, tp, kvh, nkv, page_size, key0, key_first, kv_end, lane, 32);
   }
   cp_async_commit();
   cp_async_wait<0>();
@@ -402,30 +434,45 @@ attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__
   }
 }
 
+// One CTA per (request, kv head, row): the splits' (max, sum) pairs are read once into
+// shared memory, then every thread merges its head-dim columns over the splits in
+// ascending order with independent loads.
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* __restrict__ scratch, int max_splits, bf16* __restrict__ out, long out_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, int nh, int nkv, int window) {
-  const int b = blockIdx.y, kvh = blockIdx.x;
+  __shared__ float factor[512];
+  __shared__ float s_den;
+  const int b = blockIdx.z, kvh = blockIdx.y, r = blockIdx.x;
   const int G = nh / nkv;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
   const int rows = q_len * G;
-  if (rows > 16 || rows <= 0) return;
+  if (rows > 16 || r >= rows) return;
   const int base_pos = kv_len - q_len;
   const int key_first = window > 0 ? max(0, base_pos - window + 1) : 0;
-  const int nsplits = (kv_len - 1) / SPLIT - key_first / SPLIT + 1;
-  const float* src = scratch + ((size_t)b * nkv + kvh) * max_splits * 16 * PART;
-  for (int e = threadIdx.x; e < rows * HD; e += blockDim.x) {
-    const int r = e / HD, c = e % HD;
+  const int nsplits = min((kv_len - 1) / SPLIT - key_first / SPLIT + 1, 512);
+  const float* src = scratch + (((size_t)b * nkv + kvh) * max_splits * 16 + r) * PART;
+  const size_t stride = (size_t)16 * PART;
+  for (int s = threadIdx.x; s < nsplits; s += blockDim.x) factor[s] = src[s * stride];
+  __syncthreads();
+  if (threadIdx.x == 0) {
     float M = -INFINITY;
-    for (int s = 0; s < nsplits; ++s) M = fmaxf(M, src[(s * 16 + r) * PART]);
-    float num = 0.f, den = 0.f;
+    for (int s = 0; s < nsplits; ++s) M = fmaxf(M, factor[s]);
+    float den = 0.f;
     for (int s = 0; s < nsplits; ++s) {
-      const float ms = src[(s * 16 + r) * PART];
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      den += f * src[(s * 16 + r) * PART + 1];
-      num += f * src[(s * 16 + r) * PART + 2 + c];
+      const float f = factor[s] == -INFINITY ? 0.f : exp2f(factor[s] - M);
+      factor[s] = f;
+      den += f * src[s * stride + 1];
     }
-    out[(size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * HD + c] = __float2bfloat16_rn(num / den);
+    s_den = den;
+  }
+  __syncthreads();
+  const float inv = 1.0f / s_den;
+  bf16* orow = out + (size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * HD;
+  for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+    float num = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < nsplits; ++s) num += factor[s] * src[s * stride + 2 + c];
+    orow[c] = __float2bfloat16_rn(num * inv);
   }
 }
 
@@ -491,7 +538,7 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
         (const bf16*)q, q_stride, scratch, max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables,
         max_blocks, cu_q, kv_lens, nh, nkv, page_size, window, scale_log2);
     CO_CHECK_LAUNCH("attn_split");
-    attn_combine_kernel<<<dim3(nkv, B), 128, 0, stream>>>(scratch, max_splits, (bf16*)out, out_stride, cu_q, kv_lens,
+    attn_combine_kernel<<<dim3(16, nkv, B), HD >= 128 ? 128 : 64, 0, stream>>>(scratch, max_splits, (bf16*)out, out_stride, cu_q, kv_lens,
                                                           nh, nkv, window);
     CO_CHECK_LAUNCH("attn_combine");
   }

@@ -68,24 +68,33 @@ gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
+  // Blocks are taken in batches of U: all loads of a batch are issued before its first
+  // MMA, so that a warp keeps U * NT * 512 bytes of the weight stream in flight.
+  constexpr int U = (MT * NT >= 8) ? 2 : ((MT * NT >= 4) ? 4 : 8);
   const int nblk = (K + 31) >> 5;
-#pragma unroll 4
-  for (int blk = warp; blk < nblk; blk += warps) {
-    const int k = (blk << 5) + (t << 3);
-    const bool valid = k < K;  // K is a multiple of 8: a 16-byte piece is whole or absent
-    uint4 wv[NT];
+  for (int blk0 = warp; blk0 < nblk; blk0 += warps * U) {
+    uint4 wv[U][NT], xa[U][MT], xb[U][MT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) wv[nt] = valid ? ld_stream(wrow[nt] + k) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < U; ++u) {
+      const int k = ((blk0 + u * warps) << 5) + (t << 3);
+      const bool valid = k < K;  // K is a multiple of 8: a 16-byte piece is whole or absent
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const uint4 xa = (valid && xok[mt][0]) ? __ldg((const uint4*)(xrow[mt][0] + k)) : make_uint4(0, 0, 0, 0);
-      const uint4 xb = (valid && xok[mt][1]) ? __ldg((const uint4*)(xrow[mt][1] + k)) : make_uint4(0, 0, 0, 0);
+      for (int nt = 0; nt < NT; ++nt) wv[u][nt] = valid ? ld_stream(wrow[nt] + k) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        mma_bf16(acc[mt][nt], xa.x, xb.x, xa.y, xb.y, wv[nt].x, wv[nt].y);
-        mma_bf16(acc[mt][nt], xa.z, xb.z, xa.w, xb.w, wv[nt].z, wv[nt].w);
+      for (int mt = 0; mt < MT; ++mt) {
+        xa[u][mt] = (valid && xok[mt][0]) ? __ldg((const uint4*)(xrow[mt][0] + k)) : make_uint4(0, 0, 0, 0);
+        xb[u][mt] = (valid && xok[mt][1]) ? __ldg((const uint4*)(xrow[mt][1] + k)) : make_uint4(0, 0, 0, 0);
       }
     }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16(acc[mt][nt], xa[u][mt].x, xb[u][mt].x, xa[u][mt].y, xb[u][mt].y, wv[u][nt].x, wv[u][nt].y);
+          mma_bf16(acc[mt][nt], xa[u][mt].z, xb[u][mt].z, xa[u][mt].w, xb[u][mt].w, wv[u][nt].z, wv[u][nt].w);
+        }
   }
 
   // Partial sums of every warp, laid out so that lanes write consecutive words.

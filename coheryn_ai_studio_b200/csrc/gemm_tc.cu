@@ -1,0 +1,322 @@
+// out[M, N] = x[M, K] . W[N, K]^T (+ bias | gated SiLU) for many rows (prompt portions), in
+// bfloat16 on the 5th-generation tensor cores: TMA (cp.async.bulk.tensor) stages 128-byte
+// swizzled tiles of both operands in shared memory, one thread issues tcgen05.mma with the
+// accumulator in tensor memory, and the epilogue reads it back with tcgen05.ld.
+//
+// One CTA computes a 128 x BN tile of the output (tokens on the 128 TMEM lanes, output
+// features on BN columns) over all of K in steps of 64:
+//   warp 0   producer: waits for a free stage, arms its mbarrier with the byte count and
+//            issues the two TMA loads (x tile 128 x 64, W tile BN x 64);
+//   warp 1   MMA issuer: waits for a full stage, issues four m128 nBN k16 MMAs, and lets
+//            tcgen05.commit release the stage (and, after the last step, signal the epilogue);
+//   warps 2-5 epilogue: each reads its 32 lanes of the accumulator 32 columns at a time,
+//            applies bias or the gate, converts and stores.
+// Rows and columns beyond M, N and the K tail are zero filled by TMA and masked on store.
+// Every wait is bounded: on expiry the kernel records an error code and winds down.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // tokens per tile = TMEM lanes
+constexpr int BK = 64;           // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr unsigned WAIT_LIMIT = 1u << 26;
+
+constexpr int EPI_PLAIN = 0, EPI_GATED_SILU = 1;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  const unsigned addr = smem_u32(bar);
+  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
+// 128-byte mode: start address >> 4, leading byte offset 1 (unused with a swizzle), stride
+// byte offset 1024 >> 4 between groups of eight rows, descriptor version 1, layout type 2.
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_u32(tile) & 0x3ffff) >> 4);
+  d |= (unsigned long long)1 << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N >> 3, M >> 4.
+__host__ __device__ constexpr unsigned umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN, int STAGES>
+struct Smem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype, int M, int N,
+               int K, long ldo, int epilogue, int* __restrict__ status) {
+  using S = Smem<BN, STAGES>;
+  extern __shared__ unsigned char smem_raw[];
+  // 128-byte swizzled tiles must start on a 1024-byte boundary.
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned long long* full = (unsigned long long*)(tiles + STAGES * S::STAGE_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* accum_full = empty + STAGES;
+  unsigned* tmem_slot = (unsigned*)(accum_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int k_tiles = (K + BK - 1) / BK;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;     // a power of two >= 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(accum_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {   // one warp allocates the accumulator columns (and frees them at the end)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const int s = kt % STAGES;
+        if (kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) { atomicExch(status, 11); break; }
+        unsigned char* a = tiles + s * S::STAGE_BYTES;
+        mbar_expect_tx(&full[s], S::STAGE_BYTES);
+        tma_load_2d(a, &map_x, kt * BK, m0, &full[s]);
+        tma_load_2d(a + S::A_BYTES, &map_w, kt * BK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr unsigned idesc = umma_idesc(BM, BN);
+      bool ok = true;
+      for (int kt = 0; kt < k_tiles && ok; ++kt) {
+        const int s = kt % STAGES;
+        if (!mbar_wait(&full[s], (kt / STAGES) & 1)) { atomicExch(status, 12); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned char* a = tiles + s * S::STAGE_BYTES;
+        const unsigned long long da = umma_desc(a), db = umma_desc(a + S::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)   // 32 bytes (>> 4 = 2) further along the swizzled row per step
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+        umma_commit(&empty[s]);                 // arrives when these MMAs have read the stage
+      }
+      umma_commit(accum_full);                  // arrives when every MMA issued so far is complete
+    }
+  } else {
+    // Epilogue warps 2..5: TMEM lane quarter = warp % 4.
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    const bool waited = mbar_wait(accum_full, 0);
+    if (!waited && lane == 0) atomicExch(status, 13);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (waited) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        unsigned r[32];
+        tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+        if (row >= M) continue;
+        if (epilogue == EPI_GATED_SILU) {
+          // columns (2j, 2j+1) = (gate_j, up_j): 16 outputs per 32 columns
+          const int oc = (n0 + c0) >> 1;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
+            v[j] = (g / (1.0f + __expf(-g))) * u;
+          }
+          const int n_out = N >> 1;
+          if (out_dtype == CO_BF16) {
+            __nv_bfloat16* p = (__nv_bfloat16*)out + (size_t)row * ldo + oc;
+            if (oc + 16 <= n_out && (((uintptr_t)p) & 15) == 0) {
+              uint4 q[2];
+              __nv_bfloat162* h = (__nv_bfloat162*)q;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              ((uint4*)p)[0] = q[0]; ((uint4*)p)[1] = q[1];
+            } else {
+              for (int j = 0; j < 16 && oc + j < n_out; ++j) p[j] = __float2bfloat16_rn(v[j]);
+            }
+          } else {
+            float* p = (float*)out + (size_t)row * ldo + oc;
+            for (int j = 0; j < 16 && oc + j < n_out; ++j) p[j] = v[j];
+          }
+          continue;
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (n0 + c0 + j < N) v[j] += co_load_any(bias, bias_dtype, n0 + c0 + j);
+        }
+        const int nc = n0 + c0;
+        if (out_dtype == CO_BF16) {
+          __nv_bfloat16* p = (__nv_bfloat16*)out + (size_t)row * ldo + nc;
+          if (nc + 32 <= N && (((uintptr_t)p) & 15) == 0) {
+            uint4 q[4];
+            __nv_bfloat162* h = (__nv_bfloat162*)q;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ((uint4*)p)[j] = q[j];
+          } else {
+            for (int j = 0; j < 32 && nc + j < N; ++j) p[j] = __float2bfloat16_rn(v[j]);
+          }
+        } else {
+          float* p = (float*)out + (size_t)row * ldo + nc;
+          if (nc + 32 <= N && (((uintptr_t)p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ((float4*)p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            for (int j = 0; j < 32 && nc + j < N; ++j) p[j] = v[j];
+          }
+        }
+      }
+    }
+  }
+
+  // Wind down: everybody meets, then the allocating warp frees the accumulator columns.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 matrix with row stride ld (elements) as a 2-D tensor map whose box is
+// box_rows x 64 elements, 128-byte swizzled, zero filled out of bounds.
+bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
+  EncodeTiled fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, int bias_dtype, void* out,
+              int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status, cudaStream_t stream) {
+  auto kernel = gemm_tc_kernel<BN, STAGES>;
+  constexpr int smem = Smem<BN, STAGES>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) CO_FAIL("gemm_tc: %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  kernel<<<grid, 192, smem, stream>>>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status);
+  CO_CHECK_LAUNCH("gemm_tc");
+  return 0;
+}
+}  // namespace
+
+// x: [M, K] bfloat16 with row stride ldx; w: [N, K] bfloat16 contiguous; K and ldx multiples
+// of 8, bases 16-byte aligned.  epilogue 0: out[M, N] (+ bias); 1: gated SiLU over
+// interleaved rows of w, out[M, N/2].  status: device word that receives 11/12/13 if a
+// bounded wait of the producer / the MMA issuer / the epilogue ran out.
+CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
+                                   int out_dtype, int M, int N, int K, long ldx, long ldo, int epilogue,
+                                   int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc: K = %d and the row stride %ld must be multiples of 8", K, ldx);
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc: operands must be 16-byte aligned");
+  if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc: gated epilogue needs an even number of rows");
+  if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
+  const int bn = N >= 192 ? 256 : (N >= 96 ? 128 : (N >= 48 ? 64 : 32));
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, K, bn))
+    CO_FAIL("gemm_bf16_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%ld)", M, N, K, ldx);
+#define GO(BN_, ST_) return launch_tc<BN_, ST_>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, stream)
+  if (bn == 256) GO(256, 4);
+  if (bn == 128) GO(128, 6);
+  if (bn == 64) GO(64, 8);
+  GO(32, 8);
+#undef GO
+}

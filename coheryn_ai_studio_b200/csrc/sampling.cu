@@ -57,6 +57,71 @@ argmax_kernel(const float* __restrict__ logits, long stride, int V, int* __restr
   }
 }
 
+// Two-stage variant for wide rows: stage 1 lets many CTAs scan pieces of a row, stage 2
+// (argmax_kernel over the partial values with their indices) picks among the pieces.
+constexpr int ARGMAX_PIECE = 4096;
+
+__global__ void __launch_bounds__(256)
+argmax_pieces_kernel(const float* __restrict__ logits, long stride, int V, float* __restrict__ part_val,
+                     int* __restrict__ part_idx, int pieces, int* __restrict__ status) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int r = blockIdx.y, piece = blockIdx.x;
+  const float* row = logits + (size_t)r * stride;
+  const int lo = piece * ARGMAX_PIECE, hi = min(V, lo + ARGMAX_PIECE);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  bool bad = false;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = row[i];
+    if (!isfinite(v)) bad = true;
+    if (better(v, i, bv, bi)) { bv = v; bi = i; }
+  }
+  if (bad) atomicExch(status, 2);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
+    part_val[(size_t)r * pieces + piece] = bv;
+    part_idx[(size_t)r * pieces + piece] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(64)
+argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int pieces,
+                    int* __restrict__ out) {
+  const int r = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+    const float v = part_val[(size_t)r * pieces + i];
+    const int idx = part_idx[(size_t)r * pieces + i];
+    if (better(v, idx, bv, bi)) { bv = v; bi = idx; }
+  }
+  __shared__ float sv[2];
+  __shared__ int si[2];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (better(sv[1], si[1], bv, bi)) { bv = sv[1]; bi = si[1]; }
+    out[r] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
 // Order-preserving map: larger float -> SMALLER key, so ascending keys walk the
 // candidates from the largest logit down.
 __device__ __forceinline__ unsigned desc_key(float v) {
@@ -294,10 +359,27 @@ CO_EXPORT int coheryn_apply_penalties(float* logits, long stride, int n, const i
   return 0;
 }
 
+// Number of 8-byte scratch slots coheryn_argmax wants for R rows of V logits (0: none).
+CO_EXPORT long coheryn_argmax_scratch_slots(int R, int V) {
+  const int pieces = (V + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
+  return pieces >= 4 ? (long)R * pieces : 0;
+}
+
+// scratch: 8 bytes per slot (see above), or null for the single-kernel path.
 CO_EXPORT int coheryn_argmax(const float* logits, long stride, int R, int V, int* out, int* status,
-                             cudaStream_t stream) {
+                             void* scratch, long scratch_slots, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0) CO_FAIL("argmax: empty vocabulary");
+  const int pieces = (V + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
+  if (pieces >= 4 && scratch && scratch_slots >= (long)R * pieces) {
+    float* pv = (float*)scratch;
+    int* pi = (int*)scratch + (size_t)R * pieces;
+    argmax_pieces_kernel<<<dim3(pieces, R), 256, 0, stream>>>(logits, stride, V, pv, pi, pieces, status);
+    CO_CHECK_LAUNCH("argmax_pieces");
+    argmax_final_kernel<<<R, 64, 0, stream>>>(pv, pi, pieces, out);
+    CO_CHECK_LAUNCH("argmax_final");
+    return 0;
+  }
   argmax_kernel<<<R, 1024, 0, stream>>>(logits, stride, V, out, status);
   CO_CHECK_LAUNCH("argmax");
   return 0;

@@ -38,6 +38,7 @@ def core():
         lib = build.core_library()
         lib.coheryn_last_error.restype = ctypes.c_char_p
         lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        lib.coheryn_argmax_scratch_slots.restype = ctypes.c_long
         _core = lib
     return _core
 
@@ -208,8 +209,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> Non
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     _i32(out, "out")
     lib = core()
+    slots = int(lib.coheryn_argmax_scratch_slots(c_int(R), c_int(V)))
+    scratch = torch.empty(2 * slots, dtype=torch.int32, device=logits.device) if slots else None
     _check(lib, lib.coheryn_argmax(_ptr(logits), c_long(logits.stride(0)), c_int(R), c_int(V),
-                                   _ptr(out), _ptr(status), _stream()))
+                                   _ptr(out), _ptr(status), _ptr(scratch), c_long(slots), _stream()))
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
@@ -254,6 +257,44 @@ def gemm_bf16_small(x, w, bias, out, gated: bool = False) -> None:
         c_int(1 if gated else 0), _stream()))
 
 
+_tc_status = {}
+
+
+def tc_status(device) -> torch.Tensor:
+    """Device word that the tensor-core GEMM sets when one of its bounded waits runs out."""
+    key = str(device)
+    if key not in _tc_status:
+        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[key]
+
+
+def check_tc_status(device) -> None:
+    code = int(tc_status(device).item())
+    if code:
+        tc_status(device).zero_()
+        raise KernelError(f"gemm_bf16_tc gave up waiting (code {code}: 11 producer, 12 MMA issuer, 13 epilogue)")
+
+
+def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
+    """TMA + tcgen05 product for many rows (prompt portions); see csrc/gemm_tc.cu."""
+    _dev(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == K
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N // 2 if gated else N)
+    lib = core()
+    _check(lib, lib.coheryn_gemm_bf16_tc(
+        _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
+        c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)),
+        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _stream()))
+
+
+def _tc_ok(x, w) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 64
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
 def _small_ok(x, w) -> bool:
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= 64
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
@@ -272,6 +313,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return out
     if _small_ok(x, w):
         gemm_bf16_small(x, w, bias, out)
+    elif _tc_ok(x, w):
+        gemm_bf16_tc(x, w, bias, out)
     else:
         gemm_simt(x, w, bias, out)
     return out
@@ -346,6 +389,9 @@ def gated_silu_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         return out
     if _small_ok(x, w_gate_up):
         gemm_bf16_small(x, w_gate_up, None, out, gated=True)
+        return out
+    if _tc_ok(x, w_gate_up):
+        gemm_bf16_tc(x, w_gate_up, None, out, gated=True)
         return out
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     gemm_simt(x, w_gate_up, None, gu)

@@ -116,6 +116,41 @@ def test_gemm_bf16_small(shape, gated):
                               torch.empty(M, N // 2 if gated else N, dtype=torch.float32, device=DEV), gated=gated)
 
 
+@pytest.mark.parametrize("shape", [(128, 256, 64), (65, 32, 8), (200, 300, 136), (300, 1000, 96), (257, 96, 1000),
+                                   (2048, 2048, 1536), (513, 1536, 8960), (130, 151936, 64), (1000, 48, 72)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_gemm_bf16_tc(shape, gated):
+    """TMA + tcgen05 kernel against float64, with tails in M, N and K."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    x = t32(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
+    w = t32((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
+    acc = x.double().cpu() @ w.double().cpu().T
+    if gated:
+        g, u = acc[:, 0::2], acc[:, 1::2]
+        ref = g / (1 + torch.exp(-g)) * u
+        out = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_tc(x, w, None, out, gated=True)
+        ops().check_tc_status(DEV)
+        assert (out.double().cpu() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max()) + 1e-3
+    else:
+        b = t32(rng.standard_normal(N).astype(np.float32))
+        ref = acc + b.double().cpu()
+        out = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc(x, w, b, out)
+        ops().check_tc_status(DEV)
+        assert (out.double().cpu() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+        outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_tc(x, w, None, outb)
+        assert (outb.double().cpu() - acc).abs().max() <= 2 ** -7 * max(1.0, acc.abs().max())
+        # a strided input (a column slice of a wider buffer, 16-byte aligned)
+        wide = torch.zeros(M, K + 16, dtype=torch.bfloat16, device=DEV)
+        wide[:, 8:8 + K] = x
+        out2 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc(wide[:, 8:8 + K], w, b, out2)
+        assert torch.equal(out, out2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_rows_do_not_depend_on_batch(dtype):
     """A row's product is the same alone and inside a larger batch (bitwise)."""
@@ -312,6 +347,17 @@ def test_argmax_first_maximum():
     lg[3, 5] = float("nan")
     ops().argmax(lg, out, status)
     assert status.item() == 2
+
+
+def test_argmax_wide_rows_use_many_blocks():
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((9, 151936)).astype(np.float32)
+    x[0, 4095] = x[0, 4096] = x[0, 151935] = 99.0        # ties across pieces: lowest id wins
+    x[1, 151935] = 77.0
+    out = torch.empty(9, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().argmax(t32(x), out, status)
+    assert out.tolist() == [4095, 151935] + [int(r.argmax()) for r in x[2:]] and status.item() == 0
 
 
 @pytest.mark.parametrize("V", [5, 1000, 151936])
