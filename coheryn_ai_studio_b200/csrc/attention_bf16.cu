@@ -7,15 +7,15 @@
 // that is read.  Two kernels:
 //
 //  * attn_tiles:  one CTA per (request, kv head, tile of 64 rows); four warps of 16 rows
-//    share key/value tiles of 64 positions that are copied from the pages into shared
+//    share key/value tiles of 32 positions that are copied from the pages into shared
 //    memory with cp.async (double buffered).  Used for prompt portions.
 //  * attn_split:  for requests with at most 16 rows per kv head (decoding).  The key range
-//    is cut into splits of 256 positions at ABSOLUTE multiples of 256; one CTA per
-//    (request, kv head, split), each of its four warps taking one tile of 64 positions.
+//    is cut into splits of 128 positions at ABSOLUTE multiples of 128; one CTA per
+//    (request, kv head, split), each of its four warps taking tiles of 32 positions.
 //    The warps' (max, sum, accumulator) triples are merged in warp order and written to
 //    scratch; attn_combine merges the splits of a row in ascending order.
 //
-// Tiles start at absolute multiples of 64 and splits at absolute multiples of 256, so a
+// Tiles start at absolute multiples of 32 and splits at absolute multiples of 128, so a
 // row's result depends only on its own position and window, never on the batch.
 #include <cuda_bf16.h>
 
@@ -27,10 +27,8 @@
 
 namespace {
 constexpr int HD = CO_HEAD_DIM;
-constexpr int BN = 64;            // key positions per tile
-constexpr int BM = 64;            // query rows per CTA in attn_tiles
 constexpr int LDS = HD + 8;       // shared-memory row stride: 16 bytes of padding keep ldmatrix conflict-free
-constexpr int SPLIT = 256;        // key positions per split in attn_split
+constexpr int SPLIT_MIN = 128;    // the smaller of the two split sizes of attn_split
 constexpr int CHUNKS = HD / 8;    // 16-byte pieces per row
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
 
@@ -65,17 +63,18 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// The pages that hold positions [key0, key0 + BN): each lane of a warp fetches up to two
+// The pages that hold positions [key0, key0 + TB): each lane of a warp fetches up to two
 // block-table entries once per tile (entries lane and lane + 32 of the tile's page run);
 // page_of() then hands them out by shuffle, so that the copies below wait on no load.
 struct TilePages {
   int e0, e1, first_block;
 };
+template <int TB>
 __device__ __forceinline__ TilePages tile_pages(const int* __restrict__ table, int page_size, int key0,
                                                 int kv_begin, int kv_end) {
   const int lane = threadIdx.x & 31;
   TilePages tp;
-  const int lo = max(key0, kv_begin), hi = min(key0 + BN, kv_end) - 1;   // positions really read
+  const int lo = max(key0, kv_begin), hi = min(key0 + TB, kv_end) - 1;   // positions really read
   tp.first_block = lo / page_size;
   const int last_block = hi >= lo ? hi / page_size : tp.first_block - 1;
   tp.e0 = tp.first_block + lane <= last_block ? table[tp.first_block + lane] : 0;
@@ -89,26 +88,41 @@ __device__ __forceinline__ int page_of(const TilePages& tp, int block) {
   return i < 32 ? a : b;
 }
 
-// Copies key or value rows of positions [key0, key0 + BN) of one kv head from the pages
-// into a [BN][LDS] tile; positions outside [kv_begin, kv_end) are zero filled and their
-// pages are not touched (a window may already have given them back).  `nthreads` threads
-// with ids `tid` cooperate (whole warps; every lane runs every iteration).
+// Copies key or value rows of positions [key0, key0 + TB) of one kv head from the pages
+// into a [TB][LDS] tile; positions outside [kv_begin, kv_end) are zero filled and their
+// pages are not touched (a window may already have given them back).  NT threads with ids
+// `tid` cooperate (whole warps, NT = 32 or 128): a thread owns TB / NT rows or, with more
+// threads than rows, a share of one row; the row's address is worked out once.
+__host__ __device__ constexpr int largest_divisor_up_to(int n, int cap) {
+  int best = 1;
+  for (int d = 1; d <= cap; ++d)
+    if (n % d == 0) best = d;
+  return best;
+}
+
+template <int NT, int TB>
 __device__ __forceinline__ void load_tile(bf16* tile, const bf16* __restrict__ cache, const TilePages& tp,
                                           int kvh, int nkv, int page_size, int key0, int kv_begin, int kv_end,
-                                          int tid, int nthreads) {
-  constexpr int TOTAL = BN * CHUNKS;
-  for (int c0 = 0; c0 < TOTAL; c0 += nthreads) {
-    const int c = c0 + tid;
-    const int row = c / CHUNKS, piece = c % CHUNKS;
+                                          int tid) {
+  constexpr int SLOTS = NT >= TB ? NT / TB : 1;                  // threads that sit on one row
+  constexpr int TPR = largest_divisor_up_to(CHUNKS, SLOTS);      // of which this many copy
+  constexpr int RPT = NT >= TB ? 1 : TB / NT;                    // rows per thread
+  constexpr int PIECES = CHUNKS / TPR;                           // 16-byte pieces per thread and row
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int row = NT >= TB ? tid / SLOTS : i * NT + tid;
+    const int sub = NT >= TB ? tid % SLOTS : 0;
+    const int piece0 = sub * PIECES;
     const int pos = key0 + row;
-    const bool valid = c < TOTAL && pos >= kv_begin && pos < kv_end;
+    const bool valid = pos >= kv_begin && pos < kv_end;
     const int block = valid ? pos / page_size : tp.first_block;
-    const int page = page_of(tp, block);
-    if (c < TOTAL) {
-      const bf16* src = valid ? cache + (((size_t)page * nkv + kvh) * page_size + (pos - block * page_size)) * HD + piece * 8
-                              : cache;
-      cp_async16(tile + row * LDS + piece * 8, src, valid);
-    }
+    const int page = page_of(tp, block);                         // a shuffle: every lane takes part
+    if (sub >= TPR) continue;
+    const bf16* src = valid ? cache + (((size_t)page * nkv + kvh) * page_size + (pos - block * page_size)) * HD + piece0 * 8
+                            : cache;
+    bf16* dst = tile + row * LDS + piece0 * 8;
+#pragma unroll
+    for (int c = 0; c < PIECES; ++c) cp_async16(dst + c * 8, valid ? src + c * 8 : src, valid);
   }
 }
 
@@ -117,103 +131,132 @@ struct RowState {
   float l[2];   // this thread's share of the running sum
 };
 
-// One warp, 16 query rows against one tile of BN key positions in shared memory:
-// S = Q K^T, masking, online softmax, O += P V.
-//   qf: the warp's Q fragments; Ks/Vs: [BN][LDS] tiles; key0: position of the tile's row 0;
-//   lo[h], hi[h]: first and last visible key position of the thread's rows g (h=0), g+8 (h=1).
-__device__ __forceinline__ void attend_tile(const unsigned (&qf)[HD / 16][4], const bf16* Ks, const bf16* Vs,
-                                            float (&o)[HD / 8][4], RowState& st, int key0, const int (&lo)[2],
-                                            const int (&hi)[2], float scale_log2) {
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // ex2(-inf) = +0
+  return y;
+}
+
+// One warp, MT tiles of 16 query rows against one tile of TB key positions in shared memory:
+// S = Q K^T, masking, online softmax, O += P V.  Key and value fragments are fetched once and
+// used for all MT row tiles.
+//   Q fragments: registers (qf) when MT == 1 and QSMEM is false, else read from the warp's
+//   rows in shared memory (Qs, [16 * MT][LDS]).
+//   Ks/Vs: [TB][LDS] tiles; key0: position of the tile's row 0; lo/hi[mi][h]: first and last
+//   visible key of the thread's rows g (h = 0) and g + 8 (h = 1) of row tile mi.  MASK false
+//   promises that every key of the tile is visible to every row.
+template <int MT, int TB, bool QSMEM, bool MASK>
+__device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16* Qs, const bf16* Ks, const bf16* Vs,
+                                            float (&o)[MT][HD / 8][4], RowState (&st)[MT], int key0,
+                                            const int (&lo)[MT][2], const int (&hi)[MT][2], float scale_log2) {
   const int lane = threadIdx.x & 31;
   const int t = lane & 3;
-  float s[BN / 8][4];
+  const int id = lane >> 3, r = lane & 7;
+  float s[MT][TB / 8][4];
 #pragma unroll
-  for (int j = 0; j < BN / 8; ++j)
+  for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+    for (int j = 0; j < TB / 8; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[mi][j][i] = 0.f;
 
   // S = Q K^T.  ldmatrix.x4 on K rows yields the B fragments of two neighbouring key tiles.
-  {
-    const int id = lane >> 3, r = lane & 7;
 #pragma unroll
-    for (int kd = 0; kd < HD / 16; ++kd) {
+  for (int kd = 0; kd < HD / 16; ++kd) {
+    unsigned a[MT][4];
 #pragma unroll
-      for (int jp = 0; jp < BN / 16; ++jp) {
-        unsigned b[4];
-        ldmatrix_x4(b, Ks + (jp * 16 + (id >> 1) * 8 + r) * LDS + kd * 16 + (id & 1) * 8);
-        mma_bf16(s[2 * jp], qf[kd], b[0], b[1]);
-        mma_bf16(s[2 * jp + 1], qf[kd], b[2], b[3]);
+    for (int mi = 0; mi < MT; ++mi) {
+      if (QSMEM) ldmatrix_x4(a[mi], Qs + (mi * 16 + (id & 1) * 8 + r) * LDS + kd * 16 + (id >> 1) * 8);
+      else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[mi][i] = qf[kd][i];
+      }
+    }
+#pragma unroll
+    for (int jp = 0; jp < TB / 16; ++jp) {
+      unsigned b[4];
+      ldmatrix_x4(b, Ks + (jp * 16 + (id >> 1) * 8 + r) * LDS + kd * 16 + (id & 1) * 8);
+#pragma unroll
+      for (int mi = 0; mi < MT; ++mi) {
+        mma_bf16(s[mi][2 * jp], a[mi], b[0], b[1]);
+        mma_bf16(s[mi][2 * jp + 1], a[mi], b[2], b[3]);
       }
     }
   }
 
-  // Mask and online softmax.  Thread holds, for rows g (i = 0,1) and g+8 (i = 2,3), the
-  // key columns key0 + 8 j + 2 t + (i & 1).
+  // Online softmax.  A thread holds, for rows g (i = 0,1) and g+8 (i = 2,3), the key
+  // columns key0 + 8 j + 2 t + (i & 1).  The maximum is tracked in the log2 domain of the
+  // scaled scores; p = 2^(s * scale_log2 - m) is one fused multiply-add and one ex2.
+  bool rescale = false;
+  float corr[MT][2];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    float mx = -INFINITY;
+  for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
-    for (int j = 0; j < BN / 8; ++j)
+    for (int h = 0; h < 2; ++h) {
+      float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int key = key0 + j * 8 + 2 * t + i;
-        float v = s[j][2 * h + i] * scale_log2;
-        if (key < lo[h] || key > hi[h]) v = -INFINITY;
-        s[j][2 * h + i] = v;
-        mx = fmaxf(mx, v);
-      }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(st.m[h], mx);
-    // Everything masked so far: keep the state untouched and let p be zero.
-    const float m_use = m_new == -INFINITY ? 0.f : m_new;
-    const float corr = st.m[h] == -INFINITY ? 0.f : exp2f(st.m[h] - m_use);
-    float part = 0.f;
+      for (int j = 0; j < TB / 8; ++j)
 #pragma unroll
-    for (int j = 0; j < BN / 8; ++j)
+        for (int i = 0; i < 2; ++i) {
+          if (MASK) {
+            const int key = key0 + j * 8 + 2 * t + i;
+            if (key < lo[mi][h] || key > hi[mi][h]) s[mi][j][2 * h + i] = -INFINITY;
+          }
+          mx = fmaxf(mx, s[mi][j][2 * h + i]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(st[mi].m[h], mx * scale_log2);   // scale > 0 keeps the order
+      // Everything masked so far: keep the state and let every p be zero.
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float c = ex2_approx(st[mi].m[h] - m_use);
+      float part = 0.f;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const float p = exp2f(s[j][2 * h + i] - m_use);  // exp2(-inf) = 0 for masked keys
-        s[j][2 * h + i] = p;
-        part += p;
-      }
-    st.l[h] = st.l[h] * corr + part;
-    st.m[h] = m_new;
+      for (int j = 0; j < TB / 8; ++j)
 #pragma unroll
-    for (int dt = 0; dt < HD / 8; ++dt) {
-      o[dt][2 * h] *= corr;
-      o[dt][2 * h + 1] *= corr;
+        for (int i = 0; i < 2; ++i) {
+          const float p = ex2_approx(fmaf(s[mi][j][2 * h + i], scale_log2, -m_use));
+          s[mi][j][2 * h + i] = p;
+          part += p;
+        }
+      st[mi].l[h] = st[mi].l[h] * c + part;
+      st[mi].m[h] = m_new;
+      corr[mi][h] = c;
+      rescale |= c != 1.f;
     }
+  if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; ++dt) {
+        o[mi][dt][0] *= corr[mi][0]; o[mi][dt][1] *= corr[mi][0];
+        o[mi][dt][2] *= corr[mi][1]; o[mi][dt][3] *= corr[mi][1];
+      }
   }
 
   // O += P V.  The S accumulators of two neighbouring key tiles are the A fragment of one
   // 16-position step; ldmatrix.x4.trans on V rows yields B fragments of two head-dim tiles.
-  {
-    const int id = lane >> 3, r = lane & 7;
 #pragma unroll
-    for (int kt = 0; kt < BN / 16; ++kt) {
-      unsigned a[4];
-      a[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
-      a[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
-      a[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
-      a[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+  for (int kt = 0; kt < TB / 16; ++kt) {
+    unsigned a[MT][4];
 #pragma unroll
-      for (int dp = 0; dp < HD / 16; ++dp) {
-        unsigned b[4];
-        ldmatrix_x4_trans(b, Vs + (kt * 16 + (id & 1) * 8 + r) * LDS + dp * 16 + (id >> 1) * 8);
-        mma_bf16(o[2 * dp], a, b[0], b[1]);
-        mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+    for (int mi = 0; mi < MT; ++mi) {
+      a[mi][0] = pack_bf16(s[mi][2 * kt][0], s[mi][2 * kt][1]);
+      a[mi][1] = pack_bf16(s[mi][2 * kt][2], s[mi][2 * kt][3]);
+      a[mi][2] = pack_bf16(s[mi][2 * kt + 1][0], s[mi][2 * kt + 1][1]);
+      a[mi][3] = pack_bf16(s[mi][2 * kt + 1][2], s[mi][2 * kt + 1][3]);
+    }
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      unsigned b[4];
+      ldmatrix_x4_trans(b, Vs + (kt * 16 + (id & 1) * 8 + r) * LDS + dp * 16 + (id >> 1) * 8);
+#pragma unroll
+      for (int mi = 0; mi < MT; ++mi) {
+        mma_bf16(o[mi][2 * dp], a[mi], b[0], b[1]);
+        mma_bf16(o[mi][2 * dp + 1], a[mi], b[2], b[3]);
       }
     }
   }
-}
-
-// Loads the warp's 16 query rows (already in shared memory, [16][LDS]) as A fragments.
-__device__ __forceinline__ void load_q_frags(unsigned (&qf)[HD / 16][4], const bf16* Qs) {
-  const int lane = threadIdx.x & 31;
-  const int id = lane >> 3, r = lane & 7;
-#pragma unroll
-  for (int kd = 0; kd < HD / 16; ++kd) ldmatrix_x4(qf[kd], Qs + ((id & 1) * 8 + r) * LDS + kd * 16 + (id >> 1) * 8);
 }
 
 // Copies query rows [row0, row0 + nrows) of (request, kv head) into shared memory; rows at
@@ -231,18 +274,29 @@ __device__ __forceinline__ void load_q_rows(bf16* Qs, const bf16* __restrict__ q
 }
 
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
+// attn_tiles: 64 query rows per CTA (four warps of 16), key tiles of 32 positions, two
+// stages: about 52 KB of shared memory and at most 128 registers per thread at head size
+// 128, so that four CTAs (16 warps) share an SM and cover each other's latencies.
+constexpr int TMT = 1;
+constexpr int TBN = 32;
+constexpr int BM = 64 * TMT;      // query rows per CTA: four warps of 16 * TMT rows
+
+__global__ void __launch_bounds__(128, HD <= 128 ? 4 : 1)
 attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                   const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window,
                   float scale_log2, int skip_small) {
+  // The query rows stay in shared memory; two stages of (K tile, V tile) follow them.
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][LDS]
-  bf16* Ks = Qs + BM * LDS;                                    // [2][BN][LDS]
-  bf16* Vs = Ks + 2 * BN * LDS;                                // [2][BN][LDS]
+  bf16* stages = Qs + BM * LDS;                                 // [2][2][TBN][LDS]
+  constexpr int STAGE = 2 * TBN * LDS;
 
-  const int b = blockIdx.z, kvh = blockIdx.y, rt = blockIdx.x;
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  // Late row tiles see the most keys: they are started first.
+  const int b = blockIdx.z, kvh = blockIdx.y, rt = gridDim.x - 1 - blockIdx.x;
   const int G = nh / nkv;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
   const int rows = q_len * G;
@@ -256,78 +310,97 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
   const int row_first = rt * BM, row_last = min(rows, row_first + BM) - 1;
   const int pos_lo = base_pos + row_first / G, pos_hi = base_pos + row_last / G;
   const int key_first = window > 0 ? max(0, pos_lo - window + 1) : 0;
-  const int tile_first = key_first / BN, tile_last = pos_hi / BN;
+  const int tile_first = key_first / TBN, tile_last = pos_hi / TBN;
   const int kv_end = pos_hi + 1;
 
+  // The page ids of a tile are fetched one iteration before its copies are issued, so that
+  // no copy waits on a block-table load.
+  auto issue = [&](int tile, const TilePages& tp) {
+    if (tile <= tile_last) {
+      bf16* st_k = stages + ((tile - tile_first) & 1) * STAGE;
+      load_tile<128, TBN>(st_k, k_cache, tp, kvh, nkv, page_size, tile * TBN, key_first, kv_end, tid);
+      load_tile<128, TBN>(st_k + TBN * LDS, v_cache, tp, kvh, nkv, page_size, tile * TBN, key_first, kv_end, tid);
+    }
+    cp_async_commit();
+  };
+  auto pages = [&](int tile) {
+    return tile <= tile_last ? tile_pages<TBN>(table, page_size, tile * TBN, key_first, kv_end) : TilePages{0, 0, 0};
+  };
   load_q_rows(Qs, q, q_stride, tok0, kvh, G, row_first, BM, rows, tid, 128);
-  {
-    const TilePages tp = tile_pages(table, page_size, tile_first * BN, key_first, kv_end);
-    load_tile(Ks, k_cache, tp, kvh, nkv, page_size, tile_first * BN, key_first, kv_end, tid, 128);
-    load_tile(Vs, v_cache, tp, kvh, nkv, page_size, tile_first * BN, key_first, kv_end, tid, 128);
-  }
-  cp_async_commit();
+  issue(tile_first, pages(tile_first));      // group 0: the query rows and the first tile
+  TilePages tp_next = pages(tile_first + 1);
 
-  int lo[2], hi[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = row_first + warp * 16 + h * 8 + g;
-    if (r < rows) {
-      hi[h] = base_pos + r / G;
-      lo[h] = window > 0 ? max(0, hi[h] - window + 1) : 0;
-    } else {
-      hi[h] = -1; lo[h] = 0;
-    }
-  }
-  // The warp's own key range (skip tiles in which none of its 16 rows sees a key).
-  const int w_row_first = row_first + warp * 16;
-  const int w_row_last = min(rows - 1, w_row_first + 15);
+  // Visible key range of the thread's rows, and of the warp's rows as a whole.
+  int lo[TMT][2], hi[TMT][2];
+  const int w_row_first = row_first + warp * 16 * TMT;
+  const int w_row_last = min(rows - 1, w_row_first + 16 * TMT - 1);
   const bool w_active = w_row_first < rows;
-  const int w_hi = w_active ? base_pos + w_row_last / G : -1;
-  const int w_lo = w_active ? (window > 0 ? max(0, base_pos + w_row_first / G - window + 1) : 0) : 0;
-
-  float o[HD / 8][4];
 #pragma unroll
-  for (int dt = 0; dt < HD / 8; ++dt)
+  for (int mi = 0; mi < TMT; ++mi)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[dt][i] = 0.f;
-  RowState st;
-  st.m[0] = st.m[1] = -INFINITY;
-  st.l[0] = st.l[1] = 0.f;
-  unsigned qf[HD / 16][4];
-
-  for (int tile = tile_first; tile <= tile_last; ++tile) {
-    const int buf = (tile - tile_first) & 1;
-    if (tile < tile_last) {
-      const TilePages tp = tile_pages(table, page_size, (tile + 1) * BN, key_first, kv_end);
-      load_tile(Ks + (buf ^ 1) * BN * LDS, k_cache, tp, kvh, nkv, page_size, (tile + 1) * BN, key_first, kv_end, tid, 128);
-      load_tile(Vs + (buf ^ 1) * BN * LDS, v_cache, tp, kvh, nkv, page_size, (tile + 1) * BN, key_first, kv_end, tid, 128);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    for (int h = 0; h < 2; ++h) {
+      const int r = w_row_first + mi * 16 + h * 8 + g;
+      if (r < rows) {
+        hi[mi][h] = base_pos + r / G;
+        lo[mi][h] = window > 0 ? max(0, hi[mi][h] - window + 1) : 0;
+      } else {
+        hi[mi][h] = -1; lo[mi][h] = 0;
+      }
     }
-    __syncthreads();
-    if (tile == tile_first) load_q_frags(qf, Qs + warp * 16 * LDS);
-    const int key0 = tile * BN;
-    if (w_active && key0 <= w_hi && key0 + BN > w_lo)
-      attend_tile(qf, Ks + buf * BN * LDS, Vs + buf * BN * LDS, o, st, key0, lo, hi, scale_log2);
-    __syncthreads();
-  }
+  const int w_hi_max = w_active ? base_pos + w_row_last / G : -1;           // last key any row sees
+  const int w_hi_min = w_active ? base_pos + w_row_first / G : -1;          // last key EVERY row sees
+  const int w_lo_min = w_active && window > 0 ? max(0, base_pos + w_row_first / G - window + 1) : 0;
+  const int w_lo_max = w_active && window > 0 ? max(0, base_pos + w_row_last / G - window + 1) : 0;
+  const bool w_full = w_row_first + 16 * TMT <= rows;                       // no padding rows
 
+  float o[TMT][HD / 8][4];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = row_first + warp * 16 + h * 8 + g;
-    float l = st.l[h];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (r >= rows) continue;
-    const float inv = 1.0f / l;
-    bf16* orow = out + (size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * HD;
+  for (int mi = 0; mi < TMT; ++mi)
 #pragma unroll
     for (int dt = 0; dt < HD / 8; ++dt)
-      *reinterpret_cast<__nv_bfloat162*>(orow + dt * 8 + 2 * t) =
-          __floats2bfloat162_rn(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[mi][dt][i] = 0.f;
+  RowState st[TMT];
+#pragma unroll
+  for (int mi = 0; mi < TMT; ++mi) {
+    st[mi].m[0] = st[mi].m[1] = -INFINITY;
+    st[mi].l[0] = st[mi].l[1] = 0.f;
   }
+  const bf16* Qw = Qs + warp * 16 * TMT * LDS;
+
+  for (int tile = tile_first; tile <= tile_last; ++tile) {
+    issue(tile + 1, tp_next);     // into the stage that tile - 1 used (all warps are past it)
+    tp_next = pages(tile + 2);
+    cp_async_wait<1>();           // this tile's group has landed; the next one may be in flight
+    __syncthreads();
+    const bf16* st_k = stages + ((tile - tile_first) & 1) * STAGE;
+    const int key0 = tile * TBN;
+    if (w_active && key0 <= w_hi_max && key0 + TBN > w_lo_min) {
+      const bool all_visible = w_full && key0 + TBN - 1 <= w_hi_min && key0 >= w_lo_max;
+      if (all_visible)
+        attend_tile<TMT, TBN, true, false>(nullptr, Qw, st_k, st_k + TBN * LDS, o, st, key0, lo, hi, scale_log2);
+      else
+        attend_tile<TMT, TBN, true, true>(nullptr, Qw, st_k, st_k + TBN * LDS, o, st, key0, lo, hi, scale_log2);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int mi = 0; mi < TMT; ++mi)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = w_row_first + mi * 16 + h * 8 + g;
+      float l = st[mi].l[h];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (r >= rows) continue;
+      const float inv = 1.0f / l;
+      bf16* orow = out + (size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * HD;
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; ++dt)
+        *reinterpret_cast<__nv_bfloat162*>(orow + dt * 8 + 2 * t) =
+            __floats2bfloat162_rn(o[mi][dt][2 * h] * inv, o[mi][dt][2 * h + 1] * inv);
+    }
 }
 
 // ------------------------------------------------------------------------------------
@@ -335,16 +408,29 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
 // [0] = max (log2 domain), [1] = sum, [2..] = unnormalised accumulator.
 constexpr int PART = HD + 2;
 
+// Key positions per warp step in attn_split: a warp owns one buffer of SBN keys and SBN
+// values and walks its share of the split (positions w*SBN, (w+4)*SBN, ... of the split)
+// through it.  About 74 KB per CTA at head size 128: three CTAs, twelve warps per SM,
+// each with its own copies in flight.
+//
+// Two shapes are built: <64, 256> (one CTA per SM, eight tiles of 64 in flight: best when
+// the whole grid fits the GPU at once) and <32, 128> (three CTAs per SM: best when CTAs
+// queue up).  Which one runs depends only on the batch's size, and a row's result depends
+// on the shape (rounding), so a request may see either across steps.
+template <int SBN, int SPLIT>
 __global__ void __launch_bounds__(128)
 attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__ scratch, int max_splits,
                   const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window, float scale_log2) {
+  constexpr int SPLIT_TILES = SPLIT / (4 * SBN);   // tiles per warp
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][LDS]
-  bf16* KVs = Qs + 16 * LDS;                                   // [4 warps][2][BN][LDS]
+  bf16* KVs = Qs + 16 * LDS;                                   // [4 warps][2][SBN][LDS]
   float* merge = reinterpret_cast<float*>(KVs);                // reused after the tiles: [4][16][PART]
 
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const int b = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
   const int G = nh / nkv;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
@@ -359,59 +445,69 @@ attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__
   const int* table = block_tables + (size_t)b * max_blocks;
   const int kv_end = pos_hi + 1;
 
-  // Each warp takes one tile of the split.
-  const int key0 = split * SPLIT + warp * BN;
-  bf16* Kw = KVs + (size_t)warp * 2 * BN * LDS;
-  bf16* Vw = Kw + BN * LDS;
-  const bool w_active = key0 <= pos_hi && key0 + BN > key_first;
+  bf16* Kw = KVs + (size_t)warp * 2 * SBN * LDS;
+  bf16* Vw = Kw + SBN * LDS;
+  auto tile_key0 = [&](int i) { return split * SPLIT + (i * 4 + warp) * SBN; };
+  // The warp's first tile that reaches into the visible range (a window hides earlier ones).
+  int i0 = 0;
+  while (i0 < SPLIT_TILES && tile_key0(i0) + SBN <= key_first) ++i0;
   load_q_rows(Qs, q, q_stride, tok0, kvh, G, 0, 16, rows, tid, 128);
-  if (w_active) {
-    const TilePages tp = tile_pages(table, page_size, key0, key_first, kv_end);
-    load_tile(Kw, k_cache, tp, kvh, nkv, page_size, key0, key_first, kv_end, lane, 32);
-    load_tile(Vw, v_cache, tp, kvh, nkv, page_size, key0, key_first, kv_end, lane, 32);
+  if (i0 < SPLIT_TILES && tile_key0(i0) <= pos_hi) {
+    const TilePages tp = tile_pages<SBN>(table, page_size, tile_key0(i0), key_first, kv_end);
+    load_tile<32, SBN>(Kw, k_cache, tp, kvh, nkv, page_size, tile_key0(i0), key_first, kv_end, lane);
+    load_tile<32, SBN>(Vw, v_cache, tp, kvh, nkv, page_size, tile_key0(i0), key_first, kv_end, lane);
   }
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();
 
-  int lo[2], hi[2];
+  int lo[1][2], hi[1][2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = h * 8 + g;
     if (r < rows) {
-      hi[h] = base_pos + r / G;
-      lo[h] = window > 0 ? max(0, hi[h] - window + 1) : 0;
+      hi[0][h] = base_pos + r / G;
+      lo[0][h] = window > 0 ? max(0, hi[0][h] - window + 1) : 0;
     } else {
-      hi[h] = -1; lo[h] = 0;
+      hi[0][h] = -1; lo[0][h] = 0;
     }
   }
-  float o[HD / 8][4];
+  float o[1][HD / 8][4];
 #pragma unroll
   for (int dt = 0; dt < HD / 8; ++dt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[dt][i] = 0.f;
-  RowState st;
-  st.m[0] = st.m[1] = -INFINITY;
-  st.l[0] = st.l[1] = 0.f;
-  if (w_active) {
-    unsigned qf[HD / 16][4];
-    load_q_frags(qf, Qs);
-    attend_tile(qf, Kw, Vw, o, st, key0, lo, hi, scale_log2);
+    for (int i = 0; i < 4; ++i) o[0][dt][i] = 0.f;
+  RowState st[1];
+  st[0].m[0] = st[0].m[1] = -INFINITY;
+  st[0].l[0] = st[0].l[1] = 0.f;
+#pragma unroll 1
+  for (int i = i0; i < SPLIT_TILES; ++i) {
+    if (tile_key0(i) > pos_hi) break;     // tiles of a warp ascend: nothing further is visible
+    if (i > i0) {
+      __syncwarp();                       // every lane is done reading the buffer
+      const TilePages tp = tile_pages<SBN>(table, page_size, tile_key0(i), key_first, kv_end);
+      load_tile<32, SBN>(Kw, k_cache, tp, kvh, nkv, page_size, tile_key0(i), key_first, kv_end, lane);
+      load_tile<32, SBN>(Vw, v_cache, tp, kvh, nkv, page_size, tile_key0(i), key_first, kv_end, lane);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncwarp();
+    }
+    attend_tile<1, SBN, true, true>(nullptr, Qs, Kw, Vw, o, st, tile_key0(i), lo, hi, scale_log2);
   }
   __syncthreads();   // all warps are done with their tiles: the buffer becomes the merge area
 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = h * 8 + g;
-    float l = st.l[h];
+    float l = st[0].l[h];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     float* dst = merge + ((size_t)warp * 16 + r) * PART;
-    if (t == 0) { dst[0] = st.m[h]; dst[1] = l; }
+    if (t == 0) { dst[0] = st[0].m[h]; dst[1] = l; }
 #pragma unroll
     for (int dt = 0; dt < HD / 8; ++dt) {
-      dst[2 + dt * 8 + 2 * t] = o[dt][2 * h];
-      dst[2 + dt * 8 + 2 * t + 1] = o[dt][2 * h + 1];
+      dst[2 + dt * 8 + 2 * t] = o[0][dt][2 * h];
+      dst[2 + dt * 8 + 2 * t + 1] = o[0][dt][2 * h + 1];
     }
   }
   __syncthreads();
@@ -437,11 +533,14 @@ attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__
 // One CTA per (request, kv head, row): the splits' (max, sum) pairs are read once into
 // shared memory, then every thread merges its head-dim columns over the splits in
 // ascending order with independent loads.
+template <int SPLIT>
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* __restrict__ scratch, int max_splits, bf16* __restrict__ out, long out_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, int nh, int nkv, int window) {
   __shared__ float factor[512];
   __shared__ float s_den;
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const int b = blockIdx.z, kvh = blockIdx.y, r = blockIdx.x;
   const int G = nh / nkv;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
@@ -476,19 +575,46 @@ attn_combine_kernel(const float* __restrict__ scratch, int max_splits, bf16* __r
   }
 }
 
-constexpr size_t TILES_SMEM = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
-constexpr size_t SPLIT_TILE_SMEM = (size_t)(16 + 4 * 2 * BN) * LDS * sizeof(bf16);
-constexpr size_t SPLIT_MERGE_SMEM = (size_t)16 * LDS * sizeof(bf16) + (size_t)4 * 16 * PART * sizeof(float);
-constexpr size_t SPLIT_SMEM = SPLIT_TILE_SMEM > SPLIT_MERGE_SMEM ? SPLIT_TILE_SMEM : SPLIT_MERGE_SMEM;
+constexpr size_t TILES_SMEM = (size_t)(BM + 4 * TBN) * LDS * sizeof(bf16);
+constexpr size_t split_smem(int sbn) {
+  const size_t tiles = (size_t)(16 + 4 * 2 * sbn) * LDS * sizeof(bf16);
+  const size_t merge = (size_t)16 * LDS * sizeof(bf16) + (size_t)4 * 16 * PART * sizeof(float);
+  return tiles > merge ? tiles : merge;
+}
+
+template <int SBN, int SPLIT>
+int launch_split(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
+                 const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
+                 int page_size, int window, float scale_log2, int max_kv_len, float* scratch, long scratch_floats,
+                 cudaStream_t stream) {
+  constexpr size_t SMEM = split_smem(SBN);
+  const int max_splits = (max_kv_len + SPLIT - 1) / SPLIT + 1;
+  if (!scratch || scratch_floats < (long)B * nkv * max_splits * 16 * PART)
+    CO_FAIL("attention_bf16: scratch of %ld floats is too small", scratch_floats);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<SBN, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  co_launch(attn_split_kernel<SBN, SPLIT>, dim3(max_splits, nkv, B), dim3(128), SMEM, stream, (const bf16*)q, q_stride,
+            scratch, max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens,
+            nh, nkv, page_size, window, scale_log2);
+  CO_CHECK_LAUNCH("attn_split");
+  co_launch(attn_combine_kernel<SPLIT>, dim3(16, nkv, B), dim3(HD >= 128 ? 128 : 64), 0, stream, (const float*)scratch,
+            max_splits, (bf16*)out, out_stride, cu_q, kv_lens, nh, nkv, window);
+  CO_CHECK_LAUNCH("attn_combine");
+  return 0;
+}
 }  // namespace
 
 CO_EXPORT int coheryn_attn_head_dim() { return HD; }
-CO_EXPORT int coheryn_attn_split_keys() { return SPLIT; }
+CO_EXPORT int coheryn_attn_split_keys() { return SPLIT_MIN; }
 
 // Floats of scratch that coheryn_attention_bf16 needs for B requests of at most
 // max_kv_len positions when some request takes the split path.
 CO_EXPORT long coheryn_attn_scratch_floats(int B, int nkv, int max_kv_len) {
-  const long max_splits = (max_kv_len + SPLIT - 1) / SPLIT + 1;
+  const long max_splits = (max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1;   // covers both split sizes
   return (long)B * nkv * max_splits * 16 * PART;
 }
 
@@ -509,7 +635,8 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
   const int G = nh / nkv;
   // The split kernel keeps eight tiles in shared memory; beyond 227 KB every request takes
   // the tile kernel instead.
-  const bool split_path = any_small && G <= 16 && SPLIT_SMEM <= 227 * 1024;
+  const bool split_path = any_small && G <= 16 && split_smem(32) <= 227 * 1024 &&
+                          (max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1 <= 512;   // attn_combine keeps 512 factors
   if (any_large || (any_small && !split_path)) {
     static bool configured = false;
     if (!configured) {
@@ -518,29 +645,20 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
       configured = true;
     }
     dim3 grid((max_rows + BM - 1) / BM, nkv, B);
-    attn_tiles_kernel<<<grid, 128, TILES_SMEM, stream>>>(
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables,
-        max_blocks, cu_q, kv_lens, nh, nkv, page_size, window, scale_log2, split_path ? 1 : 0);
+    co_launch(attn_tiles_kernel, grid, dim3(128), TILES_SMEM, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+              (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
+              window, scale_log2, split_path ? 1 : 0);
     CO_CHECK_LAUNCH("attn_tiles");
   }
   if (split_path) {
-    const int max_splits = (max_kv_len + SPLIT - 1) / SPLIT + 1;
-    if (!scratch || scratch_floats < (long)B * nkv * max_splits * 16 * PART)
-      CO_FAIL("attention_bf16: scratch of %ld floats is too small", scratch_floats);
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SPLIT_SMEM);
-      if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", SPLIT_SMEM, cudaGetErrorString(e));
-      configured = true;
-    }
-    dim3 grid(max_splits, nkv, B);
-    attn_split_kernel<<<grid, 128, SPLIT_SMEM, stream>>>(
-        (const bf16*)q, q_stride, scratch, max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables,
-        max_blocks, cu_q, kv_lens, nh, nkv, page_size, window, scale_log2);
-    CO_CHECK_LAUNCH("attn_split");
-    attn_combine_kernel<<<dim3(16, nkv, B), HD >= 128 ? 128 : 64, 0, stream>>>(scratch, max_splits, (bf16*)out, out_stride, cu_q, kv_lens,
-                                                          nh, nkv, window);
-    CO_CHECK_LAUNCH("attn_combine");
+    // All CTAs of the wide shape resident at once (one per SM, with a little queueing)?
+    const long wide_ctas = (long)B * nkv * ((max_kv_len + 255) / 256 + 1);
+    if (wide_ctas <= 2 * 148 && split_smem(64) <= 227 * 1024)
+      return launch_split<64, 256>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q,
+                                   kv_lens, B, nh, nkv, page_size, window, scale_log2, max_kv_len, scratch,
+                                   scratch_floats, stream);
+    return launch_split<32, 128>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens,
+                                 B, nh, nkv, page_size, window, scale_log2, max_kv_len, scratch, scratch_floats, stream);
   }
   return 0;
 }

@@ -28,6 +28,32 @@ void co_count_launch();
     if (e__ != cudaSuccess) CO_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// Programmatic dependent launch: a kernel launched with co_launch() may begin while its
+// predecessor in the stream is still running.  It must call co_pdl_wait() before it reads
+// or writes anything a predecessor touches (weights and other constants may be fetched
+// earlier), and it calls co_pdl_launch_dependents() to let its own successor start its
+// preamble.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void co_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void co_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool co_pdl_enabled();   // COHERYN_PDL=0 in the environment switches the launch attribute off
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t co_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = co_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T>
 __device__ __forceinline__ float co_to_float(T v);
 template <>

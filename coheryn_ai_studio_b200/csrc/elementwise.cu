@@ -10,6 +10,8 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V, int* __restrict__ status) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= V) {
@@ -26,9 +28,9 @@ CO_EXPORT int coheryn_embed_gather(const void* table, int table_dtype, const int
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == CO_F32)
-    embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V, status);
+    co_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, status);
   else if (table_dtype == CO_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H, V, status);
+    co_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, status);
   else
     CO_FAIL("embed_gather: unknown table dtype %d", table_dtype);
   CO_CHECK_LAUNCH("embed_gather");
@@ -47,6 +49,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    const int* __restrict__ rows, const void* __restrict__ weight,
                                    int wdtype, float eps, TO* __restrict__ out, int H, int update) {
   __shared__ float scratch[33];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const int r = blockIdx.x;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float* x = resid + src * H;
@@ -71,15 +75,99 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   }
 }
 
+// Vector variant for widths that are a multiple of 4 and at most 8192: the row stays in
+// registers between the two passes (float4 per thread and step), the delta is read four at
+// a time.  Same arithmetic and the same order of summation per thread count.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&a);
+    raw.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+
+template <typename TD, typename TO, typename TW, int STEPS>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const int* __restrict__ rows,
+                       const TW* __restrict__ weight, float eps, TO* __restrict__ out, int H, int update) {
+  __shared__ float scratch[33];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* x = resid + src * H;
+  const TD* d = delta ? delta + src * H : nullptr;
+  float4 v[STEPS];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    const int j = (i * 256 + threadIdx.x) * 4;
+    if (j < H) {
+      v[i] = Vec4<float>::load(x + j);
+      if (d) {
+        const float4 dv = Vec4<TD>::load(d + j);
+        v[i].x += dv.x; v[i].y += dv.y; v[i].z += dv.z; v[i].w += dv.w;
+        if (update) Vec4<float>::store(x + j, v[i]);
+      }
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+  }
+  ss = co_block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* o = out + (size_t)r * H;
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    const int j = (i * 256 + threadIdx.x) * 4;
+    if (j < H) {
+      const float4 w = Vec4<TW>::load(weight + j);
+      Vec4<TO>::store(o + j, make_float4((v[i].x * scale) * w.x, (v[i].y * scale) * w.y, (v[i].z * scale) * w.z,
+                                         (v[i].w * scale) * w.w));
+    }
+  }
+}
+
+template <typename TD, typename TO, typename TW>
+void launch_rmsnorm_vec(float* resid, const void* delta, const int* rows, const void* weight, float eps, void* out,
+                        int n_rows, int H, int update, cudaStream_t stream) {
+  const int steps = (H / 4 + 255) / 256;
+#define GO(S) co_launch(add_rmsnorm_vec_kernel<TD, TO, TW, S>, dim3(n_rows), dim3(256), 0, stream, resid, (const TD*)delta, \
+                        rows, (const TW*)weight, eps, (TO*)out, H, update)
+  if (steps <= 1) GO(1); else if (steps <= 2) GO(2); else if (steps <= 4) GO(4); else GO(8);
+#undef GO
+}
+
 CO_EXPORT int coheryn_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const int* rows,
                                   const void* weight, int wdtype, float eps, void* out, int out_dtype,
                                   int n_rows, int H, int update, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (rows && update) CO_FAIL("add_rmsnorm: cannot update the residual through a row gather");
+  if (H % 4 == 0 && H <= 8192 && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)delta & 7) == 0 &&
+      ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0 && (!delta || delta_dtype == out_dtype)) {
+    const bool bf = out_dtype == CO_BF16;
+    if (bf && wdtype == CO_BF16) launch_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(resid, delta, rows, weight, eps, out, n_rows, H, update, stream);
+    else if (bf) launch_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, float>(resid, delta, rows, weight, eps, out, n_rows, H, update, stream);
+    else if (wdtype == CO_F32) launch_rmsnorm_vec<float, float, float>(resid, delta, rows, weight, eps, out, n_rows, H, update, stream);
+    else launch_rmsnorm_vec<float, float, __nv_bfloat16>(resid, delta, rows, weight, eps, out, n_rows, H, update, stream);
+    CO_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+  }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define LAUNCH(TD, TO)                                                                         \
-  add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(resid, (const TD*)delta, rows, weight, \
-                                                             wdtype, eps, (TO*)out, H, update)
+#define LAUNCH(TD, TO)                                                                              \
+  co_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid, (const TD*)delta, rows, \
+            weight, wdtype, eps, (TO*)out, H, update)
   if (delta_dtype == CO_F32 && out_dtype == CO_F32) LAUNCH(float, float);
   else if (delta_dtype == CO_BF16 && out_dtype == CO_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (delta_dtype == CO_F32 && out_dtype == CO_BF16) LAUNCH(float, __nv_bfloat16);
@@ -97,6 +185,8 @@ CO_EXPORT int coheryn_add_rmsnorm(float* resid, const void* delta, int delta_dty
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const size_t m = i / I, j = i % I;
@@ -111,8 +201,8 @@ CO_EXPORT int coheryn_silu_mul(const void* in, void* out, int dtype, int M, int 
   if (total == 0) return 0;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == CO_F32) silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)in, (float*)out, I, total);
-  else if (dtype == CO_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, total);
+  if (dtype == CO_F32) co_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, I, total);
+  else if (dtype == CO_BF16) co_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, total);
   else CO_FAIL("silu_mul: unknown dtype %d", dtype);
   CO_CHECK_LAUNCH("silu_mul");
   return 0;
@@ -132,6 +222,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const float2* __restrict__ cos_sin, const int* __restrict__ slots,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv,
                                      int hd, int rot, int page_size, int write_kv) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // [0, nh): q   [nh, nh+nkv): k   [nh+nkv, nh+2nkv): v
   const int row_stride = (nh + 2 * nkv) * hd;
@@ -165,19 +257,85 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// Vector variant: one block per token; an item is 16 bytes of a head's first half together
+// with the matching 16 bytes of its second half (q and k heads), or 16 bytes of a v head.
+// Needs rot == hd and hd/2 a multiple of the vector width.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_kv_write_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const float2* __restrict__ cos_sin,
+                         const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache, int nh,
+                         int nkv, int hd, int page_size, int write_kv) {
+  constexpr int VEC = 16 / sizeof(T);
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int t = blockIdx.x;
+  const int half = hd >> 1, per_half = half / VEC, per_head = hd / VEC;
+  T* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+  const int pos = positions[t];
+  const float2* cs = cos_sin + (size_t)pos * half;
+  const int slot = write_kv ? slots[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  const int rot_items = (nh + (write_kv ? nkv : 0)) * per_half;
+  const int items = rot_items + (write_kv ? nkv * per_head : 0);
+  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    if (it < rot_items) {
+      const int head = it / per_half, c = (it % per_half) * VEC;
+      T* src = row + (size_t)head * hd;
+      T a[VEC], b[VEC];
+      *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(src + c);
+      *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(src + half + c);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float fa = co_to_float(a[i]), fb = co_to_float(b[i]);
+        const float2 k = cs[c + i];
+        a[i] = co_from_float<T>(fmaf(fa, k.x, -(fb * k.y)));
+        b[i] = co_from_float<T>(fmaf(fa, k.y, fb * k.x));
+      }
+      T* dst = src;
+      if (head >= nh) {
+        if (slot < 0) continue;
+        dst = k_cache + (((size_t)page * nkv + (head - nh)) * page_size + off) * hd;
+      }
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(a);
+      *reinterpret_cast<uint4*>(dst + half + c) = *reinterpret_cast<const uint4*>(b);
+    } else {
+      if (slot < 0) continue;
+      const int j = it - rot_items;
+      const int kvh = j / per_head, c = (j % per_head) * VEC;
+      const T* src = row + (size_t)(nh + nkv + kvh) * hd;
+      T* dst = v_cache + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+    }
+  }
+}
+
 CO_EXPORT int coheryn_rope_kv_write(void* qkv, int dtype, const int* positions, const float* cos_sin,
                                     const int* slots, void* k_cache, void* v_cache, int T, int nh, int nkv,
                                     int hd, int rot, int page_size, int write_kv, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > hd || (rot & 1)) CO_FAIL("rope_kv_write: rotary size %d does not fit head size %d", rot, hd);
+  const int vec = dtype == CO_F32 ? 4 : 8;
+  if (rot == hd && (hd / 2) % vec == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 &&
+      ((uintptr_t)v_cache & 15) == 0) {
+    if (dtype == CO_F32)
+      co_launch(rope_kv_write_vec_kernel<float>, dim3(T), dim3(128), 0, stream, (float*)qkv, positions,
+                (const float2*)cos_sin, slots, (float*)k_cache, (float*)v_cache, nh, nkv, hd, page_size, write_kv);
+    else if (dtype == CO_BF16)
+      co_launch(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (__nv_bfloat16*)qkv, positions,
+                (const float2*)cos_sin, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, hd, page_size,
+                write_kv);
+    else CO_FAIL("rope_kv_write: unknown dtype %d", dtype);
+    CO_CHECK_LAUNCH("rope_kv_write");
+    return 0;
+  }
   dim3 grid(T, nh + 2 * nkv);
   const int threads = hd >= 128 ? 64 : 32;
   if (dtype == CO_F32)
-    rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, positions, (const float2*)cos_sin, slots,
-                                                              (float*)k_cache, (float*)v_cache, nh, nkv, hd, rot, page_size, write_kv);
+    co_launch(rope_kv_write_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, positions, (const float2*)cos_sin, slots,
+              (float*)k_cache, (float*)v_cache, nh, nkv, hd, rot, page_size, write_kv);
   else if (dtype == CO_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, (const float2*)cos_sin, slots,
-                                                                      (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, hd, rot, page_size, write_kv);
+    co_launch(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)qkv, positions, (const float2*)cos_sin, slots,
+              (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, hd, rot, page_size, write_kv);
   else CO_FAIL("rope_kv_write: unknown dtype %d", dtype);
   CO_CHECK_LAUNCH("rope_kv_write");
   return 0;

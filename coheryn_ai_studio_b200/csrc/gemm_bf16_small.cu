@@ -4,13 +4,18 @@
 // shaped around the weight stream, not around the arithmetic.
 //
 // A CTA owns NT*8 consecutive rows of W (output features) for ALL tokens; its warps
-// split K in interleaved blocks of 32 (warp w takes blocks w, w+W, ...), each thread
-// fetching 16 contiguous bytes of a W row per block with a streaming load.  Tokens sit
-// on the M axis of the MMA (tiles of 16, zero padded), features on the N axis (tiles of
-// 8).  The k order inside a block is permuted identically for both operands so that a
-// thread's 16 bytes feed two MMAs without a shuffle.  Per-warp partial sums are combined
-// through shared memory in warp order.  An output element is therefore always summed in
-// the same order, whatever M is: a row's result does not depend on the batch around it.
+// split K in interleaved blocks of 64 (warp w takes blocks w, w+W, ...).  In a block a
+// thread fetches 32 contiguous bytes of a W row with streaming loads, so the four
+// threads that share a row cover one 128-byte line.  Tokens sit on the M axis of the MMA
+// (tiles of 16, zero padded), features on the N axis (tiles of 8).  The k order inside a
+// block is permuted identically for both operands so that a thread's 16 bytes feed two
+// MMAs without a shuffle.  Per-warp partial sums are combined through shared memory in
+// warp order.  An output element is therefore always summed in the same order, whatever
+// M is: a row's result does not depend on the batch around it.
+//
+// The first batch of weight loads is issued BEFORE the kernel waits for its predecessor
+// in the stream (programmatic dependent launch): weights depend on nothing, so the stream
+// of the next matrix starts while the previous kernel drains.
 //
 // Epilogues: bias; or gated SiLU over interleaved rows (row 2j = gate_j, row 2j+1 = up_j:
 // out[m, j] = silu(acc[2j]) * acc[2j+1]), which keeps a gate/up pair in one thread.
@@ -34,10 +39,10 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int EPI_PLAIN = 0, EPI_GATED_SILU = 1;
+constexpr int EPI_GATED_SILU = 1;
 
 template <int MT, int NT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                   const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype,
                   int M, int N, int K, long ldx, long ldo, int epilogue) {
@@ -49,6 +54,27 @@ gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   const __nv_bfloat16* wrow[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) wrow[nt] = w + (size_t)min(n_base + nt * 8 + g, N - 1) * K;
+
+  // Blocks of 64 k are taken in batches of U: all loads of a batch are issued before its
+  // first MMA, so that a warp keeps U * NT * 1 KB of the weight stream in flight.
+  constexpr int U = (MT * NT >= 8) ? 1 : ((MT * NT >= 4) ? 2 : 4);
+  const int nblk = (K + 63) >> 6;
+  uint4 wv[U][NT][2];
+  auto load_w = [&](int blk0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = ((blk0 + u * warps) << 6) + (t << 4);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int p = 0; p < 2; ++p)   // K is a multiple of 8: a 16-byte piece is whole or absent
+          wv[u][nt][p] = (k + 8 * p < K) ? ld_stream(wrow[nt] + k + 8 * p) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  load_w(warp);                  // weights depend on no earlier kernel
+  co_pdl_launch_dependents();
+  co_pdl_wait();                 // x is the predecessor's output
+
   const __nv_bfloat16* xrow[MT][2];
   bool xok[MT][2];
 #pragma unroll
@@ -59,7 +85,6 @@ gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       xok[mt][h] = m < M;
       xrow[mt][h] = x + (size_t)min(m, M - 1) * ldx;
     }
-
   float acc[MT][NT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -68,33 +93,33 @@ gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
-  // Blocks are taken in batches of U: all loads of a batch are issued before its first
-  // MMA, so that a warp keeps U * NT * 512 bytes of the weight stream in flight.
-  constexpr int U = (MT * NT >= 8) ? 2 : ((MT * NT >= 4) ? 4 : 8);
-  const int nblk = (K + 31) >> 5;
   for (int blk0 = warp; blk0 < nblk; blk0 += warps * U) {
-    uint4 wv[U][NT], xa[U][MT], xb[U][MT];
+    if (blk0 != warp) load_w(blk0);
+    uint4 xa[U][MT][2], xb[U][MT][2];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int k = ((blk0 + u * warps) << 5) + (t << 3);
-      const bool valid = k < K;  // K is a multiple of 8: a 16-byte piece is whole or absent
+      const int k = ((blk0 + u * warps) << 6) + (t << 4);
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) wv[u][nt] = valid ? ld_stream(wrow[nt] + k) : make_uint4(0, 0, 0, 0);
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        xa[u][mt] = (valid && xok[mt][0]) ? __ldg((const uint4*)(xrow[mt][0] + k)) : make_uint4(0, 0, 0, 0);
-        xb[u][mt] = (valid && xok[mt][1]) ? __ldg((const uint4*)(xrow[mt][1] + k)) : make_uint4(0, 0, 0, 0);
-      }
+        for (int p = 0; p < 2; ++p) {
+          const bool valid = k + 8 * p < K;
+          xa[u][mt][p] = (valid && xok[mt][0]) ? __ldg((const uint4*)(xrow[mt][0] + k + 8 * p)) : make_uint4(0, 0, 0, 0);
+          xb[u][mt][p] = (valid && xok[mt][1]) ? __ldg((const uint4*)(xrow[mt][1] + k + 8 * p)) : make_uint4(0, 0, 0, 0);
+        }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+      for (int p = 0; p < 2; ++p)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          mma_bf16(acc[mt][nt], xa[u][mt].x, xb[u][mt].x, xa[u][mt].y, xb[u][mt].y, wv[u][nt].x, wv[u][nt].y);
-          mma_bf16(acc[mt][nt], xa[u][mt].z, xb[u][mt].z, xa[u][mt].w, xb[u][mt].w, wv[u][nt].z, wv[u][nt].w);
-        }
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint4 a = xa[u][mt][p], b = xb[u][mt][p], c = wv[u][nt][p];
+            mma_bf16(acc[mt][nt], a.x, b.x, a.y, b.y, c.x, c.y);
+            mma_bf16(acc[mt][nt], a.z, b.z, a.w, b.w, c.z, c.w);
+          }
   }
 
   // Partial sums of every warp, laid out so that lanes write consecutive words.
@@ -157,8 +182,9 @@ int launch_small(const void* x, const void* w, const void* bias, int bias_dtype,
     if (e != cudaSuccess) CO_FAIL("gemm_small: shared memory %zu: %s", smem, cudaGetErrorString(e));
   }
   const int grid = (N + NT * 8 - 1) / (NT * 8);
-  kernel<<<grid, warps * 32, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype,
-                                             out, out_dtype, M, N, K, ldx, ldo, epilogue);
+  cudaError_t e = co_launch(kernel, dim3(grid), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
+                            (const __nv_bfloat16*)w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, ldo, epilogue);
+  if (e != cudaSuccess) CO_FAIL("gemm_small: launch failed: %s", cudaGetErrorString(e));
   CO_CHECK_LAUNCH("gemm_small");
   return 0;
 }
@@ -177,12 +203,13 @@ CO_EXPORT int coheryn_gemm_bf16_small(const void* x, const void* w, const void* 
   if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_small: gated epilogue needs an even number of rows");
   if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_small: unknown epilogue %d", epilogue);
   // Rows per CTA: as many as keep at least ~2 CTAs per SM (148 SMs); more rows per CTA
-  // mean fewer re-reads of x through L2.
+  // mean fewer re-reads of x through L2.  The warps of a CTA split K (a function of K
+  // alone, so the order of summation never depends on M or N).
   const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
   int nt = 8 / mt;  // MT * NT <= 8 bounds registers and the reduction buffer
   while (nt > 1 && (N + nt * 8 - 1) / (nt * 8) < 296) nt >>= 1;
-  const int nblk = (K + 31) / 32;
-  const int warps = nblk >= 8 ? 8 : (nblk >= 4 ? 4 : (nblk >= 2 ? 2 : 1));
+  const int nblk = (K + 63) / 64;
+  const int warps = nblk >= 64 ? 16 : (nblk >= 8 ? 8 : (nblk >= 4 ? 4 : (nblk >= 2 ? 2 : 1)));
 #define GO(MT_, NT_) return launch_small<MT_, NT_>(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, ldo, epilogue, warps, stream)
   if (mt == 1) { if (nt == 8) GO(1, 8); if (nt == 4) GO(1, 4); if (nt == 2) GO(1, 2); GO(1, 1); }
   if (mt == 2) { if (nt == 4) GO(2, 4); if (nt == 2) GO(2, 2); GO(2, 1); }

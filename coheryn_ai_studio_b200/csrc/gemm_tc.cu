@@ -101,7 +101,7 @@ struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + BN * 4 /* bias */;
 };
 
 template <int BN, int STAGES>
@@ -117,6 +117,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   unsigned long long* empty = full + STAGES;
   unsigned long long* accum_full = empty + STAGES;
   unsigned* tmem_slot = (unsigned*)(accum_full + 1);
+  float* bias_s = (float*)(tiles + STAGES * S::STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -136,6 +137,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
+  co_pdl_launch_dependents();
+  co_pdl_wait();     // barriers and tensor memory are set up; x is the predecessor's output
 
   if (warp == 0) {
     if (lane == 0) {
@@ -169,6 +172,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // Epilogue warps 2..5: TMEM lane quarter = warp % 4.
     const int quarter = warp & 3;
     const int row = m0 + quarter * 32 + lane;
+    if (bias) {   // the tile's slice of the bias, once, while the main loop runs
+      for (int i = threadIdx.x - 64; i < BN; i += 128) bias_s[i] = n0 + i < N ? co_load_any(bias, bias_dtype, n0 + i) : 0.f;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     const bool waited = mbar_wait(accum_full, 0);
     if (!waited && lane == 0) atomicExch(status, 13);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -186,7 +193,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-            v[j] = (g / (1.0f + __expf(-g))) * u;
+            v[j] = __fdividef(g, 1.0f + __expf(-g)) * u;
           }
           const int n_out = N >> 1;
           if (out_dtype == CO_BF16) {
@@ -211,8 +218,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         if (bias) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (n0 + c0 + j < N) v[j] += co_load_any(bias, bias_dtype, n0 + c0 + j);
+          for (int j = 0; j < 32; ++j) v[j] += bias_s[c0 + j];
         }
         const int nc = n0 + c0;
         if (out_dtype == CO_BF16) {
@@ -291,11 +297,18 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
     configured = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  kernel<<<grid, 192, smem, stream>>>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status);
+  cudaError_t le = co_launch(kernel, grid, dim3(192), (size_t)smem, stream, mx, mw, bias, bias_dtype, out, out_dtype, M, N,
+                             K, ldo, epilogue, status);
+  if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("gemm_tc");
   return 0;
 }
 }  // namespace
+
+// Tuning knobs for experiments: tile width (0 = by shape, 128 caps it) and stage count
+// (0 = the default of the tile width).
+static int g_bn = 0, g_stages = 0;
+CO_EXPORT void coheryn_gemm_tc_tune(int bn, int stages) { g_bn = bn; g_stages = stages; }
 
 // x: [M, K] bfloat16 with row stride ldx; w: [N, K] bfloat16 contiguous; K and ldx multiples
 // of 8, bases 16-byte aligned.  epilogue 0: out[M, N] (+ bias); 1: gated SiLU over
@@ -309,11 +322,19 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc: operands must be 16-byte aligned");
   if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc: gated epilogue needs an even number of rows");
   if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
-  const int bn = N >= 192 ? 256 : (N >= 96 ? 128 : (N >= 48 ? 64 : 32));
+  int bn = N >= 192 ? 256 : (N >= 96 ? 128 : (N >= 48 ? 64 : 32));
+  // Few row tiles (a decode batch, a short portion): narrower tiles put more CTAs on the
+  // weight stream.
+  const long tiles_m = (M + BM - 1) / BM;
+  while (tiles_m == 1 && bn > 64 && (N + bn - 1) / bn < 120) bn >>= 1;
+  if (g_bn == 128 && bn > 128) bn = 128;
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, K, bn))
     CO_FAIL("gemm_bf16_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%ld)", M, N, K, ldx);
 #define GO(BN_, ST_) return launch_tc<BN_, ST_>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, stream)
+  if (bn == 256 && g_stages == 2) GO(256, 2);
+  if (bn == 256 && g_stages == 3) GO(256, 3);
+  if (bn == 128 && g_stages == 3) GO(128, 3);
   if (bn == 256) GO(256, 4);
   if (bn == 128) GO(128, 6);
   if (bn == 64) GO(64, 8);

@@ -1,5 +1,6 @@
 // Error channel and identification of the kernel library.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -30,4 +31,13 @@ static unsigned long long g_launches = 0;
 void co_count_launch() { __atomic_add_fetch(&g_launches, 1ull, __ATOMIC_RELAXED); }
 CO_EXPORT unsigned long long coheryn_launch_count() {
   return __atomic_load_n(&g_launches, __ATOMIC_RELAXED);
+}
+
+bool co_pdl_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* e = getenv("COHERYN_PDL");
+    state = (e && e[0] == '0') ? 0 : 1;
+  }
+  return state == 1;
 }

@@ -24,6 +24,8 @@ argmax_kernel(const float* __restrict__ logits, long stride, int V, int* __restr
               int* __restrict__ status) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * stride;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -66,6 +68,8 @@ argmax_pieces_kernel(const float* __restrict__ logits, long stride, int V, float
                      int* __restrict__ part_idx, int pieces, int* __restrict__ status) {
   __shared__ float sv[8];
   __shared__ int si[8];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const int r = blockIdx.y, piece = blockIdx.x;
   const float* row = logits + (size_t)r * stride;
   const int lo = piece * ARGMAX_PIECE, hi = min(V, lo + ARGMAX_PIECE);
@@ -98,6 +102,8 @@ argmax_pieces_kernel(const float* __restrict__ logits, long stride, int V, float
 __global__ void __launch_bounds__(64)
 argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int pieces,
                     int* __restrict__ out) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
   const int r = blockIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -374,13 +380,13 @@ CO_EXPORT int coheryn_argmax(const float* logits, long stride, int R, int V, int
   if (pieces >= 4 && scratch && scratch_slots >= (long)R * pieces) {
     float* pv = (float*)scratch;
     int* pi = (int*)scratch + (size_t)R * pieces;
-    argmax_pieces_kernel<<<dim3(pieces, R), 256, 0, stream>>>(logits, stride, V, pv, pi, pieces, status);
+    co_launch(argmax_pieces_kernel, dim3(pieces, R), dim3(256), 0, stream, logits, stride, V, pv, pi, pieces, status);
     CO_CHECK_LAUNCH("argmax_pieces");
-    argmax_final_kernel<<<R, 64, 0, stream>>>(pv, pi, pieces, out);
+    co_launch(argmax_final_kernel, dim3(R), dim3(64), 0, stream, (const float*)pv, (const int*)pi, pieces, out);
     CO_CHECK_LAUNCH("argmax_final");
     return 0;
   }
-  argmax_kernel<<<R, 1024, 0, stream>>>(logits, stride, V, out, status);
+  co_launch(argmax_kernel, dim3(R), dim3(1024), 0, stream, logits, stride, V, out, status);
   CO_CHECK_LAUNCH("argmax");
   return 0;
 }

@@ -257,6 +257,10 @@ def gemm_bf16_small(x, w, bias, out, gated: bool = False) -> None:
         c_int(1 if gated else 0), _stream()))
 
 
+# Up to this many rows the weight-streaming mma.sync kernel runs; beyond it the TMA/tcgen05
+# kernel (which re-reads nothing of x through L2 and so scales to many rows).
+SMALL_M = 16
+
 _tc_status = {}
 
 
@@ -290,13 +294,13 @@ def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
 
 
 def _tc_ok(x, w) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 64
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > SMALL_M
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0)
 
 
 def _small_ok(x, w) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= 64
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SMALL_M
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0)
 

@@ -160,10 +160,19 @@ def test_rows_do_not_depend_on_batch(dtype):
     full = ops().linear(x, w)
     for r in (0, 13, 69):
         assert torch.equal(ops().linear(x[r:r + 1].contiguous(), w)[0], full[r])
-    if dtype == torch.bfloat16:     # the tensor-core kernel for few rows: 1, 9, 33 and 64 rows agree bitwise
-        big = ops().linear(x[:64].contiguous(), w)
+    if dtype == torch.bfloat16:     # the weight-streaming kernel: 1, 9, 33 and 64 rows agree bitwise
+        big = torch.empty(64, 90, dtype=dtype, device=DEV)
+        ops().gemm_bf16_small(x[:64].contiguous(), w, None, big)
         for m in (1, 9, 33):
-            assert torch.equal(ops().linear(x[:m].contiguous(), w), big[:m])
+            part = torch.empty(m, 90, dtype=dtype, device=DEV)
+            ops().gemm_bf16_small(x[:m].contiguous(), w, None, part)
+            assert torch.equal(part, big[:m])
+        # and the TMA/tcgen05 kernel: a row alone in its tile or among 69 others
+        tc_full = torch.empty(70, 90, dtype=dtype, device=DEV)
+        ops().gemm_bf16_tc(x, w, None, tc_full)
+        tc_part = torch.empty(17, 90, dtype=dtype, device=DEV)
+        ops().gemm_bf16_tc(x[40:57].contiguous(), w, None, tc_part)
+        assert torch.equal(tc_part, tc_full[40:57])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
