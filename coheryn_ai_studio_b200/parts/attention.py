@@ -65,24 +65,42 @@ class Attention(Mixer):
         self.b_o = tensors.get("o_proj.bias")
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        self._check(cache)
+        if cache.writes:
+            qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        else:   # this execution reads keys and values another one wrote: only q is made
+            qkv = ops.linear(x, self.w_qkv[:self.q_size], self.b_qkv[:self.q_size] if self.b_qkv is not None else None)
+        return self._attend(qkv, step, cache)
+
+    def forward_with_norm(self, residual, delta, norm, step: StepContext, cache: LayerCache):
+        """The same with the preceding norm folded into the q/k/v projection where a kernel
+        exists for it; returns (y, residual after the add)."""
+        self._check(cache)
+        if cache.writes:
+            qkv, residual = norm.fused_linear(residual, delta, self.w_qkv, self.b_qkv)
+        else:
+            qkv, residual = norm.fused_linear(residual, delta, self.w_qkv[:self.q_size],
+                                              self.b_qkv[:self.q_size] if self.b_qkv is not None else None)
+        return self._attend(qkv, step, cache), residual
+
+    @staticmethod
+    def _check(cache) -> None:
         if cache is None or cache.kind != "paged":
             raise ValueError("attention needs a paged key/value cache")
-        T = x.shape[0]
+
+    def _attend(self, qkv: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        T = qkv.shape[0]
         nh, hd = self.num_heads, self.head_dim
         rot = self.position.rotary_dim if self.position is not None else 0
         cos_sin = self.position.cos_sin() if self.position is not None else None
         if cache.writes:
-            qkv = ops.linear(x, self.w_qkv, self.b_qkv)
             ops.rope_kv_write(qkv, step.positions, cos_sin, step.slots[cache.group], cache.k, cache.v,
                               nh, self.num_kv_heads, hd, rot, cache.page_size)
             q = qkv[:, :self.q_size]
         else:
-            # This execution reads keys and values another one wrote: only q is made.
-            q = ops.linear(x, self.w_qkv[:self.q_size],
-                           self.b_qkv[:self.q_size] if self.b_qkv is not None else None)
-            ops.rope_kv_write(q, step.positions, cos_sin, None, None, None, nh, 0, hd, rot,
-                              cache.page_size)
-        o = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+            q = qkv
+            ops.rope_kv_write(q, step.positions, cos_sin, None, None, None, nh, 0, hd, rot, cache.page_size)
+        o = torch.empty((T, self.q_size), dtype=qkv.dtype, device=qkv.device)
         ops.attention(q, o, cache.k, cache.v, step, cache.group, nh, self.num_kv_heads, hd,
                       cache.page_size, self.window, self.scale)
         return ops.linear(o, self.w_o, self.b_o)
