@@ -75,7 +75,7 @@ def _existing_lib(name: str) -> Optional[str]:
 
 def _digest(sources: Sequence[str], defines: Dict[str, object], extra: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for f in list(sources) + HEADERS + sorted(x for x in os.listdir(HERE) if x.endswith(".cuh")):
+    for f in list(sources) + HEADERS + sorted(x for x in os.listdir(HERE) if x.endswith((".cuh", ".h"))):
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(f.encode())
             h.update(fh.read())

@@ -402,3 +402,48 @@ CO_EXPORT int coheryn_sample(const float* logits, long stride, int R, int V, con
   CO_CHECK_LAUNCH("sample");
   return 0;
 }
+
+// ------------------------------------------------------------------------------------
+// Allocation-free greedy selection; see no_alloc.h for who needs it and for its limits.
+// ------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// The piece buffers: values (float) for all rows first, then indices (int).  Device code
+// could name this array directly; host code may only use its address as looked up below.
+static __device__ __align__(256) unsigned char g_argmax_static_scratch[(size_t)COHERYN_ARGMAX_STATIC_SLOTS * 8];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+void* g_static_scratch_ptr[MAX_DEVICES];   // per device: the array's device address, once looked up
+}  // namespace
+
+CO_EXPORT int coheryn_argmax_static(const float* logits, long stride, int rows, int vocab, int* out, int* status,
+                                    cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) CO_FAIL("argmax_static: empty vocabulary");
+  const long pieces = ((long)vocab + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
+  if ((long)rows * pieces > COHERYN_ARGMAX_STATIC_SLOTS)
+    CO_FAIL("argmax_static: %d rows of %d logits need %ld piece slots; the static scratch holds %d "
+            "(use coheryn_argmax with a caller-provided buffer)", rows, vocab, (long)rows * pieces,
+            COHERYN_ARGMAX_STATIC_SLOTS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+    CO_FAIL("argmax_static: no usable current device (%s)", cudaGetErrorString(e));
+  void* base = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!base) {
+    // Set-up, once per device, with that device current: the symbol's name is a host-side
+    // stand-in, the kernels need the device address.
+    e = cudaGetSymbolAddress(&base, g_argmax_static_scratch);
+    if (e != cudaSuccess || !base) CO_FAIL("argmax_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    __atomic_store_n(&g_static_scratch_ptr[dev], base, __ATOMIC_RELEASE);
+  }
+  float* pv = (float*)base;
+  int* pi = (int*)base + (size_t)rows * pieces;
+  co_launch(argmax_pieces_kernel, dim3((unsigned)pieces, rows), dim3(256), 0, stream, logits, stride, vocab, pv, pi,
+            (int)pieces, status);
+  CO_CHECK_LAUNCH("argmax_static pieces");
+  co_launch(argmax_final_kernel, dim3(rows), dim3(64), 0, stream, (const float*)pv, (const int*)pi, (int)pieces, out);
+  CO_CHECK_LAUNCH("argmax_static final");
+  return 0;
+}
