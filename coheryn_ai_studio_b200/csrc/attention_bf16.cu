@@ -6,16 +6,17 @@
 // (G = heads / kv_heads), so that all G query heads of a group share each key/value tile
 // that is read.  Two kernels:
 //
-//  * attn_tiles:  one CTA per (request, kv head, tile of 64 rows); four warps of 16 rows
-//    share key/value tiles of 32 positions that are copied from the pages into shared
-//    memory with cp.async (double buffered).  Used for prompt portions.
+//  * attn_tiles:  one CTA per (request, kv head, tile of 64 rows); key/value tiles of 64
+//    positions are copied from the pages into shared memory with cp.async (double
+//    buffered); eight warps = four row tiles of 16 x two halves of each key tile, the
+//    halves merged at the end.  Used for prompt portions.
 //  * attn_split:  for requests with at most 16 rows per kv head (decoding).  The key range
 //    is cut into splits of 128 positions at ABSOLUTE multiples of 128; one CTA per
 //    (request, kv head, split), each of its four warps taking tiles of 32 positions.
 //    The warps' (max, sum, accumulator) triples are merged in warp order and written to
 //    scratch; attn_combine merges the splits of a row in ascending order.
 //
-// Tiles start at absolute multiples of 32 and splits at absolute multiples of 128, so a
+// Tiles start at absolute multiples of their size and splits likewise, so a
 // row's result depends only on its own position and window, never on the batch.
 #include <cuda_bf16.h>
 
@@ -183,7 +184,6 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
       }
     }
   }
-
   // Online softmax.  A thread holds, for rows g (i = 0,1) and g+8 (i = 2,3), the key
   // columns key0 + 8 j + 2 t + (i & 1).  The maximum is tracked in the log2 domain of the
   // scaled scores; p = 2^(s * scale_log2 - m) is one fused multiply-add and one ex2.
@@ -274,24 +274,31 @@ __device__ __forceinline__ void load_q_rows(bf16* Qs, const bf16* __restrict__ q
 }
 
 // ------------------------------------------------------------------------------------
-// attn_tiles: 64 query rows per CTA (four warps of 16), key tiles of 32 positions, two
-// stages: about 52 KB of shared memory and at most 128 registers per thread at head size
-// 128, so that four CTAs (16 warps) share an SM and cover each other's latencies.
-constexpr int TMT = 1;
-constexpr int TBN = 32;
-constexpr int BM = 64 * TMT;      // query rows per CTA: four warps of 16 * TMT rows
+// attn_tiles: 64 query rows per CTA and key tiles of 64 positions, eight warps: warp w owns
+// rows 16 * (w & 3) .. + 15 and the key half (w >> 2) of every tile, so two warps share a row
+// tile and meet once at the end (the second half's (max, sum, accumulator) is merged into
+// the first's through shared memory).  Twice the warps per row than a warp-per-row-tile
+// layout, half the steps per warp: the kernel is bound by dependent latencies, not by
+// arithmetic.  Two stages of (K tile, V tile); the copy of a row costs its thread one
+// block-table entry (fetched a tile ahead) and a handful of integer operations.
+#ifndef CO_ATTN_KGROUPS
+#define CO_ATTN_KGROUPS 2
+#endif
+constexpr int KG = CO_ATTN_KGROUPS;   // key groups: warps that share a row tile
+constexpr int TBN = 32;           // key positions per warp and step
+constexpr int TILE = KG * TBN;    // key positions per CTA step
+constexpr int BM = 64;            // query rows per CTA
 
-__global__ void __launch_bounds__(128, HD <= 128 ? 4 : 1)
+__global__ void __launch_bounds__(128 * KG, HD <= 128 ? (KG == 2 ? 2 : 1) : 1)
 attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                   const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window,
                   float scale_log2, int skip_small) {
-  // The query rows stay in shared memory; two stages of (K tile, V tile) follow them.
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][LDS]
-  bf16* stages = Qs + BM * LDS;                                 // [2][2][TBN][LDS]
-  constexpr int STAGE = 2 * TBN * LDS;
+  bf16* stages = Qs + BM * LDS;                                 // [2][K: TILE rows, V: TILE rows][LDS]
+  constexpr int STAGE = 2 * TILE * LDS;
 
   co_pdl_launch_dependents();
   co_pdl_wait();
@@ -303,6 +310,7 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
   if (rt * BM >= rows) return;
   if (skip_small && rows <= 16) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int rw = warp & 3, kg = warp >> 2;
   const int* table = block_tables + (size_t)b * max_blocks;
   const int base_pos = kv_len - q_len;   // position of the request's first token in this step
 
@@ -310,97 +318,140 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
   const int row_first = rt * BM, row_last = min(rows, row_first + BM) - 1;
   const int pos_lo = base_pos + row_first / G, pos_hi = base_pos + row_last / G;
   const int key_first = window > 0 ? max(0, pos_lo - window + 1) : 0;
-  const int tile_first = key_first / TBN, tile_last = pos_hi / TBN;
+  const int tile_first = key_first / TILE, tile_last = pos_hi / TILE;
   const int kv_end = pos_hi + 1;
 
-  // The page ids of a tile are fetched one iteration before its copies are issued, so that
-  // no copy waits on a block-table load.
-  auto issue = [&](int tile, const TilePages& tp) {
-    if (tile <= tile_last) {
-      bf16* st_k = stages + ((tile - tile_first) & 1) * STAGE;
-      load_tile<128, TBN>(st_k, k_cache, tp, kvh, nkv, page_size, tile * TBN, key_first, kv_end, tid);
-      load_tile<128, TBN>(st_k + TBN * LDS, v_cache, tp, kvh, nkv, page_size, tile * TBN, key_first, kv_end, tid);
+  // Copies: thread -> (row tid / 4 of the tile, a quarter of the row's 16-byte pieces).
+  constexpr int TPR = largest_divisor_up_to(CHUNKS, 4);
+  constexpr int PIECES = CHUNKS / TPR;
+  const int c_row = tid >> 2, c_sub = tid & 3;
+  auto page_for = [&](int tile) -> int {     // block-table entry of this thread's row in a tile
+    const int pos = tile * TILE + c_row;
+    return (tile <= tile_last && pos >= key_first && pos < kv_end) ? table[pos / page_size] : -1;
+  };
+  auto issue = [&](int tile, int page) {     // one commit group per call, possibly empty
+    if (tile <= tile_last && c_sub < TPR) {
+      bf16* st = stages + ((tile - tile_first) & 1) * STAGE + c_row * LDS + c_sub * PIECES * 8;
+      const bool valid = page >= 0;
+      const int pos = tile * TILE + c_row;
+      const size_t off = valid ? (((size_t)page * nkv + kvh) * page_size + pos % page_size) * HD + c_sub * PIECES * 8 : 0;
+#pragma unroll
+      for (int c = 0; c < PIECES; ++c) {
+        cp_async16(st + c * 8, k_cache + off + (valid ? c * 8 : 0), valid);
+        cp_async16(st + TILE * LDS + c * 8, v_cache + off + (valid ? c * 8 : 0), valid);
+      }
     }
     cp_async_commit();
   };
-  auto pages = [&](int tile) {
-    return tile <= tile_last ? tile_pages<TBN>(table, page_size, tile * TBN, key_first, kv_end) : TilePages{0, 0, 0};
-  };
-  load_q_rows(Qs, q, q_stride, tok0, kvh, G, row_first, BM, rows, tid, 128);
-  issue(tile_first, pages(tile_first));      // group 0: the query rows and the first tile
-  TilePages tp_next = pages(tile_first + 1);
+  load_q_rows(Qs, q, q_stride, tok0, kvh, G, row_first, BM, rows, tid, 128 * KG);
+  issue(tile_first, page_for(tile_first));   // group 0: the query rows and the first tile
+  int page_next = page_for(tile_first + 1);
 
   // Visible key range of the thread's rows, and of the warp's rows as a whole.
-  int lo[TMT][2], hi[TMT][2];
-  const int w_row_first = row_first + warp * 16 * TMT;
-  const int w_row_last = min(rows - 1, w_row_first + 16 * TMT - 1);
+  int lo[1][2], hi[1][2];
+  const int w_row_first = row_first + rw * 16;
+  const int w_row_last = min(rows - 1, w_row_first + 15);
   const bool w_active = w_row_first < rows;
 #pragma unroll
-  for (int mi = 0; mi < TMT; ++mi)
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = w_row_first + mi * 16 + h * 8 + g;
-      if (r < rows) {
-        hi[mi][h] = base_pos + r / G;
-        lo[mi][h] = window > 0 ? max(0, hi[mi][h] - window + 1) : 0;
-      } else {
-        hi[mi][h] = -1; lo[mi][h] = 0;
-      }
+  for (int h = 0; h < 2; ++h) {
+    const int r = w_row_first + h * 8 + g;
+    if (r < rows) {
+      hi[0][h] = base_pos + r / G;
+      lo[0][h] = window > 0 ? max(0, hi[0][h] - window + 1) : 0;
+    } else {
+      hi[0][h] = -1; lo[0][h] = 0;
     }
+  }
   const int w_hi_max = w_active ? base_pos + w_row_last / G : -1;           // last key any row sees
   const int w_hi_min = w_active ? base_pos + w_row_first / G : -1;          // last key EVERY row sees
   const int w_lo_min = w_active && window > 0 ? max(0, base_pos + w_row_first / G - window + 1) : 0;
   const int w_lo_max = w_active && window > 0 ? max(0, base_pos + w_row_last / G - window + 1) : 0;
-  const bool w_full = w_row_first + 16 * TMT <= rows;                       // no padding rows
+  const bool w_full = w_row_first + 16 <= rows;                             // no padding rows
 
-  float o[TMT][HD / 8][4];
+  float o[1][HD / 8][4];
 #pragma unroll
-  for (int mi = 0; mi < TMT; ++mi)
+  for (int dt = 0; dt < HD / 8; ++dt)
 #pragma unroll
-    for (int dt = 0; dt < HD / 8; ++dt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o[mi][dt][i] = 0.f;
-  RowState st[TMT];
-#pragma unroll
-  for (int mi = 0; mi < TMT; ++mi) {
-    st[mi].m[0] = st[mi].m[1] = -INFINITY;
-    st[mi].l[0] = st[mi].l[1] = 0.f;
-  }
-  const bf16* Qw = Qs + warp * 16 * TMT * LDS;
+    for (int i = 0; i < 4; ++i) o[0][dt][i] = 0.f;
+  RowState st[1];
+  st[0].m[0] = st[0].m[1] = -INFINITY;
+  st[0].l[0] = st[0].l[1] = 0.f;
+  const bf16* Qw = Qs + rw * 16 * LDS;
 
   for (int tile = tile_first; tile <= tile_last; ++tile) {
-    issue(tile + 1, tp_next);     // into the stage that tile - 1 used (all warps are past it)
-    tp_next = pages(tile + 2);
+    issue(tile + 1, page_next);   // into the stage that tile - 1 used (all warps are past it)
+    page_next = page_for(tile + 2);
     cp_async_wait<1>();           // this tile's group has landed; the next one may be in flight
     __syncthreads();
-    const bf16* st_k = stages + ((tile - tile_first) & 1) * STAGE;
-    const int key0 = tile * TBN;
+    const bf16* st_k = stages + ((tile - tile_first) & 1) * STAGE + kg * TBN * LDS;
+    const int key0 = tile * TILE + kg * TBN;
     if (w_active && key0 <= w_hi_max && key0 + TBN > w_lo_min) {
       const bool all_visible = w_full && key0 + TBN - 1 <= w_hi_min && key0 >= w_lo_max;
       if (all_visible)
-        attend_tile<TMT, TBN, true, false>(nullptr, Qw, st_k, st_k + TBN * LDS, o, st, key0, lo, hi, scale_log2);
+        attend_tile<1, TBN, true, false>(nullptr, Qw, st_k, st_k + TILE * LDS, o, st, key0, lo, hi, scale_log2);
       else
-        attend_tile<TMT, TBN, true, true>(nullptr, Qw, st_k, st_k + TBN * LDS, o, st, key0, lo, hi, scale_log2);
+        attend_tile<1, TBN, true, true>(nullptr, Qw, st_k, st_k + TILE * LDS, o, st, key0, lo, hi, scale_log2);
     }
     __syncthreads();
   }
 
+  // The key groups of a row tile meet: groups 1.. write their state, group 0 merges them
+  // in ascending order.
+  float* merge = reinterpret_cast<float*>(stages);              // [KG - 1][4 row warps][16 rows][HD + 2]
+  constexpr int MS = HD + 2;
+  float l2[2];
 #pragma unroll
-  for (int mi = 0; mi < TMT; ++mi)
+  for (int h = 0; h < 2; ++h) {
+    float l = st[0].l[h];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    l2[h] = l;
+  }
+  if (kg >= 1) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const int r = w_row_first + mi * 16 + h * 8 + g;
-      float l = st[mi].l[h];
-      l += __shfl_xor_sync(0xffffffffu, l, 1);
-      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      float* dst = merge + ((size_t)((kg - 1) * 4 + rw) * 16 + h * 8 + g) * MS;
+      if (t == 0) { dst[0] = st[0].m[h]; dst[1] = l2[h]; }
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; ++dt) {
+        dst[2 + dt * 8 + 2 * t] = o[0][dt][2 * h];
+        dst[2 + dt * 8 + 2 * t + 1] = o[0][dt][2 * h + 1];
+      }
+    }
+  }
+  __syncthreads();
+  if (kg == 0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = w_row_first + h * 8 + g;
       if (r >= rows) continue;
-      const float inv = 1.0f / l;
+      float M = st[0].m[h];
+#pragma unroll
+      for (int k = 1; k < KG; ++k) M = fmaxf(M, merge[((size_t)((k - 1) * 4 + rw) * 16 + h * 8 + g) * MS]);
+      float f[KG];                                      // M is finite: a row always sees its own key
+      f[0] = st[0].m[h] == -INFINITY ? 0.f : exp2f(st[0].m[h] - M);
+      float den = l2[h] * f[0];
+#pragma unroll
+      for (int k = 1; k < KG; ++k) {
+        const float* src = merge + ((size_t)((k - 1) * 4 + rw) * 16 + h * 8 + g) * MS;
+        f[k] = src[0] == -INFINITY ? 0.f : exp2f(src[0] - M);
+        den += src[1] * f[k];
+      }
+      const float inv = 1.0f / den;
       bf16* orow = out + (size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * HD;
 #pragma unroll
-      for (int dt = 0; dt < HD / 8; ++dt)
-        *reinterpret_cast<__nv_bfloat162*>(orow + dt * 8 + 2 * t) =
-            __floats2bfloat162_rn(o[mi][dt][2 * h] * inv, o[mi][dt][2 * h + 1] * inv);
+      for (int dt = 0; dt < HD / 8; ++dt) {
+        float a = o[0][dt][2 * h] * f[0], c = o[0][dt][2 * h + 1] * f[0];
+#pragma unroll
+        for (int k = 1; k < KG; ++k) {
+          const float* src = merge + ((size_t)((k - 1) * 4 + rw) * 16 + h * 8 + g) * MS;
+          a += src[2 + dt * 8 + 2 * t] * f[k];
+          c += src[2 + dt * 8 + 2 * t + 1] * f[k];
+        }
+        *reinterpret_cast<__nv_bfloat162*>(orow + dt * 8 + 2 * t) = __floats2bfloat162_rn(a * inv, c * inv);
+      }
     }
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -575,7 +626,8 @@ attn_combine_kernel(const float* __restrict__ scratch, int max_splits, bf16* __r
   }
 }
 
-constexpr size_t TILES_SMEM = (size_t)(BM + 4 * TBN) * LDS * sizeof(bf16);
+constexpr size_t TILES_SMEM = (size_t)(BM + 4 * TILE) * LDS * sizeof(bf16);
+static_assert((size_t)(KG - 1) * 4 * 16 * (HD + 2) * sizeof(float) <= (size_t)4 * TILE * LDS * sizeof(bf16), "the merge area fits the stages");
 constexpr size_t split_smem(int sbn) {
   const size_t tiles = (size_t)(16 + 4 * 2 * sbn) * LDS * sizeof(bf16);
   const size_t merge = (size_t)16 * LDS * sizeof(bf16) + (size_t)4 * 16 * PART * sizeof(float);
@@ -645,7 +697,7 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
       configured = true;
     }
     dim3 grid((max_rows + BM - 1) / BM, nkv, B);
-    co_launch(attn_tiles_kernel, grid, dim3(128), TILES_SMEM, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+    co_launch(attn_tiles_kernel, grid, dim3(128 * KG), TILES_SMEM, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
               (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
               window, scale_log2, split_path ? 1 : 0);
     CO_CHECK_LAUNCH("attn_tiles");
