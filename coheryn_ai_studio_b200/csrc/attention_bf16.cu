@@ -19,6 +19,7 @@
 // Tiles start at absolute multiples of their size and splits likewise, so a
 // row's result depends only on its own position and window, never on the batch.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -143,10 +144,10 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // used for all MT row tiles.
 //   Q fragments: registers (qf) when MT == 1 and QSMEM is false, else read from the warp's
 //   rows in shared memory (Qs, [16 * MT][LDS]).
-//   Ks/Vs: [TB][LDS] tiles; key0: position of the tile's row 0; lo/hi[mi][h]: first and last
+//   Ks/Vs: [TB][KVS] tiles; key0: position of the tile's row 0; lo/hi[mi][h]: first and last
 //   visible key of the thread's rows g (h = 0) and g + 8 (h = 1) of row tile mi.  MASK false
 //   promises that every key of the tile is visible to every row.
-template <int MT, int TB, bool QSMEM, bool MASK>
+template <int MT, int TB, bool QSMEM, bool MASK, int KVS = LDS>
 __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16* Qs, const bf16* Ks, const bf16* Vs,
                                             float (&o)[MT][HD / 8][4], RowState (&st)[MT], int key0,
                                             const int (&lo)[MT][2], const int (&hi)[MT][2], float scale_log2) {
@@ -176,7 +177,7 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
 #pragma unroll
     for (int jp = 0; jp < TB / 16; ++jp) {
       unsigned b[4];
-      ldmatrix_x4(b, Ks + (jp * 16 + (id >> 1) * 8 + r) * LDS + kd * 16 + (id & 1) * 8);
+      ldmatrix_x4(b, Ks + (jp * 16 + (id >> 1) * 8 + r) * KVS + kd * 16 + (id & 1) * 8);
 #pragma unroll
       for (int mi = 0; mi < MT; ++mi) {
         mma_bf16(s[mi][2 * jp], a[mi], b[0], b[1]);
@@ -249,7 +250,7 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
 #pragma unroll
     for (int dp = 0; dp < HD / 16; ++dp) {
       unsigned b[4];
-      ldmatrix_x4_trans(b, Vs + (kt * 16 + (id & 1) * 8 + r) * LDS + dp * 16 + (id >> 1) * 8);
+      ldmatrix_x4_trans(b, Vs + (kt * 16 + (id & 1) * 8 + r) * KVS + dp * 16 + (id >> 1) * 8);
 #pragma unroll
       for (int mi = 0; mi < MT; ++mi) {
         mma_bf16(o[mi][2 * dp], a[mi], b[0], b[1]);
@@ -626,6 +627,167 @@ attn_combine_kernel(const float* __restrict__ scratch, int max_splits, bf16* __r
   }
 }
 
+// ------------------------------------------------------------------------------------
+// attn_split with bulk copies.  Within a page the rows of a kv head are contiguous, so a
+// warp's tile of 32 positions is fetched by a few cp.async.bulk copies (one per page it
+// touches, per tensor) that ONE lane issues and an mbarrier counts in; no lane computes
+// addresses of 16-byte pieces.  The tiles are unpadded in shared memory (ldmatrix then
+// meets bank conflicts, which do not matter here: the kernel waits for memory, not for
+// arithmetic).  One tile per warp, splits of 128 positions, three CTAs per SM.
+// The wait on the mbarrier is bounded; if it runs out, `status` receives 21.
+constexpr int BSBN = 32;
+constexpr int BSPLIT = 4 * BSBN;
+
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(128)
+attn_split_bulk_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__ scratch, int max_splits,
+                       const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                       const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
+                       const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window, float scale_log2,
+                       int* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16* KVs = reinterpret_cast<bf16*>(smem_raw);                // [4 warps][K: BSBN rows, V: BSBN rows][HD]
+  bf16* Qs = KVs + 4 * 2 * BSBN * HD;                           // [16][LDS]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(Qs + 16 * LDS);   // [4]
+  float* merge = reinterpret_cast<float*>(smem_raw);            // reused after the tiles: [4][16][PART]
+
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int b = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
+  const int G = nh / nkv;
+  const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
+  const int rows = q_len * G;
+  if (rows > 16 || rows <= 0) return;
+  const int base_pos = kv_len - q_len;
+  const int pos_hi = kv_len - 1;
+  const int key_first = window > 0 ? max(0, base_pos - window + 1) : 0;
+  const int split = key_first / BSPLIT + sp;      // absolute split index
+  if (split * BSPLIT > pos_hi) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int* table = block_tables + (size_t)b * max_blocks;
+  const int kv_end = pos_hi + 1;
+
+  bf16* Kw = KVs + (size_t)warp * 2 * BSBN * HD;
+  bf16* Vw = Kw + BSBN * HD;
+  const int key0 = split * BSPLIT + warp * BSBN;
+  const int c_lo = max(key0, key_first), c_hi = min(key0 + BSBN, kv_end);   // positions to copy: [c_lo, c_hi)
+  const bool w_active = c_lo < c_hi;
+  load_q_rows(Qs, q, q_stride, tok0, kvh, G, 0, 16, rows, tid, 128);
+  cp_async_commit();
+  if (w_active) {
+    if (lane == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[warp])));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Rows of the tile that are not copied must still be finite for P V: zero them.
+    for (int i = lane; i < BSBN * CHUNKS; i += 32) {
+      const int row = i / CHUNKS;
+      if (key0 + row < c_lo || key0 + row >= c_hi) {
+        *reinterpret_cast<uint4*>(Kw + row * HD + (i % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(Vw + row * HD + (i % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes before the async copies
+    __syncwarp();
+    const TilePages tp = tile_pages<BSBN>(table, page_size, key0, key_first, kv_end);
+    if (lane == 0) {
+      const unsigned bytes = (unsigned)(c_hi - c_lo) * HD * 2 * 2;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(&bars[warp])), "r"(bytes) : "memory");
+    }
+    for (int pos = c_lo; pos < c_hi;) {
+      const int block = pos / page_size;
+      const int n = min(c_hi, (block + 1) * page_size) - pos;
+      const int page = page_of(tp, block);                      // a shuffle: every lane takes part
+      if (lane == 0) {
+        const size_t off = (((size_t)page * nkv + kvh) * page_size + (pos - block * page_size)) * HD;
+        bulk_copy(Kw + (pos - key0) * HD, k_cache + off, (unsigned)n * HD * 2, &bars[warp]);
+        bulk_copy(Vw + (pos - key0) * HD, v_cache + off, (unsigned)n * HD * 2, &bars[warp]);
+      }
+      pos += n;
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();              // the query rows are visible to every warp
+
+  int lo[1][2], hi[1][2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = h * 8 + g;
+    if (r < rows) {
+      hi[0][h] = base_pos + r / G;
+      lo[0][h] = window > 0 ? max(0, hi[0][h] - window + 1) : 0;
+    } else {
+      hi[0][h] = -1; lo[0][h] = 0;
+    }
+  }
+  float o[1][HD / 8][4];
+#pragma unroll
+  for (int dt = 0; dt < HD / 8; ++dt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[0][dt][i] = 0.f;
+  RowState st[1];
+  st[0].m[0] = st[0].m[1] = -INFINITY;
+  st[0].l[0] = st[0].l[1] = 0.f;
+  if (w_active) {
+    bool landed = false;
+    for (unsigned i = 0; i < (1u << 24) && !landed; ++i) {
+      unsigned done;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(done) : "r"(smem_addr(&bars[warp])) : "memory");
+      landed = done != 0;
+    }
+    if (landed) attend_tile<1, BSBN, true, true, HD>(nullptr, Qs, Kw, Vw, o, st, key0, lo, hi, scale_log2);
+    else if (lane == 0) atomicExch(status, 21);
+  }
+  __syncthreads();   // all warps are done with their tiles: the buffer becomes the merge area
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = h * 8 + g;
+    float l = st[0].l[h];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    float* dst = merge + ((size_t)warp * 16 + r) * PART;
+    if (t == 0) { dst[0] = st[0].m[h]; dst[1] = l; }
+#pragma unroll
+    for (int dt = 0; dt < HD / 8; ++dt) {
+      dst[2 + dt * 8 + 2 * t] = o[0][dt][2 * h];
+      dst[2 + dt * 8 + 2 * t + 1] = o[0][dt][2 * h + 1];
+    }
+  }
+  __syncthreads();
+  // Merge the four warps in warp order; write the valid rows.
+  float* dst_base = scratch + (((size_t)b * nkv + kvh) * max_splits + sp) * 16 * PART;
+  for (int e = tid; e < rows * (HD + 1); e += 128) {
+    const int r = e / (HD + 1), c = e % (HD + 1);   // c == HD: the (max, sum) pair
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, merge[(w * 16 + r) * PART]);
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = merge[(w * 16 + r) * PART];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      acc += f * (c == HD ? merge[(w * 16 + r) * PART + 1] : merge[(w * 16 + r) * PART + 2 + c]);
+    }
+    if (c == HD) { dst_base[r * PART] = M; dst_base[r * PART + 1] = acc; }
+    else dst_base[r * PART + 2 + c] = acc;
+  }
+}
+
+constexpr size_t bulk_smem() {
+  const size_t tiles = (size_t)4 * 2 * BSBN * HD * sizeof(bf16) + (size_t)16 * LDS * sizeof(bf16) + 4 * sizeof(unsigned long long);
+  const size_t merge = (size_t)4 * 16 * PART * sizeof(float);
+  return (tiles > merge ? tiles : merge) + 128;
+}
+
 constexpr size_t TILES_SMEM = (size_t)(BM + 4 * TILE) * LDS * sizeof(bf16);
 static_assert((size_t)(KG - 1) * 4 * 16 * (HD + 2) * sizeof(float) <= (size_t)4 * TILE * LDS * sizeof(bf16), "the merge area fits the stages");
 constexpr size_t split_smem(int sbn) {
@@ -658,6 +820,39 @@ int launch_split(const void* q, long q_stride, void* out, long out_stride, const
   CO_CHECK_LAUNCH("attn_combine");
   return 0;
 }
+int launch_split_bulk(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                      const void* v_cache, const int* block_tables, int max_blocks, const int* cu_q,
+                      const int* kv_lens, int B, int nh, int nkv, int page_size, int window, float scale_log2,
+                      int max_kv_len, float* scratch, long scratch_floats, int* status, cudaStream_t stream) {
+  constexpr size_t SMEM = bulk_smem();
+  const int max_splits = (max_kv_len + BSPLIT - 1) / BSPLIT + 1;
+  if (!scratch || scratch_floats < (long)B * nkv * max_splits * 16 * PART)
+    CO_FAIL("attention_bf16: scratch of %ld floats is too small", scratch_floats);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_split_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  co_launch(attn_split_bulk_kernel, dim3(max_splits, nkv, B), dim3(128), SMEM, stream, (const bf16*)q, q_stride, scratch,
+            max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv,
+            page_size, window, scale_log2, status);
+  CO_CHECK_LAUNCH("attn_split_bulk");
+  co_launch(attn_combine_kernel<BSPLIT>, dim3(16, nkv, B), dim3(HD >= 128 ? 128 : 64), 0, stream, (const float*)scratch,
+            max_splits, (bf16*)out, out_stride, cu_q, kv_lens, nh, nkv, window);
+  CO_CHECK_LAUNCH("attn_combine");
+  return 0;
+}
+
+// Which decode kernel runs: COHERYN_ATTN_SPLIT = auto | wide | narrow | bulk (experiments).
+int split_choice() {
+  static int choice = -1;
+  if (choice < 0) {
+    const char* e = getenv("COHERYN_ATTN_SPLIT");
+    choice = !e ? 0 : (e[0] == 'w' ? 1 : (e[0] == 'n' ? 2 : (e[0] == 'b' ? 3 : 0)));
+  }
+  return choice;
+}
 }  // namespace
 
 CO_EXPORT int coheryn_attn_head_dim() { return HD; }
@@ -677,7 +872,7 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
                                      const void* v_cache, const int* block_tables, int max_blocks, const int* cu_q,
                                      const int* kv_lens, int B, int nh, int nkv, int page_size, int window,
                                      float scale, int max_rows, int any_small, int any_large, int max_kv_len,
-                                     float* scratch, long scratch_floats, cudaStream_t stream) {
+                                     float* scratch, long scratch_floats, int* status, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nkv <= 0 || nh % nkv) CO_FAIL("attention_bf16: %d heads do not group over %d kv heads", nh, nkv);
   if ((q_stride & 7) || (out_stride & 1)) CO_FAIL("attention_bf16: row strides must keep 16-byte alignment");
@@ -705,12 +900,20 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
   if (split_path) {
     // All CTAs of the wide shape resident at once (one per SM, with a little queueing)?
     const long wide_ctas = (long)B * nkv * ((max_kv_len + 255) / 256 + 1);
-    if (wide_ctas <= 2 * 148 && split_smem(64) <= 227 * 1024)
+    const int choice = split_choice();
+    // Measured on a B200 inside whole decode steps (cold cache): the wide shape wins while its
+    // grid fits the GPU about twice over, the narrow one beyond.
+    const bool wide = choice == 1 || (choice == 0 && wide_ctas <= 2 * 148);
+    if (wide && split_smem(64) <= 227 * 1024)
       return launch_split<64, 256>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q,
                                    kv_lens, B, nh, nkv, page_size, window, scale_log2, max_kv_len, scratch,
                                    scratch_floats, stream);
-    return launch_split<32, 128>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens,
-                                 B, nh, nkv, page_size, window, scale_log2, max_kv_len, scratch, scratch_floats, stream);
+    if (choice != 3 || !status)   // measured: the bulk-copy shape is no faster than the cp.async one
+      return launch_split<32, 128>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q,
+                                   kv_lens, B, nh, nkv, page_size, window, scale_log2, max_kv_len, scratch,
+                                   scratch_floats, stream);
+    return launch_split_bulk(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B,
+                             nh, nkv, page_size, window, scale_log2, max_kv_len, scratch, scratch_floats, status, stream);
   }
   return 0;
 }

@@ -280,7 +280,8 @@ def check_tc_status(device) -> None:
     code = int(tc_status(device).item())
     if code:
         tc_status(device).zero_()
-        raise KernelError(f"gemm_bf16_tc gave up waiting (code {code}: 11 producer, 12 MMA issuer, 13 epilogue)")
+        raise KernelError(f"a kernel gave up a bounded wait (code {code}: gemm_bf16_tc 11 producer, 12 MMA issuer, "
+                          "13 epilogue; 21 attention bulk copy)")
 
 
 def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
@@ -413,7 +414,7 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
         _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_q), _ptr(kv_lens), c_int(B),
         c_int(num_heads), c_int(num_kv_heads), c_int(page_size), c_int(window or 0), c_float(scale),
         c_int(max(rows)), c_int(1 if any_small else 0), c_int(1 if any_large else 0), c_int(max_kv_len),
-        _ptr(scratch), c_long(floats), _stream()))
+        _ptr(scratch), c_long(floats), _ptr(tc_status(q.device)), _stream()))
 
 
 def gated_silu_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
