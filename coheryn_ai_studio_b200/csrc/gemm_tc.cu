@@ -101,14 +101,14 @@ struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + BN * 4 /* bias */;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 2 * BN * 4 /* bias */;
 };
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype, int M, int N,
-               int K, long ldo, int epilogue, int* __restrict__ status) {
+               int K, long ldo, int epilogue, int* __restrict__ status, float* __restrict__ partial, int k_per_split) {
   using S = Smem<BN, STAGES>;
   extern __shared__ unsigned char smem_raw[];
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
@@ -121,7 +121,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int k_tiles = (K + BK - 1) / BK;
+  // Split K: CTA z of the grid sums the k-steps [kt_begin, kt_begin + k_tiles) and leaves its raw
+  // float32 tile in partial[z]; splitk_reduce_kernel adds the splits in order and finishes.
+  const int kt_begin = partial ? blockIdx.z * k_per_split : 0;
+  const int k_tiles = partial ? min(k_per_split, (K + BK - 1) / BK - kt_begin) : (K + BK - 1) / BK;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;     // a power of two >= 32
 
   if (threadIdx.x == 0) {
@@ -147,8 +150,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) { atomicExch(status, 11); break; }
         unsigned char* a = tiles + s * S::STAGE_BYTES;
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
-        tma_load_2d(a, &map_x, kt * BK, m0, &full[s]);
-        tma_load_2d(a + S::A_BYTES, &map_w, kt * BK, n0, &full[s]);
+        tma_load_2d(a, &map_x, (kt_begin + kt) * BK, m0, &full[s]);
+        tma_load_2d(a + S::A_BYTES, &map_w, (kt_begin + kt) * BK, n0, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -186,6 +189,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         unsigned r[32];
         tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
         if (row >= M) continue;
+        if (partial) {
+          float* p = partial + ((size_t)blockIdx.z * M + row) * N + n0 + c0;
+          if (n0 + c0 + 32 <= N && (((uintptr_t)p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ((uint4*)p)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          } else {
+            for (int j = 0; j < 32 && n0 + c0 + j < N; ++j) p[j] = __uint_as_float(r[j]);
+          }
+          continue;
+        }
         if (epilogue == EPI_GATED_SILU) {
           // columns (2j, 2j+1) = (gate_j, up_j): 16 outputs per 32 columns
           const int oc = (n0 + c0) >> 1;
@@ -255,6 +268,230 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   }
 }
 
+// One 32-column piece of an accumulator row: bias or gate, conversion, store.
+__device__ __forceinline__ void store_piece(const unsigned (&r)[32], int row, int nc, const float* bias_piece,
+                                            void* __restrict__ out, int out_dtype, int N, long ldo, int epilogue) {
+  if (epilogue == EPI_GATED_SILU) {
+    // columns (2j, 2j+1) = (gate_j, up_j): 16 outputs per 32 columns
+    const int oc = nc >> 1, n_out = N >> 1;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
+      v[j] = __fdividef(g, 1.0f + __expf(-g)) * u;
+    }
+    if (out_dtype == CO_BF16) {
+      __nv_bfloat16* p = (__nv_bfloat16*)out + (size_t)row * ldo + oc;
+      if (oc + 16 <= n_out && (((uintptr_t)p) & 15) == 0) {
+        uint4 q[2];
+        __nv_bfloat162* h = (__nv_bfloat162*)q;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        ((uint4*)p)[0] = q[0]; ((uint4*)p)[1] = q[1];
+      } else {
+        for (int j = 0; j < 16 && oc + j < n_out; ++j) p[j] = __float2bfloat16_rn(v[j]);
+      }
+    } else {
+      float* p = (float*)out + (size_t)row * ldo + oc;
+      for (int j = 0; j < 16 && oc + j < n_out; ++j) p[j] = v[j];
+    }
+    return;
+  }
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (bias_piece) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += bias_piece[j];
+  }
+  if (out_dtype == CO_BF16) {
+    __nv_bfloat16* p = (__nv_bfloat16*)out + (size_t)row * ldo + nc;
+    if (nc + 32 <= N && (((uintptr_t)p) & 15) == 0) {
+      uint4 q[4];
+      __nv_bfloat162* h = (__nv_bfloat162*)q;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ((uint4*)p)[j] = q[j];
+    } else {
+      for (int j = 0; j < 32 && nc + j < N; ++j) p[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* p = (float*)out + (size_t)row * ldo + nc;
+    if (nc + 32 <= N && (((uintptr_t)p) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ((float4*)p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      for (int j = 0; j < 32 && nc + j < N; ++j) p[j] = v[j];
+    }
+  }
+}
+
+// Adds the float32 tiles of the K splits in ascending order and applies the epilogue.  One
+// thread per pair of neighbouring columns (a gate/up pair in the gated case).
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                                     const void* __restrict__ bias, int bias_dtype, void* __restrict__ out,
+                                     int out_dtype, long ldo, int epilogue) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const long pairs_per_row = (N + 1) / 2;
+  const long total = (long)M * pairs_per_row;
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+    const long m = e / pairs_per_row;
+    const int n = (int)(e % pairs_per_row) * 2;
+    const bool has1 = n + 1 < N;
+    float v0 = 0.f, v1 = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float* p = partial + ((size_t)z * M + m) * N + n;
+      v0 += p[0];
+      if (has1) v1 += p[1];
+    }
+    if (epilogue == EPI_GATED_SILU) {
+      const float r = __fdividef(v0, 1.0f + __expf(-v0)) * v1;
+      const size_t o = (size_t)m * ldo + (n >> 1);
+      if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
+      else ((float*)out)[o] = r;
+      continue;
+    }
+    if (bias) {
+      v0 += co_load_any(bias, bias_dtype, n);
+      if (has1) v1 += co_load_any(bias, bias_dtype, n + 1);
+    }
+    const size_t o = (size_t)m * ldo + n;
+    if (out_dtype == CO_BF16) {
+      ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v0);
+      if (has1) ((__nv_bfloat16*)out)[o + 1] = __float2bfloat16_rn(v1);
+    } else {
+      ((float*)out)[o] = v0;
+      if (has1) ((float*)out)[o + 1] = v1;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Persistent variant for products of many tiles: one CTA per SM walks the tiles
+// t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles fastest, so the CTAs that run at the
+// same time share W tiles through L2).  Two accumulators in tensor memory (2 x BN columns)
+// let the epilogue of one tile run while the MMAs of the next are issued; the shared-memory
+// stages and their barriers simply keep cycling across tiles.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                          const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype,
+                          int M, int N, int K, long ldo, int epilogue, int* __restrict__ status) {
+  using S = Smem<BN, STAGES>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned long long* full = (unsigned long long*)(tiles + STAGES * S::STAGE_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* acc_full = empty + STAGES;      // [2]
+  unsigned long long* acc_empty = acc_full + 2;       // [2]
+  unsigned* tmem_slot = (unsigned*)(acc_empty + 2);
+  float* bias_s = (float*)(tiles + STAGES * S::STAGE_BYTES + 256);   // [2][BN]
+  static_assert(2 * STAGES * 8 + 4 * 8 + 4 <= 256, "barriers fit their slot");
+  static_assert(2 * BN <= 512, "two accumulators fit tensor memory");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_tiles = (K + BK - 1) / BK;
+  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      long it = 0;   // k-steps issued so far, across tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = (int)(it % STAGES);
+          if (it >= STAGES && !mbar_wait(&empty[s], (unsigned)((it / STAGES) - 1) & 1)) { atomicExch(status, 11); ok = false; break; }
+          unsigned char* a = tiles + s * S::STAGE_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          tma_load_2d(a, &map_x, kt * BK, m0, &full[s]);
+          tma_load_2d(a + S::A_BYTES, &map_w, kt * BK, n0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr unsigned idesc = umma_idesc(BM, BN);
+      long it = 0;
+      int j = 0;     // tiles done by this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++j) {
+        const int acc = j & 1;
+        if (j >= 2 && !mbar_wait(&acc_empty[acc], (unsigned)((j >> 1) - 1) & 1)) { atomicExch(status, 14); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned d = tmem_base + (unsigned)(acc * BN);
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = (int)(it % STAGES);
+          if (!mbar_wait(&full[s], (unsigned)(it / STAGES) & 1)) { atomicExch(status, 12); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned char* a = tiles + s * S::STAGE_BYTES;
+          const unsigned long long da = umma_desc(a), db = umma_desc(a + S::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int j = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
+      const int acc = j & 1;
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int row = m0 + quarter * 32 + lane;
+      float* bias_t = bias_s + acc * BN;
+      if (bias) {
+        for (int i = threadIdx.x - 64; i < BN; i += 128) bias_t[i] = n0 + i < N ? co_load_any(bias, bias_dtype, n0 + i) : 0.f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (!mbar_wait(&acc_full[acc], (unsigned)(j >> 1) & 1)) {
+        if (lane == 0) atomicExch(status, 13);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        unsigned r[32];
+        tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), r);
+        if (row < M) store_piece(r, row, n0 + c0, bias ? bias_t + c0 : nullptr, out, out_dtype, N, ldo, epilogue);
+      }
+      // This warp has read its quarter of the accumulator: hand it back to the MMA issuer.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -287,7 +524,8 @@ bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, in
 
 template <int BN, int STAGES>
 int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, int bias_dtype, void* out,
-              int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status, cudaStream_t stream) {
+              int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status, cudaStream_t stream,
+              float* partial = nullptr, int splits = 1) {
   auto kernel = gemm_tc_kernel<BN, STAGES>;
   constexpr int smem = Smem<BN, STAGES>::TOTAL;
   static bool configured = false;
@@ -296,11 +534,45 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
     if (e != cudaSuccess) CO_FAIL("gemm_tc: %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  const int k_tiles = (K + BK - 1) / BK;
+  const int k_per_split = partial ? (k_tiles + splits - 1) / splits : k_tiles;
+  const int used = partial ? (k_tiles + k_per_split - 1) / k_per_split : 1;    // no split is left empty
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, used);
   cudaError_t le = co_launch(kernel, grid, dim3(192), (size_t)smem, stream, mx, mw, bias, bias_dtype, out, out_dtype, M, N,
-                             K, ldo, epilogue, status);
+                             K, ldo, epilogue, status, used > 1 ? partial : (float*)nullptr, k_per_split);
   if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("gemm_tc");
+  if (used > 1) {
+    const long pairs = (long)M * ((N + 1) / 2);
+    const int blocks = (int)((pairs + 255) / 256 < 148 * 8 ? (pairs + 255) / 256 : 148 * 8);
+    le = co_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)partial, used, M, N, bias,
+                   bias_dtype, out, out_dtype, ldo, epilogue);
+    if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
+    CO_CHECK_LAUNCH("splitk_reduce");
+  }
+  return 0;
+}
+template <int BN, int STAGES>
+int launch_tc_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, int bias_dtype, void* out,
+                         int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status,
+                         cudaStream_t stream) {
+  auto kernel = gemm_tc_persistent_kernel<BN, STAGES>;
+  constexpr int smem = Smem<BN, STAGES>::TOTAL;
+  static int sms = 0;
+  if (!sms) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) CO_FAIL("gemm_tc: %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const long tiles = (long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  cudaError_t le = co_launch(kernel, dim3(grid), dim3(192), (size_t)smem, stream, mx, mw, bias, bias_dtype, out,
+                             out_dtype, M, N, K, ldo, epilogue, status);
+  if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
+  CO_CHECK_LAUNCH("gemm_tc_persistent");
   return 0;
 }
 }  // namespace
@@ -310,28 +582,57 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
 static int g_bn = 0, g_stages = 0;
 CO_EXPORT void coheryn_gemm_tc_tune(int bn, int stages) { g_bn = bn; g_stages = stages; }
 
+// Tile width by shape: 256 columns where the output is wide; with a single row tile (a decode
+// batch, a short portion) narrower tiles put more CTAs on the weight stream.
+static int tile_width(int M, int N) {
+  int bn = N >= 192 ? 256 : (N >= 96 ? 128 : (N >= 48 ? 64 : 32));
+  const long tiles_m = (M + BM - 1) / BM;
+  while (tiles_m == 1 && bn > 128 && (N + bn - 1) / bn < 74) bn >>= 1;
+  if (g_bn == 128 && bn > 128) bn = 128;
+  return bn;
+}
+// K splits for outputs of too few tiles to occupy the GPU (1 = none).
+static int splits_for(int M, int N, int K, int bn) {
+  const long tiles = (long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  const int k_tiles = (K + BK - 1) / BK;
+  if (tiles >= 74 || k_tiles < 8) return 1;
+  int s = (int)(148 / tiles);
+  if (s > 8) s = 8;
+  if (s > k_tiles / 4) s = k_tiles / 4;     // at least four k-steps per split
+  return s < 2 ? 1 : s;
+}
+
+// Floats of workspace with which coheryn_gemm_bf16_tc splits K over several CTAs (0: this
+// shape is not split).  Without the workspace the product runs unsplit.
+CO_EXPORT long coheryn_gemm_tc_workspace_floats(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int s = splits_for(M, N, K, tile_width(M, N));
+  return s > 1 ? (long)s * M * N : 0;
+}
+
 // x: [M, K] bfloat16 with row stride ldx; w: [N, K] bfloat16 contiguous; K and ldx multiples
 // of 8, bases 16-byte aligned.  epilogue 0: out[M, N] (+ bias); 1: gated SiLU over
 // interleaved rows of w, out[M, N/2].  status: device word that receives 11/12/13 if a
-// bounded wait of the producer / the MMA issuer / the epilogue ran out.
+// bounded wait of the producer / the MMA issuer / the epilogue ran out (14: the issuer waiting
+// for a free accumulator in the persistent variant).  workspace: see above, may be null.
 CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
                                    int out_dtype, int M, int N, int K, long ldx, long ldo, int epilogue,
-                                   int* status, cudaStream_t stream) {
+                                   int* status, float* workspace, long workspace_floats, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc: operands must be 16-byte aligned");
   if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc: gated epilogue needs an even number of rows");
   if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
-  int bn = N >= 192 ? 256 : (N >= 96 ? 128 : (N >= 48 ? 64 : 32));
-  // Few row tiles (a decode batch, a short portion): narrower tiles put more CTAs on the
-  // weight stream.
+  const int bn = tile_width(M, N);
   const long tiles_m = (M + BM - 1) / BM;
-  while (tiles_m == 1 && bn > 64 && (N + bn - 1) / bn < 120) bn >>= 1;
-  if (g_bn == 128 && bn > 128) bn = 128;
+  int splits = splits_for(M, N, K, bn);
+  if (splits > 1 && (!workspace || workspace_floats < (long)splits * M * N)) splits = 1;
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, K, bn))
     CO_FAIL("gemm_bf16_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%ld)", M, N, K, ldx);
-#define GO(BN_, ST_) return launch_tc<BN_, ST_>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, stream)
+#define GO(BN_, ST_) return launch_tc<BN_, ST_>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, stream, workspace, splits)
+  if (bn == 256 && g_stages != 1 && tiles_m * ((N + 255) / 256) > 148)
+    return launch_tc_persistent<256, 4>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, stream);
   if (bn == 256 && g_stages == 2) GO(256, 2);
   if (bn == 256 && g_stages == 3) GO(256, 3);
   if (bn == 128 && g_stages == 3) GO(128, 3);

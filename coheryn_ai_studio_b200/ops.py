@@ -292,10 +292,13 @@ def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == K
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N // 2 if gated else N)
     lib = core()
+    lib.coheryn_gemm_tc_workspace_floats.restype = ctypes.c_long
+    floats = int(lib.coheryn_gemm_tc_workspace_floats(c_int(M), c_int(N), c_int(K)))   # > 0: K is split
+    workspace = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
     _check(lib, lib.coheryn_gemm_bf16_tc(
         _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
         c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)),
-        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _stream()))
+        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _ptr(workspace), c_long(floats), _stream()))
 
 
 def _tc_ok(x, w) -> bool:
