@@ -10,14 +10,16 @@
 //    positions are copied from the pages into shared memory with cp.async (double
 //    buffered); eight warps = four row tiles of 16 x two halves of each key tile, the
 //    halves merged at the end.  Used for prompt portions.
-//  * attn_split:  for requests with at most 16 rows per kv head (decoding).  The key range
-//    is cut into splits of 128 positions at ABSOLUTE multiples of 128; one CTA per
-//    (request, kv head, split), each of its four warps taking tiles of 32 positions.
-//    The warps' (max, sum, accumulator) triples are merged in warp order and written to
-//    scratch; attn_combine merges the splits of a row in ascending order.
+//  * attn_stream: for requests with at most 16 rows per kv head (decoding).  The key range
+//    is cut into splits of 128, 256 or 512 positions at ABSOLUTE multiples of the split; one
+//    CTA per (request, kv head, split) streams its positions through a three-stage ring of
+//    64-position tiles, each of its four warps taking 16 positions of every tile.  The warps'
+//    (max, sum, accumulator) triples are merged in warp order and written to scratch;
+//    attn_combine merges the splits of a row.
 //
-// Tiles start at absolute multiples of their size and splits likewise, so a
-// row's result depends only on its own position and window, never on the batch.
+// Tiles start at absolute multiples of their size and splits likewise.  The split size is
+// chosen from the batch's size, so a row's result may differ between batches by rounding
+// (another order of merging), never by more.
 #include <cuda_bf16.h>
 #include <stdlib.h>
 
@@ -30,7 +32,8 @@
 namespace {
 constexpr int HD = CO_HEAD_DIM;
 constexpr int LDS = HD + 8;       // shared-memory row stride: 16 bytes of padding keep ldmatrix conflict-free
-constexpr int SPLIT_MIN = 128;    // the smaller of the two split sizes of attn_split
+constexpr int SPLIT_MIN = 128;    // positions per CTA of attn_stream: one of 128, 256, 512
+constexpr int SPLIT_MAX = 512;
 constexpr int CHUNKS = HD / 8;    // 16-byte pieces per row
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
 
@@ -456,62 +459,128 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
 }
 
 // ------------------------------------------------------------------------------------
-// Scratch layout per (request, kv head, split): 16 rows x (HD + 2) floats:
-// [0] = max (log2 domain), [1] = sum, [2..] = unnormalised accumulator.
+// Scratch per (request, kv head, split): 16 x HD floats of unnormalised accumulators (row r at
+// r * HD, 16-byte aligned), then 16 pairs (max in the log2 domain, sum).  In shared memory the
+// warps' triples are laid out as rows of PART floats: [0] = max, [1] = sum, [2..] = accumulator.
 constexpr int PART = HD + 2;
+constexpr int SPLIT_FLOATS = 16 * HD + 32;
 
-// Key positions per warp step in attn_split: a warp owns one buffer of SBN keys and SBN
-// values and walks its share of the split (positions w*SBN, (w+4)*SBN, ... of the split)
-// through it.  About 74 KB per CTA at head size 128: three CTAs, twelve warps per SM,
-// each with its own copies in flight.
+// attn_stream: decoding is bound by reading each key and value once, so the kernel is a
+// copy pipeline with a little arithmetic attached.  A CTA owns `split` consecutive
+// positions (a multiple of 64, at absolute multiples of `split`) of one (request, kv head)
+// and streams them through a ring of SSTAGES tiles of 64 positions, keys and values, with
+// cp.async: while the warps work on tile i, the next SSTAGES-1 tiles are in flight.  Warp w
+// takes positions 16 w .. 16 w + 15 of every tile for the request's <= 16 rows, keeps its
+// own running (max, sum, accumulator), and the four warps merge once at the end in warp
+// order.  About 110 KB of shared memory at head size 128: two CTAs per SM, so one CTA's
+// prologue and merge hide behind the other's stream.
 //
-// Two shapes are built: <64, 256> (one CTA per SM, eight tiles of 64 in flight: best when
-// the whole grid fits the GPU at once) and <32, 128> (three CTAs per SM: best when CTAs
-// queue up).  Which one runs depends only on the batch's size, and a row's result depends
-// on the shape (rounding), so a request may see either across steps.
-template <int SBN, int SPLIT>
+// What the step's earlier kernels do not write is fetched BEFORE the kernel waits for its
+// predecessor (programmatic dependent launch): the lengths and block tables (inputs of the
+// step) and every tile whose positions all precede the request's new tokens (written by
+// earlier steps; the predecessor writes only the new tokens' slots).  With a split of 128
+// positions the whole split is in flight while the q/k/v projection still runs; after the
+// wait only the queries and the tile with the new tokens are read.
+//
+// A tile's copies are planned one iteration ahead: threads 0..63 turn the tile's positions
+// into element offsets (one division and one block-table entry from shared memory per row),
+// and the copy loop then moves consecutive 16-byte pieces with consecutive lanes, so a warp
+// instruction covers whole 128-byte lines.
+constexpr int STILE = 64;
+#ifndef CO_ATTN_STREAM_STAGES
+#define CO_ATTN_STREAM_STAGES 3
+#endif
+constexpr int SSTAGES = CO_ATTN_STREAM_STAGES;
+constexpr size_t STREAM_SMEM = (size_t)(16 + SSTAGES * 2 * STILE) * LDS * sizeof(bf16);
+static_assert(SSTAGES >= 2, "tile i is worked on while tile i + 1 is copied");
+static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)SSTAGES * 2 * STILE * LDS * sizeof(bf16),
+              "the merge area fits the ring");
+static_assert(STREAM_SMEM + 6 * 1024 <= 227 * 1024, "the ring fits shared memory at every head size");
+
 __global__ void __launch_bounds__(128)
-attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__ scratch, int max_splits,
-                  const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                  const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
-                  const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window, float scale_log2) {
-  constexpr int SPLIT_TILES = SPLIT / (4 * SBN);   // tiles per warp
+attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__ scratch, int max_splits,
+                   const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
+                   const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window, float scale_log2,
+                   int split) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ long long rowoff[SSTAGES][STILE];   // element offset of a tile's rows in a cache tensor, -1: not read
+  __shared__ int pages_s[SPLIT_MAX + 2];         // block-table entries of the split's pages
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][LDS]
-  bf16* KVs = Qs + 16 * LDS;                                   // [4 warps][2][SBN][LDS]
-  float* merge = reinterpret_cast<float*>(KVs);                // reused after the tiles: [4][16][PART]
+  bf16* ring = Qs + 16 * LDS;                                   // [SSTAGES][K, V][STILE][LDS]
+  float* merge = reinterpret_cast<float*>(ring);               // reused after the tiles: [4][16][PART]
 
   co_pdl_launch_dependents();
-  co_pdl_wait();
+  // Inputs of the step: written before its first kernel started.
   const int b = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
   const int G = nh / nkv;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
   const int rows = q_len * G;
   if (rows > 16 || rows <= 0) return;
-  const int base_pos = kv_len - q_len;
+  const int base_pos = kv_len - q_len;   // the first new position: everything before it is an earlier step's
   const int pos_hi = kv_len - 1;
   const int key_first = window > 0 ? max(0, base_pos - window + 1) : 0;
-  const int split = key_first / SPLIT + sp;      // absolute split index
-  if (split * SPLIT > pos_hi) return;
+  const int c0 = (key_first / split + sp) * split;   // the split's first position
+  if (c0 > pos_hi) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int* table = block_tables + (size_t)b * max_blocks;
-  const int kv_end = pos_hi + 1;
-
-  bf16* Kw = KVs + (size_t)warp * 2 * SBN * LDS;
-  bf16* Vw = Kw + SBN * LDS;
-  auto tile_key0 = [&](int i) { return split * SPLIT + (i * 4 + warp) * SBN; };
-  // The warp's first tile that reaches into the visible range (a window hides earlier ones).
-  int i0 = 0;
-  while (i0 < SPLIT_TILES && tile_key0(i0) + SBN <= key_first) ++i0;
-  load_q_rows(Qs, q, q_stride, tok0, kvh, G, 0, 16, rows, tid, 128);
-  if (i0 < SPLIT_TILES && tile_key0(i0) <= pos_hi) {
-    const TilePages tp = tile_pages<SBN>(table, page_size, tile_key0(i0), key_first, kv_end);
-    load_tile<32, SBN>(Kw, k_cache, tp, kvh, nkv, page_size, tile_key0(i0), key_first, kv_end, lane);
-    load_tile<32, SBN>(Vw, v_cache, tp, kvh, nkv, page_size, tile_key0(i0), key_first, kv_end, lane);
-  }
-  cp_async_commit();
-  cp_async_wait<0>();
+  const int lo_key = max(c0, key_first), hi_key = min(c0 + split, pos_hi + 1);   // positions [lo_key, hi_key) are read
+  const int t_first = (lo_key - c0) / STILE;                  // a window hides earlier tiles
+  const int t_end = (hi_key - c0 + STILE - 1) / STILE;        // tiles [t_first, t_end)
+  const int blk0 = lo_key / page_size;
+  for (int j = tid; j <= (hi_key - 1) / page_size - blk0; j += 128) pages_s[j] = table[blk0 + j];
   __syncthreads();
+
+  auto stage_of = [&](int i) { return ring + (size_t)((i - t_first) % SSTAGES) * 2 * STILE * LDS; };
+  auto plan = [&](int i) {
+    if (tid < STILE && i < t_end) {
+      const int pos = c0 + i * STILE + tid;
+      long long off = -1;
+      if (pos >= lo_key && pos < hi_key) {
+        const int blk = pos / page_size;
+        off = (((long long)pages_s[blk - blk0] * nkv + kvh) * page_size + (pos - blk * page_size)) * HD;
+      }
+      rowoff[(i - t_first) % SSTAGES][tid] = off;
+    }
+  };
+  auto issue = [&](int i) {   // one group per call, with or without copies
+    if (i < t_end) {
+      bf16* Ks = stage_of(i);
+      const long long* ro = rowoff[(i - t_first) % SSTAGES];
+#pragma unroll
+      for (int c = tid; c < STILE * CHUNKS; c += 128) {
+        const int row = c / CHUNKS, piece = c % CHUNKS;
+        const long long off = ro[row];
+        const bool valid = off >= 0;
+        const size_t src = valid ? (size_t)off + piece * 8 : 0;
+        cp_async16(Ks + row * LDS + piece * 8, k_cache + src, valid);
+        cp_async16(Ks + (STILE + row) * LDS + piece * 8, v_cache + src, valid);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < SSTAGES; ++s) plan(t_first + s);
+  __syncthreads();
+  int issued = 0;
+  while (issued < SSTAGES && (t_first + issued >= t_end || c0 + (t_first + issued + 1) * STILE <= base_pos)) {
+    issue(t_first + issued);
+    ++issued;
+  }
+  co_pdl_wait();   // the queries and the new tokens' keys and values are the predecessor's output
+  for (int c = tid; c < 16 * CHUNKS; c += 128) {
+    const int rr = c / CHUNKS, piece = c % CHUNKS;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (rr < rows)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(tok0 + rr / G) * q_stride + (size_t)(kvh * G + rr % G) * HD + piece * 8);
+    *reinterpret_cast<uint4*>(Qs + rr * LDS + piece * 8) = v;
+  }
+  for (; issued < SSTAGES; ++issued) issue(t_first + issued);
+  __syncthreads();
+  unsigned qf[HD / 16][4];
+#pragma unroll
+  for (int kd = 0; kd < HD / 16; ++kd)
+    ldmatrix_x4(qf[kd], Qs + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + kd * 16 + (lane >> 4) * 8);
 
   int lo[1][2], hi[1][2];
 #pragma unroll
@@ -524,6 +593,8 @@ attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__
       hi[0][h] = -1; lo[0][h] = 0;
     }
   }
+  // Positions [all_lo, all_hi] are visible to every valid row: tiles inside need no mask.
+  const int all_lo = window > 0 ? max(0, pos_hi - window + 1) : 0, all_hi = base_pos;
   float o[1][HD / 8][4];
 #pragma unroll
   for (int dt = 0; dt < HD / 8; ++dt)
@@ -532,221 +603,25 @@ attn_split_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__
   RowState st[1];
   st[0].m[0] = st[0].m[1] = -INFINITY;
   st[0].l[0] = st[0].l[1] = 0.f;
+
 #pragma unroll 1
-  for (int i = i0; i < SPLIT_TILES; ++i) {
-    if (tile_key0(i) > pos_hi) break;     // tiles of a warp ascend: nothing further is visible
-    if (i > i0) {
-      __syncwarp();                       // every lane is done reading the buffer
-      const TilePages tp = tile_pages<SBN>(table, page_size, tile_key0(i), key_first, kv_end);
-      load_tile<32, SBN>(Kw, k_cache, tp, kvh, nkv, page_size, tile_key0(i), key_first, kv_end, lane);
-      load_tile<32, SBN>(Vw, v_cache, tp, kvh, nkv, page_size, tile_key0(i), key_first, kv_end, lane);
-      cp_async_commit();
-      cp_async_wait<0>();
-      __syncwarp();
-    }
-    attend_tile<1, SBN, true, true>(nullptr, Qs, Kw, Vw, o, st, tile_key0(i), lo, hi, scale_log2);
-  }
-  __syncthreads();   // all warps are done with their tiles: the buffer becomes the merge area
-
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = h * 8 + g;
-    float l = st[0].l[h];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    float* dst = merge + ((size_t)warp * 16 + r) * PART;
-    if (t == 0) { dst[0] = st[0].m[h]; dst[1] = l; }
-#pragma unroll
-    for (int dt = 0; dt < HD / 8; ++dt) {
-      dst[2 + dt * 8 + 2 * t] = o[0][dt][2 * h];
-      dst[2 + dt * 8 + 2 * t + 1] = o[0][dt][2 * h + 1];
-    }
-  }
-  __syncthreads();
-  // Merge the four warps in warp order; write the valid rows.
-  float* dst_base = scratch + (((size_t)b * nkv + kvh) * max_splits + sp) * 16 * PART;
-  for (int e = tid; e < rows * (HD + 1); e += 128) {
-    const int r = e / (HD + 1), c = e % (HD + 1);   // c == HD: the (max, sum) pair
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, merge[(w * 16 + r) * PART]);
-    float acc = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = merge[(w * 16 + r) * PART];
-      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-      acc += f * (c == HD ? merge[(w * 16 + r) * PART + 1] : merge[(w * 16 + r) * PART + 2 + c]);
-    }
-    if (c == HD) { dst_base[r * PART] = M; dst_base[r * PART + 1] = acc; }
-    else dst_base[r * PART + 2 + c] = acc;
-  }
-}
-
-// One CTA per (request, kv head, row): the splits' (max, sum) pairs are read once into
-// shared memory, then every thread merges its head-dim columns over the splits in
-// ascending order with independent loads.
-template <int SPLIT>
-__global__ void __launch_bounds__(128)
-attn_combine_kernel(const float* __restrict__ scratch, int max_splits, bf16* __restrict__ out, long out_stride,
-                    const int* __restrict__ cu_q, const int* __restrict__ kv_lens, int nh, int nkv, int window) {
-  __shared__ float factor[512];
-  __shared__ float s_den;
-  co_pdl_launch_dependents();
-  co_pdl_wait();
-  const int b = blockIdx.z, kvh = blockIdx.y, r = blockIdx.x;
-  const int G = nh / nkv;
-  const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
-  const int rows = q_len * G;
-  if (rows > 16 || r >= rows) return;
-  const int base_pos = kv_len - q_len;
-  const int key_first = window > 0 ? max(0, base_pos - window + 1) : 0;
-  const int nsplits = min((kv_len - 1) / SPLIT - key_first / SPLIT + 1, 512);
-  const float* src = scratch + (((size_t)b * nkv + kvh) * max_splits * 16 + r) * PART;
-  const size_t stride = (size_t)16 * PART;
-  for (int s = threadIdx.x; s < nsplits; s += blockDim.x) factor[s] = src[s * stride];
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float M = -INFINITY;
-    for (int s = 0; s < nsplits; ++s) M = fmaxf(M, factor[s]);
-    float den = 0.f;
-    for (int s = 0; s < nsplits; ++s) {
-      const float f = factor[s] == -INFINITY ? 0.f : exp2f(factor[s] - M);
-      factor[s] = f;
-      den += f * src[s * stride + 1];
-    }
-    s_den = den;
-  }
-  __syncthreads();
-  const float inv = 1.0f / s_den;
-  bf16* orow = out + (size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * HD;
-  for (int c = threadIdx.x; c < HD; c += blockDim.x) {
-    float num = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < nsplits; ++s) num += factor[s] * src[s * stride + 2 + c];
-    orow[c] = __float2bfloat16_rn(num * inv);
-  }
-}
-
-// ------------------------------------------------------------------------------------
-// attn_split with bulk copies.  Within a page the rows of a kv head are contiguous, so a
-// warp's tile of 32 positions is fetched by a few cp.async.bulk copies (one per page it
-// touches, per tensor) that ONE lane issues and an mbarrier counts in; no lane computes
-// addresses of 16-byte pieces.  The tiles are unpadded in shared memory (ldmatrix then
-// meets bank conflicts, which do not matter here: the kernel waits for memory, not for
-// arithmetic).  One tile per warp, splits of 128 positions, three CTAs per SM.
-// The wait on the mbarrier is bounded; if it runs out, `status` receives 21.
-constexpr int BSBN = 32;
-constexpr int BSPLIT = 4 * BSBN;
-
-__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
-}
-
-__global__ void __launch_bounds__(128)
-attn_split_bulk_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__ scratch, int max_splits,
-                       const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                       const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
-                       const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window, float scale_log2,
-                       int* __restrict__ status) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  bf16* KVs = reinterpret_cast<bf16*>(smem_raw);                // [4 warps][K: BSBN rows, V: BSBN rows][HD]
-  bf16* Qs = KVs + 4 * 2 * BSBN * HD;                           // [16][LDS]
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(Qs + 16 * LDS);   // [4]
-  float* merge = reinterpret_cast<float*>(smem_raw);            // reused after the tiles: [4][16][PART]
-
-  co_pdl_launch_dependents();
-  co_pdl_wait();
-  const int b = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
-  const int G = nh / nkv;
-  const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
-  const int rows = q_len * G;
-  if (rows > 16 || rows <= 0) return;
-  const int base_pos = kv_len - q_len;
-  const int pos_hi = kv_len - 1;
-  const int key_first = window > 0 ? max(0, base_pos - window + 1) : 0;
-  const int split = key_first / BSPLIT + sp;      // absolute split index
-  if (split * BSPLIT > pos_hi) return;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int* table = block_tables + (size_t)b * max_blocks;
-  const int kv_end = pos_hi + 1;
-
-  bf16* Kw = KVs + (size_t)warp * 2 * BSBN * HD;
-  bf16* Vw = Kw + BSBN * HD;
-  const int key0 = split * BSPLIT + warp * BSBN;
-  const int c_lo = max(key0, key_first), c_hi = min(key0 + BSBN, kv_end);   // positions to copy: [c_lo, c_hi)
-  const bool w_active = c_lo < c_hi;
-  load_q_rows(Qs, q, q_stride, tok0, kvh, G, 0, 16, rows, tid, 128);
-  cp_async_commit();
-  if (w_active) {
-    if (lane == 0) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[warp])));
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // Rows of the tile that are not copied must still be finite for P V: zero them.
-    for (int i = lane; i < BSBN * CHUNKS; i += 32) {
-      const int row = i / CHUNKS;
-      if (key0 + row < c_lo || key0 + row >= c_hi) {
-        *reinterpret_cast<uint4*>(Kw + row * HD + (i % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(Vw + row * HD + (i % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes before the async copies
-    __syncwarp();
-    const TilePages tp = tile_pages<BSBN>(table, page_size, key0, key_first, kv_end);
-    if (lane == 0) {
-      const unsigned bytes = (unsigned)(c_hi - c_lo) * HD * 2 * 2;
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(&bars[warp])), "r"(bytes) : "memory");
-    }
-    for (int pos = c_lo; pos < c_hi;) {
-      const int block = pos / page_size;
-      const int n = min(c_hi, (block + 1) * page_size) - pos;
-      const int page = page_of(tp, block);                      // a shuffle: every lane takes part
-      if (lane == 0) {
-        const size_t off = (((size_t)page * nkv + kvh) * page_size + (pos - block * page_size)) * HD;
-        bulk_copy(Kw + (pos - key0) * HD, k_cache + off, (unsigned)n * HD * 2, &bars[warp]);
-        bulk_copy(Vw + (pos - key0) * HD, v_cache + off, (unsigned)n * HD * 2, &bars[warp]);
-      }
-      pos += n;
+  for (int i = t_first; i < t_end; ++i) {
+    // Tile i is group i - t_first; groups complete in order.
+    if (i == t_first) cp_async_wait<SSTAGES - 1>(); else cp_async_wait<SSTAGES - 2>();
+    __syncthreads();                // landed for all threads; every warp is done with tile i - 1
+    if (i > t_first) issue(i + SSTAGES - 1);   // into the stage that tile i - 1 used
+    plan(i + SSTAGES);              // for the next iteration's issue; its slot was last read when tile i was issued
+    const int key0 = c0 + i * STILE + warp * 16;
+    if (key0 < hi_key && key0 + 16 > lo_key) {
+      const bf16* Ks = stage_of(i) + warp * 16 * LDS;
+      if (key0 >= all_lo && key0 + 15 <= all_hi)
+        attend_tile<1, 16, false, false>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
+      else
+        attend_tile<1, 16, false, true>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
     }
   }
   cp_async_wait<0>();
-  __syncthreads();              // the query rows are visible to every warp
-
-  int lo[1][2], hi[1][2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = h * 8 + g;
-    if (r < rows) {
-      hi[0][h] = base_pos + r / G;
-      lo[0][h] = window > 0 ? max(0, hi[0][h] - window + 1) : 0;
-    } else {
-      hi[0][h] = -1; lo[0][h] = 0;
-    }
-  }
-  float o[1][HD / 8][4];
-#pragma unroll
-  for (int dt = 0; dt < HD / 8; ++dt)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[0][dt][i] = 0.f;
-  RowState st[1];
-  st[0].m[0] = st[0].m[1] = -INFINITY;
-  st[0].l[0] = st[0].l[1] = 0.f;
-  if (w_active) {
-    bool landed = false;
-    for (unsigned i = 0; i < (1u << 24) && !landed; ++i) {
-      unsigned done;
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t"
-          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
-          "selp.u32 %0, 1, 0, p;\n\t}"
-          : "=r"(done) : "r"(smem_addr(&bars[warp])) : "memory");
-      landed = done != 0;
-    }
-    if (landed) attend_tile<1, BSBN, true, true, HD>(nullptr, Qs, Kw, Vw, o, st, key0, lo, hi, scale_log2);
-    else if (lane == 0) atomicExch(status, 21);
-  }
-  __syncthreads();   // all warps are done with their tiles: the buffer becomes the merge area
+  __syncthreads();   // all warps are done with their tiles: the ring becomes the merge area
 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -764,7 +639,7 @@ attn_split_bulk_kernel(const bf16* __restrict__ q, long q_stride, float* __restr
   }
   __syncthreads();
   // Merge the four warps in warp order; write the valid rows.
-  float* dst_base = scratch + (((size_t)b * nkv + kvh) * max_splits + sp) * 16 * PART;
+  float* dst_base = scratch + (((size_t)b * nkv + kvh) * max_splits + sp) * SPLIT_FLOATS;
   for (int e = tid; e < rows * (HD + 1); e += 128) {
     const int r = e / (HD + 1), c = e % (HD + 1);   // c == HD: the (max, sum) pair
     float M = -INFINITY;
@@ -777,92 +652,145 @@ attn_split_bulk_kernel(const bf16* __restrict__ q, long q_stride, float* __restr
       const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
       acc += f * (c == HD ? merge[(w * 16 + r) * PART + 1] : merge[(w * 16 + r) * PART + 2 + c]);
     }
-    if (c == HD) { dst_base[r * PART] = M; dst_base[r * PART + 1] = acc; }
-    else dst_base[r * PART + 2 + c] = acc;
+    if (c == HD) { dst_base[16 * HD + 2 * r] = M; dst_base[16 * HD + 2 * r + 1] = acc; }
+    else dst_base[r * HD + c] = acc;
   }
 }
 
-constexpr size_t bulk_smem() {
-  const size_t tiles = (size_t)4 * 2 * BSBN * HD * sizeof(bf16) + (size_t)16 * LDS * sizeof(bf16) + 4 * sizeof(unsigned long long);
-  const size_t merge = (size_t)4 * 16 * PART * sizeof(float);
-  return (tiles > merge ? tiles : merge) + 128;
+// One CTA per (request, kv head), one warp per row and no shared memory.  A lane reads the
+// (max, sum) pair of one split (32 splits at a time), the warp agrees on the maximum, and the
+// lanes then add the splits' accumulators, four columns per lane and up to sixteen independent
+// loads at a time, in ascending order of the splits.
+__global__ void __launch_bounds__(512)
+attn_combine_kernel(const float* __restrict__ scratch, int max_splits, bf16* __restrict__ out, long out_stride,
+                    const int* __restrict__ cu_q, const int* __restrict__ kv_lens, int nh, int nkv, int window,
+                    int split) {
+  constexpr int UB = HD > 128 ? 8 : 16;   // splits whose loads are in flight together
+  co_pdl_launch_dependents();
+  // The lengths are inputs of the step: a warp without a row leaves before it waits.
+  const int b = blockIdx.y, kvh = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int G = nh / nkv;
+  const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
+  const int rows = q_len * G;
+  if (rows > 16 || warp >= rows) return;
+  co_pdl_wait();
+  const int base_pos = kv_len - q_len;
+  const int key_first = window > 0 ? max(0, base_pos - window + 1) : 0;
+  const int nsplits = (kv_len - 1) / split - key_first / split + 1;
+  const float* base = scratch + ((size_t)b * nkv + kvh) * max_splits * SPLIT_FLOATS;
+  for (int r = warp; r < rows; r += nwarps) {
+    float M = -INFINITY;
+    for (int s = lane; s < nsplits; s += 32) M = fmaxf(M, base[(size_t)s * SPLIT_FLOATS + 16 * HD + 2 * r]);
+    M = co_warp_max(M);
+    float den = 0.f;
+    float4 acc[(HD + 127) / 128];
+#pragma unroll
+    for (int q = 0; q < (HD + 127) / 128; ++q) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < nsplits; s0 += 32) {
+      float f = 0.f, l = 0.f;
+      if (s0 + lane < nsplits) {
+        const float2 ml = *reinterpret_cast<const float2*>(base + (size_t)(s0 + lane) * SPLIT_FLOATS + 16 * HD + 2 * r);
+        f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+        l = ml.y;
+      }
+      den += f * l;
+      const int n = min(32, nsplits - s0);
+      for (int u0 = 0; u0 < n; u0 += UB) {
+        float4 t[UB][(HD + 127) / 128];
+#pragma unroll
+        for (int u = 0; u < UB; ++u)
+#pragma unroll
+          for (int q = 0; q < (HD + 127) / 128; ++q) {
+            const int c = q * 128 + lane * 4;
+            t[u][q] = (u0 + u < n && c < HD)
+                          ? *reinterpret_cast<const float4*>(base + (size_t)(s0 + u0 + u) * SPLIT_FLOATS + r * HD + c)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+        for (int u = 0; u < UB; ++u) {
+          const float fu = __shfl_sync(0xffffffffu, f, (u0 + u) & 31);
+#pragma unroll
+          for (int q = 0; q < (HD + 127) / 128; ++q) {
+            acc[q].x += fu * t[u][q].x; acc[q].y += fu * t[u][q].y; acc[q].z += fu * t[u][q].z; acc[q].w += fu * t[u][q].w;
+          }
+        }
+      }
+    }
+    den = co_warp_sum(den);
+    const float inv = 1.0f / den;
+    bf16* orow = out + (size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * HD;
+#pragma unroll
+    for (int q = 0; q < (HD + 127) / 128; ++q) {
+      const int c = q * 128 + lane * 4;
+      if (c < HD) {
+        __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[q].x * inv, acc[q].y * inv);
+        __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc[q].z * inv, acc[q].w * inv);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned*>(&lo2);
+        raw.y = *reinterpret_cast<unsigned*>(&hi2);
+        *reinterpret_cast<uint2*>(orow + c) = raw;
+      }
+    }
+  }
 }
 
 constexpr size_t TILES_SMEM = (size_t)(BM + 4 * TILE) * LDS * sizeof(bf16);
 static_assert((size_t)(KG - 1) * 4 * 16 * (HD + 2) * sizeof(float) <= (size_t)4 * TILE * LDS * sizeof(bf16), "the merge area fits the stages");
-constexpr size_t split_smem(int sbn) {
-  const size_t tiles = (size_t)(16 + 4 * 2 * sbn) * LDS * sizeof(bf16);
-  const size_t merge = (size_t)16 * LDS * sizeof(bf16) + (size_t)4 * 16 * PART * sizeof(float);
-  return tiles > merge ? tiles : merge;
-}
 
-template <int SBN, int SPLIT>
-int launch_split(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
-                 const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
-                 int page_size, int window, float scale_log2, int max_kv_len, float* scratch, long scratch_floats,
-                 cudaStream_t stream) {
-  constexpr size_t SMEM = split_smem(SBN);
-  const int max_splits = (max_kv_len + SPLIT - 1) / SPLIT + 1;
-  if (!scratch || scratch_floats < (long)B * nkv * max_splits * 16 * PART)
-    CO_FAIL("attention_bf16: scratch of %ld floats is too small", scratch_floats);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<SBN, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
-    configured = true;
-  }
-  co_launch(attn_split_kernel<SBN, SPLIT>, dim3(max_splits, nkv, B), dim3(128), SMEM, stream, (const bf16*)q, q_stride,
-            scratch, max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens,
-            nh, nkv, page_size, window, scale_log2);
-  CO_CHECK_LAUNCH("attn_split");
-  co_launch(attn_combine_kernel<SPLIT>, dim3(16, nkv, B), dim3(HD >= 128 ? 128 : 64), 0, stream, (const float*)scratch,
-            max_splits, (bf16*)out, out_stride, cu_q, kv_lens, nh, nkv, window);
-  CO_CHECK_LAUNCH("attn_combine");
-  return 0;
-}
-int launch_split_bulk(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
-                      const void* v_cache, const int* block_tables, int max_blocks, const int* cu_q,
-                      const int* kv_lens, int B, int nh, int nkv, int page_size, int window, float scale_log2,
-                      int max_kv_len, float* scratch, long scratch_floats, int* status, cudaStream_t stream) {
-  constexpr size_t SMEM = bulk_smem();
-  const int max_splits = (max_kv_len + BSPLIT - 1) / BSPLIT + 1;
-  if (!scratch || scratch_floats < (long)B * nkv * max_splits * 16 * PART)
-    CO_FAIL("attention_bf16: scratch of %ld floats is too small", scratch_floats);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_split_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
-    configured = true;
-  }
-  co_launch(attn_split_bulk_kernel, dim3(max_splits, nkv, B), dim3(128), SMEM, stream, (const bf16*)q, q_stride, scratch,
-            max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv,
-            page_size, window, scale_log2, status);
-  CO_CHECK_LAUNCH("attn_split_bulk");
-  co_launch(attn_combine_kernel<BSPLIT>, dim3(16, nkv, B), dim3(HD >= 128 ? 128 : 64), 0, stream, (const float*)scratch,
-            max_splits, (bf16*)out, out_stride, cu_q, kv_lens, nh, nkv, window);
-  CO_CHECK_LAUNCH("attn_combine");
-  return 0;
-}
-
-// Which decode kernel runs: COHERYN_ATTN_SPLIT = auto | wide | narrow | bulk (experiments).
-int split_choice() {
-  static int choice = -1;
-  if (choice < 0) {
+// Positions per CTA of attn_stream.  coheryn_attn_set_split (or COHERYN_ATTN_SPLIT = 128 |
+// 256 | 512 in the environment, read at first use) fixes it; otherwise the largest of the
+// three whose grid still fills the GPU (two CTAs per SM), else the smallest.
+int g_forced_split = -1;
+int split_keys(int B, int nkv, int max_kv_len) {
+  if (g_forced_split < 0) {
     const char* e = getenv("COHERYN_ATTN_SPLIT");
-    choice = !e ? 0 : (e[0] == 'w' ? 1 : (e[0] == 'n' ? 2 : (e[0] == 'b' ? 3 : 0)));
+    const int v = e ? atoi(e) : 0;
+    g_forced_split = (v == 128 || v == 256 || v == 512) ? v : 0;
   }
-  return choice;
+  if (g_forced_split) return g_forced_split;
+  const long slots = (STREAM_SMEM + 1024 <= 227 * 1024 / 2 ? 2 : 1) * 148L;
+  for (int s = SPLIT_MAX; s > SPLIT_MIN; s >>= 1)
+    if ((long)B * nkv * ((max_kv_len + s - 1) / s) >= slots) return s;
+  return SPLIT_MIN;
+}
+
+int launch_stream(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
+                  const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
+                  int page_size, int window, float scale_log2, int max_kv_len, int max_rows, float* scratch,
+                  long scratch_floats, cudaStream_t stream) {
+  const int split = split_keys(B, nkv, max_kv_len);
+  const int max_splits = (max_kv_len + split - 1) / split + 1;
+  if (!scratch || scratch_floats < (long)B * nkv * max_splits * SPLIT_FLOATS)
+    CO_FAIL("attention_bf16: scratch of %ld floats is too small", scratch_floats);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM);
+    if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", STREAM_SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  co_launch(attn_stream_kernel, dim3(max_splits, nkv, B), dim3(128), STREAM_SMEM, stream, (const bf16*)q, q_stride,
+            scratch, max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens,
+            nh, nkv, page_size, window, scale_log2, split);
+  CO_CHECK_LAUNCH("attn_stream");
+  const int threads = 32 * (max_rows < 16 ? max_rows : 16);
+  co_launch(attn_combine_kernel, dim3(nkv, B), dim3(threads), 0, stream, (const float*)scratch, max_splits,
+            (bf16*)out, out_stride, cu_q, kv_lens, nh, nkv, window, split);
+  CO_CHECK_LAUNCH("attn_combine");
+  return 0;
 }
 }  // namespace
 
 CO_EXPORT int coheryn_attn_head_dim() { return HD; }
 CO_EXPORT int coheryn_attn_split_keys() { return SPLIT_MIN; }
+// keys = 128, 256 or 512 fixes the positions per CTA of the decode kernel; 0 restores the choice by batch size.
+CO_EXPORT void coheryn_attn_set_split(int keys) { g_forced_split = (keys == 128 || keys == 256 || keys == 512) ? keys : 0; }
 
 // Floats of scratch that coheryn_attention_bf16 needs for B requests of at most
 // max_kv_len positions when some request takes the split path.
 CO_EXPORT long coheryn_attn_scratch_floats(int B, int nkv, int max_kv_len) {
-  const long max_splits = (max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1;   // covers both split sizes
-  return (long)B * nkv * max_splits * 16 * PART;
+  const long max_splits = (max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1;   // the smallest split needs the most
+  return (long)B * nkv * max_splits * SPLIT_FLOATS;
 }
 
 // q: [T, nh*HD] rows of stride q_stride; out likewise.  Caches: [page][kv head][slot][HD].
@@ -875,14 +803,15 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
                                      float* scratch, long scratch_floats, int* status, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nkv <= 0 || nh % nkv) CO_FAIL("attention_bf16: %d heads do not group over %d kv heads", nh, nkv);
-  if ((q_stride & 7) || (out_stride & 1)) CO_FAIL("attention_bf16: row strides must keep 16-byte alignment");
+  if ((q_stride & 7) || (out_stride & 3) || ((uintptr_t)out & 7))
+    CO_FAIL("attention_bf16: q rows must keep 16-byte and out rows 8-byte alignment");
   if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
     CO_FAIL("attention_bf16: operands must be 16-byte aligned");
   const float scale_log2 = scale * 1.4426950408889634f;
   const int G = nh / nkv;
-  // The split kernel keeps eight tiles in shared memory; beyond 227 KB every request takes
-  // the tile kernel instead.
-  const bool split_path = any_small && G <= 16 && split_smem(32) <= 227 * 1024 &&
+  // Requests with at most 16 rows per kv head stream their keys through attn_stream.
+  (void)status;
+  const bool split_path = any_small && G <= 16 &&
                           (max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1 <= 512;   // attn_combine keeps 512 factors
   if (any_large || (any_small && !split_path)) {
     static bool configured = false;
@@ -897,23 +826,8 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
               window, scale_log2, split_path ? 1 : 0);
     CO_CHECK_LAUNCH("attn_tiles");
   }
-  if (split_path) {
-    // All CTAs of the wide shape resident at once (one per SM, with a little queueing)?
-    const long wide_ctas = (long)B * nkv * ((max_kv_len + 255) / 256 + 1);
-    const int choice = split_choice();
-    // Measured on a B200 inside whole decode steps (cold cache): the wide shape wins while its
-    // grid fits the GPU about twice over, the narrow one beyond.
-    const bool wide = choice == 1 || (choice == 0 && wide_ctas <= 2 * 148);
-    if (wide && split_smem(64) <= 227 * 1024)
-      return launch_split<64, 256>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q,
-                                   kv_lens, B, nh, nkv, page_size, window, scale_log2, max_kv_len, scratch,
-                                   scratch_floats, stream);
-    if (choice != 3 || !status)   // measured: the bulk-copy shape is no faster than the cp.async one
-      return launch_split<32, 128>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q,
-                                   kv_lens, B, nh, nkv, page_size, window, scale_log2, max_kv_len, scratch,
-                                   scratch_floats, stream);
-    return launch_split_bulk(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B,
-                             nh, nkv, page_size, window, scale_log2, max_kv_len, scratch, scratch_floats, status, stream);
-  }
+  if (split_path)
+    return launch_stream(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B, nh,
+                         nkv, page_size, window, scale_log2, max_kv_len, max_rows, scratch, scratch_floats, stream);
   return 0;
 }

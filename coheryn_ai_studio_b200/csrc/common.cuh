@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 // dtype codes shared with the Python side (ops.py).
 #define CO_F32 0
@@ -38,9 +39,31 @@ __device__ __forceinline__ void co_pdl_launch_dependents() { asm volatile("gridd
 
 bool co_pdl_enabled();   // COHERYN_PDL=0 in the environment switches the launch attribute off
 
+// Kernels ask for the largest shared-memory carve-out, whatever they use themselves: an SM
+// changes its split between L1 and shared memory only when it is empty, so kernels with
+// different preferences cannot share an SM, and a dependent launch cannot take its place
+// early on an SM that its predecessor still occupies.  A kernel that lives on L1 hits is
+// launched with keep_l1 = true and keeps the default split.  COHERYN_CARVEOUT=0 in the
+// environment leaves every kernel's default.
+inline void co_prefer_max_shared(const void* kernel) {
+  static const void* seen[128];
+  static int n = 0;
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("COHERYN_CARVEOUT");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (!enabled) return;
+  for (int i = 0; i < n; ++i)
+    if (seen[i] == kernel) return;
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  if (n < 128) seen[n++] = kernel;
+}
+
 template <typename... KArgs, typename... Args>
-inline cudaError_t co_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             Args... args) {
+inline cudaError_t co_launch_ex(bool keep_l1, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, Args... args) {
+  if (!keep_l1) co_prefer_max_shared((const void*)kernel);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -52,6 +75,39 @@ inline cudaError_t co_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   cfg.attrs = attr;
   cfg.numAttrs = co_pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+// The same for a kernel whose CTAs form clusters of `cluster_x` along x (1: no clusters).
+template <typename... KArgs, typename... Args>
+inline cudaError_t co_launch_cluster(int cluster_x, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+  co_prefer_max_shared((const void*)kernel);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (co_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t co_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  return co_launch_ex(false, kernel, grid, block, smem, stream, args...);
 }
 
 template <typename T>

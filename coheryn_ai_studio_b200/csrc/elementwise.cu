@@ -99,14 +99,46 @@ template <> struct Vec4<__nv_bfloat16> {
   }
 };
 
+// Thread-block clusters: rank and size of this CTA's cluster (1 CTA when launched without one),
+// and a sum over the cluster's CTAs: every CTA writes its term into slot `rank` of EVERY
+// CTA's `slots` (distributed shared memory), the cluster meets at its hardware barrier, and
+// each CTA adds its own copy of the slots in rank order.  No CTA reads a peer's memory, so
+// none has to outlive the others.  `v` must be the same in all threads of the CTA.
+__device__ __forceinline__ unsigned co_cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned co_cluster_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ float co_cluster_sum(float v, float* slots /* >= cluster size floats, shared */) {
+  const unsigned n = co_cluster_size(), rank = co_cluster_rank();
+  if (n == 1) return v;
+  if (threadIdx.x < n) {
+    unsigned local = (unsigned)__cvta_generic_to_shared(slots + rank), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(threadIdx.x));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  float total = 0.f;
+  for (unsigned k = 0; k < n; ++k) total += slots[k];
+  return total;
+}
+
 template <typename TD, typename TO, typename TW, int STEPS>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const int* __restrict__ rows,
                        const TW* __restrict__ weight, float eps, TO* __restrict__ out, int H, int update) {
   __shared__ float scratch[33];
+  __shared__ float cl_slots[8];
   co_pdl_launch_dependents();
+  // The CTAs of a cluster share a row: CTA k of n takes the k-th run of columns.
+  const int cl_n = (int)co_cluster_size(), cl_r = (int)co_cluster_rank();
+  const int c_per = ((H / 4 + cl_n - 1) / cl_n) * 4;
+  const int c_lo = cl_r * c_per, c_hi = min(H, c_lo + c_per);
+  float4 wv[STEPS];   // the weights depend on no earlier kernel
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+    wv[i] = j < c_hi ? Vec4<TW>::load(weight + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   co_pdl_wait();
-  const int r = blockIdx.x;
+  const int r = blockIdx.x / cl_n;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float* x = resid + src * H;
   const TD* d = delta ? delta + src * H : nullptr;
@@ -114,8 +146,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, 
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < STEPS; ++i) {
-    const int j = (i * 256 + threadIdx.x) * 4;
-    if (j < H) {
+    const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+    if (j < c_hi) {
       v[i] = Vec4<float>::load(x + j);
       if (d) {
         const float4 dv = Vec4<TD>::load(d + j);
@@ -125,26 +157,31 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, 
       ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
     }
   }
-  ss = co_block_sum(ss, scratch);
+  ss = co_cluster_sum(co_block_sum(ss, scratch), cl_slots);
   const float scale = 1.0f / sqrtf(ss / (float)H + eps);
   TO* o = out + (size_t)r * H;
 #pragma unroll
   for (int i = 0; i < STEPS; ++i) {
-    const int j = (i * 256 + threadIdx.x) * 4;
-    if (j < H) {
-      const float4 w = Vec4<TW>::load(weight + j);
+    const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+    if (j < c_hi) {
+      const float4 w = wv[i];
       Vec4<TO>::store(o + j, make_float4((v[i].x * scale) * w.x, (v[i].y * scale) * w.y, (v[i].z * scale) * w.z,
                                          (v[i].w * scale) * w.w));
     }
   }
 }
 
+// With few rows one CTA per row leaves the GPU idle and the row's latency long: a cluster of
+// four CTAs shares each row (from 1024 columns on, up to 64 rows).
+inline int norm_cluster(int n_rows, int H) { return (n_rows <= 64 && H >= 1024 && (H / 4) % 4 == 0) ? 4 : 1; }
+
 template <typename TD, typename TO, typename TW>
 void launch_rmsnorm_vec(float* resid, const void* delta, const int* rows, const void* weight, float eps, void* out,
                         int n_rows, int H, int update, cudaStream_t stream) {
-  const int steps = (H / 4 + 255) / 256;
-#define GO(S) co_launch(add_rmsnorm_vec_kernel<TD, TO, TW, S>, dim3(n_rows), dim3(256), 0, stream, resid, (const TD*)delta, \
-                        rows, (const TW*)weight, eps, (TO*)out, H, update)
+  const int cl = norm_cluster(n_rows, H);
+  const int steps = (H / 4 / cl + 255) / 256;
+#define GO(S) co_launch_cluster(cl, add_rmsnorm_vec_kernel<TD, TO, TW, S>, dim3(n_rows * cl), dim3(256), 0, stream, resid, \
+                                (const TD*)delta, rows, (const TW*)weight, eps, (TO*)out, H, update)
   if (steps <= 1) GO(1); else if (steps <= 2) GO(2); else if (steps <= 4) GO(4); else GO(8);
 #undef GO
 }
@@ -175,6 +212,150 @@ CO_EXPORT int coheryn_add_rmsnorm(float* resid, const void* delta, int delta_dty
   else CO_FAIL("add_rmsnorm: unknown dtypes %d/%d", delta_dtype, out_dtype);
 #undef LAUNCH
   CO_CHECK_LAUNCH("add_rmsnorm");
+  return 0;
+}
+
+// The same with the delta given as a stack of float32 partial sums [splits][n][H] (a matrix
+// product that split K over CTAs and left the addition to its consumer): the parts are added
+// in order 0, 1, ... and then to the residual.  All of a thread's loads are independent.
+template <typename TO, typename TW, int STEPS>
+__global__ void __launch_bounds__(256)
+add_parts_rmsnorm_vec_kernel(float* __restrict__ resid, const float* __restrict__ parts, int splits, size_t split_stride,
+                             const int* __restrict__ rows, const TW* __restrict__ weight, float eps,
+                             TO* __restrict__ out, int H, int update) {
+  __shared__ float scratch[33];
+  __shared__ float cl_slots[8];
+  co_pdl_launch_dependents();
+  // The CTAs of a cluster share a row: CTA k of n takes the k-th run of columns.
+  const int cl_n = (int)co_cluster_size(), cl_r = (int)co_cluster_rank();
+  const int c_per = ((H / 4 + cl_n - 1) / cl_n) * 4;
+  const int c_lo = cl_r * c_per, c_hi = min(H, c_lo + c_per);
+  float4 wv[STEPS];   // the weights depend on no earlier kernel
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+    wv[i] = j < c_hi ? Vec4<TW>::load(weight + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  co_pdl_wait();
+  const int r = blockIdx.x / cl_n;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* x = resid + src * H;
+  const float* d = parts + src * H;
+  // Eight parts of every step are fetched before the first is added: the row's latency is a
+  // couple of round trips whatever the number of parts; the additions keep the order 0, 1, ...
+  constexpr int ZB = 8;
+  float4 v[STEPS], sum[STEPS];
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+    v[i] = j < c_hi ? Vec4<float>::load(x + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int z0 = 0; z0 < splits; z0 += ZB) {
+    float4 t[STEPS][ZB];
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+      const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+#pragma unroll
+      for (int u = 0; u < ZB; ++u)
+        t[i][u] = (j < c_hi && z0 + u < splits) ? Vec4<float>::load(d + (size_t)(z0 + u) * split_stride + j)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i)
+#pragma unroll
+      for (int u = 0; u < ZB; ++u) {
+        sum[i].x += t[i][u].x; sum[i].y += t[i][u].y; sum[i].z += t[i][u].z; sum[i].w += t[i][u].w;
+      }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+    if (j < c_hi) {
+      v[i].x += sum[i].x; v[i].y += sum[i].y; v[i].z += sum[i].z; v[i].w += sum[i].w;
+      if (update) Vec4<float>::store(x + j, v[i]);
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+  }
+  ss = co_cluster_sum(co_block_sum(ss, scratch), cl_slots);
+  const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* o = out + (size_t)r * H;
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) {
+    const int j = c_lo + (i * 256 + threadIdx.x) * 4;
+    if (j < c_hi) {
+      const float4 w = wv[i];
+      Vec4<TO>::store(o + j, make_float4((v[i].x * scale) * w.x, (v[i].y * scale) * w.y, (v[i].z * scale) * w.z,
+                                         (v[i].w * scale) * w.w));
+    }
+  }
+}
+
+template <typename TO>
+__global__ void add_parts_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ parts, int splits,
+                                         size_t split_stride, const int* __restrict__ rows,
+                                         const void* __restrict__ weight, int wdtype, float eps, TO* __restrict__ out,
+                                         int H, int update) {
+  __shared__ float scratch[33];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* x = resid + src * H;
+  const float* d = parts + src * H;
+  auto value = [&](int j) {
+    float sum = d[j];
+    for (int z = 1; z < splits; ++z) sum += d[z * split_stride + j];
+    return x[j] + sum;
+  };
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = value(j);
+    ss += v * v;
+  }
+  ss = co_block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* o = out + (size_t)r * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = value(j);
+    o[j] = co_from_float<TO>((v * scale) * co_load_any(weight, wdtype, j));
+    if (update) x[j] = v;   // after the last read of x[j] by this thread, its only reader
+  }
+}
+
+// parts: float32 [splits][n][H] with `split_stride` elements between splits (n = the rows of
+// resid).  Otherwise as coheryn_add_rmsnorm.
+CO_EXPORT int coheryn_add_parts_rmsnorm(float* resid, const float* parts, int splits, long split_stride,
+                                        const int* rows, const void* weight, int wdtype, float eps, void* out,
+                                        int out_dtype, int n_rows, int H, int update, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (splits < 1 || !parts) CO_FAIL("add_parts_rmsnorm: %d parts", splits);
+  if (rows && update) CO_FAIL("add_parts_rmsnorm: cannot update the residual through a row gather");
+  const bool bf = out_dtype == CO_BF16;
+  if (!bf && out_dtype != CO_F32) CO_FAIL("add_parts_rmsnorm: unknown output dtype %d", out_dtype);
+  if (H % 4 == 0 && H <= 8192 && (split_stride & 3) == 0 && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)parts & 15) == 0 &&
+      ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const int cl = norm_cluster(n_rows, H);
+    const int steps = (H / 4 / cl + 255) / 256;
+#define GO2(TO, TW, S) co_launch_cluster(cl, add_parts_rmsnorm_vec_kernel<TO, TW, S>, dim3(n_rows * cl), dim3(256), 0, stream, resid, parts, \
+                                 splits, (size_t)split_stride, rows, (const TW*)weight, eps, (TO*)out, H, update)
+#define GO(TO, TW) do { if (steps <= 1) GO2(TO, TW, 1); else if (steps <= 2) GO2(TO, TW, 2); else if (steps <= 4) GO2(TO, TW, 4); else GO2(TO, TW, 8); } while (0)
+    if (bf && wdtype == CO_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+    else if (bf) GO(__nv_bfloat16, float);
+    else if (wdtype == CO_F32) GO(float, float);
+    else GO(float, __nv_bfloat16);
+#undef GO
+#undef GO2
+    CO_CHECK_LAUNCH("add_parts_rmsnorm");
+    return 0;
+  }
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (bf) co_launch(add_parts_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, resid, parts, splits,
+                    (size_t)split_stride, rows, weight, wdtype, eps, (__nv_bfloat16*)out, H, update);
+  else co_launch(add_parts_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, resid, parts, splits,
+                 (size_t)split_stride, rows, weight, wdtype, eps, (float*)out, H, update);
+  CO_CHECK_LAUNCH("add_parts_rmsnorm");
   return 0;
 }
 

@@ -341,7 +341,7 @@ int launch_small_norm(const float* resid_in, const void* delta, const void* norm
     if (e != cudaSuccess) CO_FAIL("gemm_small_norm: shared memory %zu: %s", smem, cudaGetErrorString(e));
   }
   const int grid = (N + NT * 8 - 1) / (NT * 8);
-  cudaError_t e = co_launch(kernel, dim3(grid), dim3(warps * 32), smem, stream, resid_in, (const __nv_bfloat16*)delta,
+  cudaError_t e = co_launch_ex(true /* x is re-read through L1 */, kernel, dim3(grid), dim3(warps * 32), smem, stream, resid_in, (const __nv_bfloat16*)delta,
                             norm_w, norm_dtype, eps, resid_out, (const __nv_bfloat16*)w, bias, bias_dtype, out,
                             out_dtype, M, N, K, ldo, epilogue);
   if (e != cudaSuccess) CO_FAIL("gemm_small_norm: launch failed: %s", cudaGetErrorString(e));
@@ -359,7 +359,7 @@ int launch_small(const void* x, const void* w, const void* bias, int bias_dtype,
     if (e != cudaSuccess) CO_FAIL("gemm_small: shared memory %zu: %s", smem, cudaGetErrorString(e));
   }
   const int grid = (N + NT * 8 - 1) / (NT * 8);
-  cudaError_t e = co_launch(kernel, dim3(grid), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
+  cudaError_t e = co_launch_ex(true /* x is re-read through L1 */, kernel, dim3(grid), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
                             (const __nv_bfloat16*)w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, ldo, epilogue);
   if (e != cudaSuccess) CO_FAIL("gemm_small: launch failed: %s", cudaGetErrorString(e));
   CO_CHECK_LAUNCH("gemm_small");

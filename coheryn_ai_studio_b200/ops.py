@@ -6,6 +6,7 @@ or without the compiled library they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -105,7 +106,8 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, update: bool = True) -> None:
     """x = resid (+ delta); resid = x if update; out = x / sqrt(mean(x^2) + eps) * weight.
     With ``rows`` only those rows are read (out[r] comes from row rows[r]) and the
-    residual is left as it is."""
+    residual is left as it is.  ``delta`` may be a float32 stack [splits, n, H] of partial sums
+    (see ``linear(partial_ok=True)``): they are added in order, then to the residual."""
     _dev(resid, delta, weight, out, rows)
     H = resid.shape[-1]
     assert resid.dtype == torch.float32 and resid.is_contiguous()
@@ -117,9 +119,16 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         update = False
     else:
         assert resid.shape[0] >= n
+    lib = core()
+    if delta is not None and delta.dim() == 3:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and delta.shape[1:] == resid.shape
+        _check(lib, lib.coheryn_add_parts_rmsnorm(
+            _ptr(resid), _ptr(delta), c_int(delta.shape[0]), c_long(delta.stride(0)), _ptr(rows), _ptr(weight),
+            c_int(_code(weight)), c_float(eps), _ptr(out), c_int(_code(out)), c_int(n), c_int(H),
+            c_int(1 if update else 0), _stream()))
+        return
     if delta is not None:
         assert delta.is_contiguous() and delta.shape == resid.shape
-    lib = core()
     _check(lib, lib.coheryn_add_rmsnorm(
         _ptr(resid), _ptr(delta), c_int(_code(delta) if delta is not None else F32), _ptr(rows),
         _ptr(weight), c_int(_code(weight)), c_float(eps), _ptr(out), c_int(_code(out)), c_int(n),
@@ -301,6 +310,79 @@ def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
         c_int(1 if gated else 0), _ptr(tc_status(x.device)), _ptr(workspace), c_long(floats), _stream()))
 
 
+_few_workspaces = {}
+_few_retired = []     # outgrown workspaces stay alive: captured graphs may still name them
+
+
+def _few_workspace(device, floats: int) -> torch.Tensor:
+    """Zero-initialised scratch of the few-rows product: counters, then the K splits' tiles.
+    One per device: the products that share it must run in stream order on one stream."""
+    key = str(device)
+    ws = _few_workspaces.get(key)
+    if ws is None or ws.numel() < floats:
+        if ws is not None:
+            _few_retired.append(ws)
+        ws = torch.zeros(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _few_workspaces[key] = ws
+    return ws
+
+
+def few_splits(N: int, K: int) -> int:
+    """Into how many slices of K the few-rows product cuts this weight shape (1: none)."""
+    return int(core().coheryn_gemm_tc_few_splits(c_int(N), c_int(K)))
+
+
+def gemm_bf16_tc_few(x, w, bias, out, gated: bool = False, defer: bool = False) -> None:
+    """TMA + tcgen05 product for at most 64 rows with the features on the accumulator's
+    lanes (decode, short portions); see csrc/gemm_tc_few.cu.  ``defer``: ``out`` is a float32
+    stack [splits, M, N] of the K slices' sums, left for the consumer to add."""
+    _dev(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == K
+    assert x.stride(1) == 1 and out.stride(-1) == 1
+    lib = core()
+    if defer:
+        assert not gated and out.dtype == torch.float32 and out.is_contiguous()
+        assert out.shape == (few_splits(N, K), M, N)
+        floats = 0
+    else:
+        assert out.shape == (M, N // 2 if gated else N)
+        lib.coheryn_gemm_tc_few_workspace_floats.restype = ctypes.c_long
+        floats = int(lib.coheryn_gemm_tc_few_workspace_floats(c_int(M), c_int(N), c_int(K)))   # > 0: K is split
+    workspace = _few_workspace(x.device, floats) if floats else None
+    _check(lib, lib.coheryn_gemm_bf16_tc_few(
+        _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
+        c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(-2)),
+        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _ptr(workspace),
+        c_long(workspace.numel() if workspace is not None else 0), c_int(1 if defer else 0), _stream()))
+
+
+# Up to this many rows the few-rows tcgen05 kernel takes the products whose K it need not
+# split, or whose consumer adds the splits (0 switches it off).  A product that would have to
+# add its own splits goes to the mma.sync kernel instead: measured on a B200, the in-kernel
+# addition through memory costs several dependent round trips.
+FEW_M = int(os.environ.get("COHERYN_FEW_M", "16"))
+
+
+# A product hands its K slices to the consumer only from this K on.  Measured on a B200 at 8
+# rows: for K = 1536 (12 slices of two steps) the norm that adds twelve parts loses more than
+# the product gains over the mma.sync kernel; for K = 8960 the pair is 5 us faster.
+DEFER_MIN_K = 4096
+
+
+def _few_ok(x, w, partial_ok: bool = False) -> bool:
+    if not _few_shape_ok(x, w):
+        return False
+    return partial_ok or few_splits(w.shape[0], w.shape[1]) == 1
+
+
+def _few_shape_ok(x, w) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= FEW_M
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
 def _tc_ok(x, w) -> bool:
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > SMALL_M
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
@@ -343,16 +425,27 @@ def _small_ok(x, w) -> bool:
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+           partial_ok: bool = False) -> torch.Tensor:
     """y = x @ w.T (+ bias), float32 accumulation.  float32 operands use FMA on the CUDA
     cores (no reduced-precision tensor mode); bfloat16 operands use the tensor-core
-    kernels where the shape allows and the FMA kernel otherwise."""
+    kernels where the shape allows and the FMA kernel otherwise.  With ``partial_ok`` the
+    result may come as a float32 stack [splits, M, N] of partial sums whose addition is left
+    to the consumer (``add_rmsnorm`` takes such a stack as its delta)."""
     M, N = x.shape[0], w.shape[0]
+    if partial_ok and out is None and M and w.shape[1] >= DEFER_MIN_K and _few_shape_ok(x, w):
+        splits = few_splits(N, w.shape[1])
+        if splits > 1:
+            parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+            gemm_bf16_tc_few(x, w, bias, parts, defer=True)
+            return parts
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     if M == 0:
         return out
-    if _small_ok(x, w):
+    if _few_ok(x, w):
+        gemm_bf16_tc_few(x, w, bias, out)
+    elif _small_ok(x, w):
         gemm_bf16_small(x, w, bias, out)
     elif _tc_ok(x, w):
         gemm_bf16_tc(x, w, bias, out)
@@ -384,6 +477,12 @@ def attention_lib(head_dim: int):
     return lib
 
 
+def set_attention_split(head_dim: int, keys: int) -> None:
+    """Fix the positions per CTA of the decode attention kernel for this head size (128, 256
+    or 512); 0 restores the choice by batch size.  For tests and experiments."""
+    attention_lib(head_dim).coheryn_attn_set_split(c_int(keys))
+
+
 def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads, num_kv_heads,
                    head_dim, page_size, window, scale, cu_q=None, kv_lens=None, q_lens=None,
                    max_kv_len=None, force_simple=False) -> None:
@@ -394,7 +493,7 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
     multiple of 16 up to 256; everything else goes to the float32-arithmetic kernel."""
     fast = (not force_simple and q.dtype == torch.bfloat16 and cu_q is not None and kv_lens is not None
             and q_lens is not None and max_kv_len is not None and head_dim % 16 == 0 and 16 <= head_dim <= 256
-            and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0)
+            and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0)
     if not fast:
         attention_simple(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads,
                          num_kv_heads, head_dim, page_size, window, scale)
@@ -427,6 +526,9 @@ def gated_silu_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     I = w_gate_up.shape[0] // 2
     out = torch.empty((M, I), dtype=x.dtype, device=x.device)
     if M == 0:
+        return out
+    if _few_ok(x, w_gate_up):
+        gemm_bf16_tc_few(x, w_gate_up, None, out, gated=True)
         return out
     if _small_ok(x, w_gate_up):
         gemm_bf16_small(x, w_gate_up, None, out, gated=True)

@@ -103,7 +103,7 @@ class Attention(Mixer):
         o = torch.empty((T, self.q_size), dtype=qkv.dtype, device=qkv.device)
         ops.attention(q, o, cache.k, cache.v, step, cache.group, nh, self.num_kv_heads, hd,
                       cache.page_size, self.window, self.scale)
-        return ops.linear(o, self.w_o, self.b_o)
+        return ops.linear(o, self.w_o, self.b_o, partial_ok=self.partial_output)
 
 
 register_mixer("attention", Attention)

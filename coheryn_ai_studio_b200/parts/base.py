@@ -111,6 +111,10 @@ class Part:
 
 
 class Mixer(Part):
+    # Set by the model when every norm takes partial sums: the part may then return its output
+    # as a float32 stack [splits, T, H] whose sum is the output (see Norm.accepts_partial_sums).
+    partial_output = False
+
     def cache_requirement(self):
         """PagedKV, FixedState or None."""
         return None
@@ -120,11 +124,17 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    partial_output = False   # as for Mixer
+
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Norm(Part):
+    # True if ``delta`` may also be a float32 stack [splits, T, H] of partial sums, which the
+    # norm adds in order before it adds them to the residual.
+    accepts_partial_sums = False
+
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError

@@ -40,6 +40,13 @@ class DecoderModel:
                 raise ValueError(f"no arrangement {ls.arrangement!r} is registered") from None
             self.layers.append(arr(mixer, ff, n1, n2))
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, runtime)
+        # Outputs go from a layer to the NEXT norm (the following layer's, or the final one),
+        # so partial sums may flow only if every norm of the model can add them.
+        norms = [n for layer in self.layers for n in (layer.mixer_norm, layer.feed_forward_norm)] + [self.final_norm]
+        if all(n.accepts_partial_sums for n in norms):
+            for layer in self.layers:
+                layer.mixer.partial_output = True
+                layer.feed_forward.partial_output = True
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.status = None

@@ -16,6 +16,8 @@ from .base import Norm, Runtime, register_norm
 
 
 class RMSNorm(Norm):
+    accepts_partial_sums = True
+
     def __init__(self, runtime: Runtime, size: int, eps: float):
         super().__init__(runtime)
         self.size, self.eps = int(size), float(eps)

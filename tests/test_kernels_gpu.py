@@ -34,6 +34,34 @@ def test_embed_gather(table_dtype):
     assert status.item() == 1
 
 
+@pytest.mark.parametrize("H", [72, 1536, 3000, 1537])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("splits", [1, 3, 12])
+def test_add_rmsnorm_takes_partial_sums(H, dtype, splits):
+    """The delta as a float32 stack of partial sums: added in order, then to the residual."""
+    rng = np.random.default_rng(H + splits)
+    resid = rng.standard_normal((5, H)).astype(np.float32) * 3
+    parts = rng.standard_normal((splits, 5, H)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    total = parts[0].copy()
+    for z in range(1, splits):
+        total = total + parts[z]            # float32, in order
+    x = resid + total
+    ref = plain.rms_norm(x, w, 1e-5)
+    tol = 2e-6 * np.abs(ref).max() if dtype == torch.float32 else 2 ** -8 * np.abs(ref).max()
+    r_dev = t32(resid)
+    out = torch.empty(5, H, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(r_dev, t32(parts), t32(w), 1e-5, out)
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
+    assert np.abs(r_dev.cpu().numpy() - x).max() == 0.0
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    r_dev = t32(resid)
+    out2 = torch.empty(2, H, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(r_dev, t32(parts), t32(w), 1e-5, out2, rows=rows)
+    assert np.abs(out2.float().cpu().numpy() - ref[[4, 1]]).max() <= tol
+    assert torch.equal(r_dev, t32(resid))
+
+
 @pytest.mark.parametrize("H", [72, 1536, 3000])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(H, dtype):
@@ -114,6 +142,59 @@ def test_gemm_bf16_small(shape, gated):
     with pytest.raises(Exception, match="multiples of 8"):
         ops().gemm_bf16_small(x[:, :K - 4].contiguous(), w[:, :K - 4].contiguous(), None,
                               torch.empty(M, N // 2 if gated else N, dtype=torch.float32, device=DEV), gated=gated)
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 1536), (8, 2048, 1536), (16, 17920, 1536), (5, 100, 72), (9, 50, 40),
+                                   (17, 1536, 8960), (33, 300, 520), (64, 1536, 1536), (64, 151936, 64),
+                                   (40, 2048, 1536), (3, 1000, 96), (2, 136, 4104)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_gemm_bf16_tc_few(shape, gated):
+    """The few-rows tcgen05 kernel (features on the accumulator's lanes, K split over CTAs
+    with an ordered reduction) against float64, with tails in N and K; twice in a row (the
+    split counters reset themselves), and a row's result must not depend on the batch."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    x = t32(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
+    w = t32((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
+    acc = x.double().cpu() @ w.double().cpu().T
+    if gated:
+        g, u = acc[:, 0::2], acc[:, 1::2]
+        ref = g / (1 + torch.exp(-g)) * u
+        out = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_tc_few(x, w, None, out, gated=True)
+        ops().check_tc_status(DEV)
+        assert (out.double().cpu() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max()) + 1e-3
+        again = torch.full_like(out, 3.0)
+        ops().gemm_bf16_tc_few(x, w, None, again, gated=True)
+        assert torch.equal(out, again)
+    else:
+        b = t32(rng.standard_normal(N).astype(np.float32))
+        ref = acc + b.double().cpu()
+        out = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc_few(x, w, b, out)
+        ops().check_tc_status(DEV)
+        assert (out.double().cpu() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+        outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_tc_few(x, w, None, outb)
+        assert (outb.double().cpu() - acc).abs().max() <= 2 ** -7 * max(1.0, acc.abs().max())
+        # a strided input (a column slice of a wider buffer, 16-byte aligned)
+        wide = torch.zeros(M, K + 16, dtype=torch.bfloat16, device=DEV)
+        wide[:, 8:8 + K] = x
+        out2 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc_few(wide[:, 8:8 + K], w, b, out2)
+        assert torch.equal(out, out2)
+        # the last row alone: the same bits as inside the batch
+        alone = torch.empty(1, N, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc_few(x[M - 1:], w, b, alone)
+        assert torch.equal(alone[0], out[M - 1])
+        # the K slices' sums left to the consumer
+        S = ops().few_splits(N, K)
+        parts = torch.full((S, M, N), 7.0, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc_few(x, w, b, parts, defer=True)
+        assert (parts.double().sum(0).cpu() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+        if S > 1 and K >= ops().DEFER_MIN_K and M <= ops().FEW_M:
+            assert torch.equal(ops().linear(x, w, b, partial_ok=True), parts)
+    ops().check_tc_status(DEV)
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 64), (65, 32, 8), (200, 300, 136), (300, 1000, 96), (257, 96, 1000),
@@ -289,6 +370,40 @@ def test_attention_finds_a_far_key(dtype):
         for h in range(nh):
             hit = np.abs(got[0, h * hd:(h + 1) * hd] - vs[0][target, h // (nh // nkv)]).max() < 0.05
             assert hit == inside, (target, window, h)
+
+
+@pytest.mark.parametrize("split", [128, 256, 512, 0])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 64), (3, 1, 32, 16), (14, 2, 64, 8)])
+def test_decode_attention_split_sizes(split, nh, nkv, hd, page):
+    """The decode kernel at each of its split sizes: lengths around tile (64) and split edges,
+    two-token tails, and windows that begin inside a tile and inside a split."""
+    rng = np.random.default_rng(split + hd)
+    lens = [1, 63, 64, 65, 129, 511, 512, 513, 700, 1300]
+    dtype = torch.bfloat16
+    kc, vc, bt, ks, vs = paged_setup(rng, lens, nkv, hd, page, dtype)
+    q_lens = [1, 1, 1, 2, 1, 1, 2, 1, 1, 1] if (nh // nkv) * 2 <= 16 else [1] * len(lens)
+    reqs, poss = [], []
+    for b, (n, ql) in enumerate(zip(lens, q_lens)):
+        ql = min(ql, n)
+        q_lens[b] = ql
+        reqs += [b] * ql
+        poss += list(range(n - ql, n))
+    T = len(reqs)
+    q = torch.from_numpy(rng.standard_normal((T, nh * hd)).astype(np.float32)).to(dtype).to(DEV)
+    scale = 1.0 / np.sqrt(hd)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    ops().set_attention_split(hd, split)
+    try:
+        for window in (None, 100, 333, 640):
+            out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+            ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
+                                 nh, nkv, hd, page, window, scale, cu_q=t32(cu), kv_lens=t32(np.asarray(lens, np.int32)),
+                                 q_lens=q_lens, max_kv_len=max(lens))
+            ref = attention_reference(q.float().cpu().numpy(), ks, vs, reqs, poss, nh, nkv, hd, window, scale)
+            tol = 2 ** -8 * np.abs(ref) + 2 ** -8
+            assert np.all(np.abs(out.float().cpu().numpy() - ref) <= tol), window
+    finally:
+        ops().set_attention_split(hd, 0)
 
 
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (3, 1, 32, 32), (5, 5, 48, 48), (2, 1, 64, 32)])
