@@ -37,6 +37,7 @@ class _Group:
 @dataclass
 class _Request:
     slot: int
+    serial: int = 0                      # unique per admission: tells a re-admitted id from the old one
     length: int = 0                      # tokens whose keys/values are committed
     tokens: List[int] = field(default_factory=list)    # committed + reserved token ids
     tables: List[List[int]] = field(default_factory=list)   # per group: page per block, -1 once given back
@@ -80,6 +81,7 @@ class CacheManager:
                                    dtype=dtype, device=device)
         self.slots = SlotPool(max_requests)
         self.requests: Dict[str, _Request] = {}
+        self._admissions = 0
         self.prefix_reuse = bool(prefix_reuse) and not self._state and all(
             g.need.window is None for g in self.groups)
 
@@ -119,7 +121,8 @@ class CacheManager:
             return None
         for st in self._state.values():
             st[slot].zero_()
-        r = _Request(slot=slot, tables=[[] for _ in self.groups])
+        self._admissions += 1
+        r = _Request(slot=slot, serial=self._admissions, tables=[[] for _ in self.groups])
         self.requests[req_id] = r
         if prompt is not None and self.prefix_reuse and self.groups and len(prompt) > 1:
             limit = (len(prompt) - 1) // self.page_size
@@ -183,6 +186,10 @@ class CacheManager:
 
     def state_slot(self, req_id: str) -> int:
         return self.requests[req_id].slot
+
+    def serial(self, req_id: str) -> int:
+        """A number unique to this admission of the request."""
+        return self.requests[req_id].serial
 
     def commit(self, req_id: str) -> None:
         """The reserved tokens' keys and values are written: advance the length, hash the

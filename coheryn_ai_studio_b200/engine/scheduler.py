@@ -36,7 +36,7 @@ class RequestRefused(ValueError):
     """The request can never run on this engine."""
 
 
-@dataclass
+@dataclass(eq=False)     # a request is itself: lists of requests compare by identity
 class Request:
     request_id: str
     prompt: List[int]
@@ -54,6 +54,19 @@ class Request:
     @property
     def tokens(self) -> List[int]:
         return self.prompt + self.output
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def token_slice(self, start: int, stop: int) -> List[int]:
+        """tokens[start:stop] without building the whole list."""
+        n = len(self.prompt)
+        if stop <= n:
+            return self.prompt[start:stop]
+        if start >= n:
+            return self.output[start - n:stop - n]
+        return self.prompt[start:] + self.output[:stop - n]
 
     @property
     def finished(self) -> bool:
@@ -129,20 +142,23 @@ class Scheduler:
 
         def fits(req: Request, n: int) -> bool:
             need = self.cache.pages_needed(req.request_id, n)
+            if not any(need):
+                return True
             avail = self.cache.available_pages()
             return all(r + x <= a for r, x, a in zip(reserved, need, avail))
 
         def take(req: Request, n: int) -> None:
             for i, x in enumerate(self.cache.pages_needed(req.request_id, n)):
                 reserved[i] += x
-            toks = req.tokens[req.num_computed:req.num_computed + n]
-            plan.append(Scheduled(req, toks, req.num_computed + n == len(req.prompt) + len(req.output)))
+            toks = req.token_slice(req.num_computed, req.num_computed + n)
+            plan.append(Scheduled(req, toks, req.num_computed + n == req.num_tokens))
 
         # running requests, oldest first
+        preempted_ids = set()
         for req in sorted(self.running, key=lambda r: r.arrival):
-            if req not in self.running or budget == 0:      # preempted below, or nothing left
+            if budget == 0 or req.request_id in preempted_ids:      # nothing left, or preempted below
                 continue
-            n = min(len(req.tokens) - req.num_computed, budget)
+            n = min(req.num_tokens - req.num_computed, budget)
             while not fits(req, n):
                 planned = {s.request.request_id for s in plan}
                 victims = [r for r in self.running if r is not req and r.request_id not in planned]
@@ -150,7 +166,9 @@ class Scheduler:
                     # Nobody left to preempt: run the part of the portion that fits.
                     n = self._largest_fit(req, n, reserved)
                     break
-                self._preempt(max(victims, key=lambda r: r.arrival))
+                victim = max(victims, key=lambda r: r.arrival)
+                preempted_ids.add(victim.request_id)
+                self._preempt(victim)
             if n == 0:
                 continue
             take(req, n)
@@ -165,7 +183,7 @@ class Scheduler:
             if reused is None:
                 break
             req.num_computed = reused
-            n = min(len(req.tokens) - req.num_computed, budget)
+            n = min(req.num_tokens - req.num_computed, budget)
             if not fits(req, n):
                 # Beside running requests a newcomer waits for room for its whole first
                 # portion; alone it starts with what fits.

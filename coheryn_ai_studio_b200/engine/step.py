@@ -85,17 +85,34 @@ class _DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.launches = 0
+        self.bound = [[(None, 0)] * B for _ in range(groups)]     # per group and row: (request, pages written)
+        self.windowed = [g.need.window is not None for g in runner.cache.groups]
 
-    def fill(self, lay: _Layout) -> None:
+    def fill(self, lay: _Layout, serials: Sequence[int]) -> None:
+        """Write the batch into the pinned buffer and copy it to the device.  A row whose
+        request (the same admission: ``serials``) sat there in the last step too only gets the
+        pages it has gained since: block tables grow at the end and keep what they held.  (A window that
+        gives pages back marks them -1 in place: such rows are written whole.)"""
         h = self.h
         h["ids"][:] = lay.ids; h["pos"][:] = lay.pos; h["req"][:] = lay.req; h["cu"][:] = lay.cu
         h["kv_lens"][:] = lay.kv_lens; h["state_slots"][:] = lay.state_slots; h["rows"][:] = lay.rows
         for g, lists in enumerate(lay.tables):
             tab = h[f"table{g}"].reshape(self.B, self.width)
+            known = self.bound[g]
             for b, pages in enumerate(lists):
-                tab[b, :len(pages)] = pages
+                n = len(pages)
+                rid, have = known[b]
+                if rid == serials[b] and have <= n and not self.windowed[g]:
+                    if have < n:
+                        tab[b, have:n] = pages[have:]
+                else:
+                    tab[b, :n] = pages
+                known[b] = (serials[b], n)
             h[f"slots{g}"][:] = lay.slots[g]
         self.dev.copy_(self.host, non_blocking=True)
+
+    def forget_rows(self) -> None:
+        self.bound = [[(None, 0)] * self.B for _ in self.bound]
 
     def run(self, runner: "StepRunner") -> torch.Tensor:
         if self.graph is None:
@@ -180,6 +197,18 @@ class StepRunner:
         q_lens = [len(e.tokens) for e in entries]
         starts = [cache.length(e.request_id) for e in entries]
         T = sum(q_lens)
+        if T == B:       # one token each (decoding): no per-request arrays
+            ar = np.arange(B + 1, dtype=np.int32)
+            st = np.asarray(starts, np.int32)
+            rows = [b for b, e in enumerate(entries) for _ in e.want]
+            groups = range(len(cache.groups))
+            return _Layout(
+                B=B, T=T, ids=np.asarray([e.tokens[0] for e in entries], np.int32), pos=st, req=ar[:B], cu=ar,
+                kv_lens=st + 1, state_slots=np.asarray([cache.state_slot(e.request_id) for e in entries], np.int32),
+                rows=np.asarray(rows, np.int32),
+                tables=[[cache.block_table(e.request_id, g) for e in entries] for g in groups],
+                slots=[np.asarray([cache.slot_ids(e.request_id, g)[0] for e in entries], np.int32) for g in groups],
+                q_lens=q_lens)
         ids = np.empty(T, np.int32); pos = np.empty(T, np.int32); req = np.empty(T, np.int32)
         cu = np.zeros(B + 1, np.int32)
         rows: List[int] = []
@@ -245,7 +274,7 @@ class StepRunner:
                 g = self._graphs.get(lay.B)
                 if g is None:
                     g = self._graphs[lay.B] = _DecodeGraph(self, lay.B)
-                g.fill(lay)
+                g.fill(lay, [self.cache.serial(e.request_id) for e in entries])
                 self.h2d_bytes += g.host.numel() * 4
                 logits = g.run(self)
             else:
@@ -254,6 +283,8 @@ class StepRunner:
         except Exception:
             for e in entries:
                 self.cache.rollback(e.request_id)
+            for g in self._graphs.values():       # rolled-back pages may come back as others
+                g.forget_rows()
             raise
         for e in entries:
             self.cache.commit(e.request_id)
