@@ -286,9 +286,12 @@ CO_EXPORT int coheryn_gemm_bf16_tc_few(const void* x, const void* w, const void*
 #define GO(BT_, ST_) return launch_few<BT_, ST_>(mw, mx, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, workspace, splits, defer, stream)
   // One CTA per SM at most: a deeper ring keeps more of the stream in flight (and still leaves
   // room beside it for the next product's CTAs to fetch their first tiles early).
-  if (bt == 16 && (long)((N + BF - 1) / BF) * splits <= 148) GO(16, 7);
+  const bool one_wave = (long)((N + BF - 1) / BF) * splits <= 148;
+  if (bt == 16 && one_wave) GO(16, 7);
   if (bt == 16) GO(16, 5);
+  if (bt == 32 && one_wave) GO(32, 7);
   if (bt == 32) GO(32, 5);
+  if (one_wave) GO(64, 7);
   GO(64, 4);
 #undef GO
 }

@@ -362,7 +362,9 @@ def gemm_bf16_tc_few(x, w, bias, out, gated: bool = False, defer: bool = False) 
 # split, or whose consumer adds the splits (0 switches it off).  A product that would have to
 # add its own splits goes to the mma.sync kernel instead: measured on a B200, the in-kernel
 # addition through memory costs several dependent round trips.
-FEW_M = int(os.environ.get("COHERYN_FEW_M", "16"))
+FEW_M = int(os.environ.get("COHERYN_FEW_M", "32"))
+# ... and up to this many rows the products whose K slices the consumer adds.
+FEW_DEFER_M = int(os.environ.get("COHERYN_FEW_DEFER_M", "64"))
 
 
 # A product hands its K slices to the consumer only from this K on.  Measured on a B200 at 8
@@ -377,8 +379,8 @@ def _few_ok(x, w, partial_ok: bool = False) -> bool:
     return partial_ok or few_splits(w.shape[0], w.shape[1]) == 1
 
 
-def _few_shape_ok(x, w) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= FEW_M
+def _few_shape_ok(x, w, limit: Optional[int] = None) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= (FEW_M if limit is None else limit)
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0)
 
@@ -433,7 +435,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     result may come as a float32 stack [splits, M, N] of partial sums whose addition is left
     to the consumer (``add_rmsnorm`` takes such a stack as its delta)."""
     M, N = x.shape[0], w.shape[0]
-    if partial_ok and out is None and M and w.shape[1] >= DEFER_MIN_K and _few_shape_ok(x, w):
+    if partial_ok and out is None and M and w.shape[1] >= DEFER_MIN_K and _few_shape_ok(x, w, FEW_DEFER_M):
         splits = few_splits(N, w.shape[1])
         if splits > 1:
             parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)

@@ -192,7 +192,7 @@ def test_gemm_bf16_tc_few(shape, gated):
         parts = torch.full((S, M, N), 7.0, dtype=torch.float32, device=DEV)
         ops().gemm_bf16_tc_few(x, w, b, parts, defer=True)
         assert (parts.double().sum(0).cpu() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
-        if S > 1 and K >= ops().DEFER_MIN_K and M <= ops().FEW_M:
+        if S > 1 and K >= ops().DEFER_MIN_K and M <= ops().FEW_DEFER_M:
             assert torch.equal(ops().linear(x, w, b, partial_ok=True), parts)
     ops().check_tc_status(DEV)
 
