@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <stdlib.h>
 
+#include "attention_tc.h"
 #include "common.cuh"
 
 #ifndef CO_HEAD_DIM
@@ -795,12 +796,14 @@ CO_EXPORT long coheryn_attn_scratch_floats(int B, int nkv, int max_kv_len) {
 
 // q: [T, nh*HD] rows of stride q_stride; out likewise.  Caches: [page][kv head][slot][HD].
 // cu_q [B+1], kv_lens [B] on the device.  Host hints: max_rows = the largest q_len*G of the
-// batch, any_small / any_large = whether some request has <= 16 / > 16 rows, max_kv_len.
+// batch, any_small / any_large = whether some request has <= 16 / > 16 rows, max_kv_len,
+// total_tokens = T, num_pages = pages per cache tensor.
 CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                                      const void* v_cache, const int* block_tables, int max_blocks, const int* cu_q,
                                      const int* kv_lens, int B, int nh, int nkv, int page_size, int window,
                                      float scale, int max_rows, int any_small, int any_large, int max_kv_len,
-                                     float* scratch, long scratch_floats, int* status, cudaStream_t stream) {
+                                     float* scratch, long scratch_floats, int* status, int total_tokens,
+                                     int num_pages, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nkv <= 0 || nh % nkv) CO_FAIL("attention_bf16: %d heads do not group over %d kv heads", nh, nkv);
   if ((q_stride & 7) || (out_stride & 3) || ((uintptr_t)out & 7))
@@ -814,17 +817,25 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
   const bool split_path = any_small && G <= 16 &&
                           (max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1 <= 512;   // attn_combine keeps 512 factors
   if (any_large || (any_small && !split_path)) {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES_SMEM);
-      if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", TILES_SMEM, cudaGetErrorString(e));
-      configured = true;
+    // Prompt portions: the tcgen05 kernel where it takes the shape, else the mma.sync one.
+    if (status && coheryn_attention_tc_takes(nh, nkv, page_size) && ((uintptr_t)out & 7) == 0) {
+      if (coheryn_attention_tc_launch(q, q_stride, total_tokens, out, out_stride, k_cache, v_cache, num_pages, block_tables,
+                                      max_blocks, cu_q, kv_lens, B, nh, nkv, page_size, window, scale_log2, max_rows,
+                                      split_path ? 1 : 0, status, stream))
+        return -1;
+    } else {
+      static bool configured = false;
+      if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILES_SMEM);
+        if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", TILES_SMEM, cudaGetErrorString(e));
+        configured = true;
+      }
+      dim3 grid((max_rows + BM - 1) / BM, nkv, B);
+      co_launch(attn_tiles_kernel, grid, dim3(128 * KG), TILES_SMEM, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+                (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
+                window, scale_log2, split_path ? 1 : 0);
+      CO_CHECK_LAUNCH("attn_tiles");
     }
-    dim3 grid((max_rows + BM - 1) / BM, nkv, B);
-    co_launch(attn_tiles_kernel, grid, dim3(128 * KG), TILES_SMEM, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
-              (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
-              window, scale_log2, split_path ? 1 : 0);
-    CO_CHECK_LAUNCH("attn_tiles");
   }
   if (split_path)
     return launch_stream(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B, nh,

@@ -169,7 +169,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
         raise BuildError(f"the bfloat16 attention kernels take head sizes 16..256 in steps "
                          f"of 16, not {head_dim}")
-    return load_library(f"attn_hd{head_dim}", ["attention_bf16.cu", "runtime.cu"],
+    return load_library(f"attn_hd{head_dim}", ["attention_bf16.cu", "attention_tc.cu", "runtime.cu"],
                         {"CO_HEAD_DIM": head_dim})
 
 
@@ -177,6 +177,6 @@ def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     """Compile everything ahead of time (no GPU needed)."""
     paths = [build_library("core", CORE_SOURCES)]
     for hd in head_dims:
-        paths.append(build_library(f"attn_hd{hd}", ["attention_bf16.cu", "runtime.cu"],
+        paths.append(build_library(f"attn_hd{hd}", ["attention_bf16.cu", "attention_tc.cu", "runtime.cu"],
                                    {"CO_HEAD_DIM": hd}))
     return paths

@@ -290,7 +290,7 @@ def check_tc_status(device) -> None:
     if code:
         tc_status(device).zero_()
         raise KernelError(f"a kernel gave up a bounded wait (code {code}: gemm_bf16_tc 11 producer, 12 MMA issuer, "
-                          "13 epilogue; 21 attention bulk copy)")
+                          "13 epilogue; 31-39 attention_tc: 31 producer, 32-36 MMA issuer, 37-39 softmax)")
 
 
 def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
@@ -518,7 +518,8 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
         _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_q), _ptr(kv_lens), c_int(B),
         c_int(num_heads), c_int(num_kv_heads), c_int(page_size), c_int(window or 0), c_float(scale),
         c_int(max(rows)), c_int(1 if any_small else 0), c_int(1 if any_large else 0), c_int(max_kv_len),
-        _ptr(scratch), c_long(floats), _ptr(tc_status(q.device)), _stream()))
+        _ptr(scratch), c_long(floats), _ptr(tc_status(q.device)), c_int(q.shape[0]), c_int(k_cache.shape[0]),
+        _stream()))
 
 
 def gated_silu_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:

@@ -372,6 +372,36 @@ def test_attention_finds_a_far_key(dtype):
             assert hit == inside, (target, window, h)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 16), (4, 1, 64, 8), (8, 8, 128, 64), (6, 2, 64, 128),
+                                            (16, 1, 128, 256), (3, 1, 192, 32), (2, 1, 256, 16)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window):
+    """Prompt portions through the tcgen05 kernel (S and O in tensor memory, P fed back from
+    it): whole prompts and tails that start inside a key tile, several key tiles, row tiles
+    that end inside a token group, a window that begins inside a tile."""
+    rng = np.random.default_rng(nh + hd + page)
+    lens = [300, 700, 129, 64]
+    q_lens = [300, 257, 20, 64]
+    kc, vc, bt, ks, vs = paged_setup(rng, lens, nkv, hd, page, torch.bfloat16)
+    reqs, poss = [], []
+    for b, (n, ql) in enumerate(zip(lens, q_lens)):
+        reqs += [b] * ql
+        poss += list(range(n - ql, n))
+    T = len(reqs)
+    q = torch.from_numpy(rng.standard_normal((T, nh * hd)).astype(np.float32)).to(torch.bfloat16).to(DEV)
+    scale = 1.0 / np.sqrt(hd)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    out = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
+                         nh, nkv, hd, page, window, scale, cu_q=t32(cu), kv_lens=t32(np.asarray(lens, np.int32)),
+                         q_lens=q_lens, max_kv_len=max(lens))
+    ops().check_tc_status(DEV)
+    ref = attention_reference(q.float().cpu().numpy(), ks, vs, reqs, poss, nh, nkv, hd, window, scale)
+    tol = 2 ** -8 * np.abs(ref) + 2 ** -8
+    err = np.abs(out.float().cpu().numpy() - ref)
+    assert np.all(err <= tol), (float(err.max()), np.argwhere(err > tol)[:5].tolist())
+
+
 @pytest.mark.parametrize("split", [128, 256, 512, 0])
 @pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 64), (3, 1, 32, 16), (14, 2, 64, 8)])
 def test_decode_attention_split_sizes(split, nh, nkv, hd, page):
