@@ -11,10 +11,11 @@
 //   warp 1     MMA issuer: S = Q K^T into tensor memory (tcgen05.mma, both operands K-major in
 //              shared memory), and O += P V with P read from tensor memory and V in shared
 //              memory as it lies in the cache (positions x head dim: operand B MN-major);
-//   warps 2-5  softmax: thread = row.  It reads its row of S, tracks the running maximum in
-//              the log2 domain, turns the row into probabilities (float32), writes them as
-//              bfloat16 pairs into tensor memory for the next MMA, and rescales its row of O
-//              when the maximum moved.  At the end it divides by the sum and stores the row.
+//   warps 2-9  softmax: two threads per row, each with half of the tile's key columns.  They
+//              read their part of S, agree on the row's maximum, turn the scores into
+//              probabilities (float32, log2 domain), write them as bfloat16 pairs into tensor
+//              memory for the next MMA, and rescale their half of the row of O when the
+//              reference maximum moved.  At the end they divide by the sum and store the row.
 // S for the next key tile is issued as soon as the softmax threads hold the current one in
 // registers, so the exponentials overlap the next Q K^T.
 //
@@ -39,9 +40,9 @@ constexpr bool SUPPORTED = HD % 64 == 0 && HD <= 256;
 constexpr int BN = 128;                          // key positions per tile
 constexpr int KCH = SUPPORTED ? HD / 64 : 1;     // 64-column chunks of the head dim
 constexpr int CHUNK_BYTES = 128 * 128;           // 128 rows of 128 bytes
-constexpr int NST = HD <= 128 ? 2 : 1;           // K/V stages
+constexpr int NST = HD <= 128 ? 3 : 1;           // K/V stages
 constexpr int Q_BYTES = KCH * CHUNK_BYTES, KV_BYTES = KCH * CHUNK_BYTES;
-constexpr int SMEM_BYTES = Q_BYTES + NST * 2 * KV_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = Q_BYTES + NST * 2 * KV_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 1024 /* row_ex */;
 constexpr int COL_S = 0, COL_O = 128, COL_P = 128 + HD;
 constexpr int TMEM_COLS = COL_P + 64 <= 256 ? 256 : 512;
 static_assert(!SUPPORTED || SMEM_BYTES <= 227 * 1024, "the stages fit shared memory");
@@ -52,7 +53,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(320, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long out_stride,
                const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
@@ -68,17 +69,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   unsigned long long* v_full = k_full + NST;        // [NST]
   unsigned long long* kv_empty = v_full + NST;      // [NST]
   unsigned long long* s_full = kv_empty + NST;      // MMA -> softmax: S is complete
-  unsigned long long* s_free = s_full + 1;          // softmax -> MMA: S is in registers (128 arrivals)
-  unsigned long long* p_full = s_free + 1;          // softmax -> MMA: P written, O rescaled (128 arrivals)
+  unsigned long long* s_free = s_full + 1;          // softmax -> MMA: S is in registers (256 arrivals)
+  unsigned long long* p_full = s_free + 1;          // softmax -> MMA: P written, O rescaled (256 arrivals)
   unsigned long long* pv_done = p_full + 1;         // MMA -> softmax: O += P V is complete
   unsigned* tmem_slot = (unsigned*)(pv_done + 1);
+  float (*row_ex)[128] = (float (*)[128])((unsigned char*)bars + 256);   // [half][row]: the two threads of a row meet here
   static_assert((5 + 3 * NST) * 8 + 4 <= 256, "barriers fit their slot");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_full, 1); mbar_init(s_free, 128); mbar_init(p_full, 128); mbar_init(pv_done, 1);
+    mbar_init(s_full, 1); mbar_init(s_free, 256); mbar_init(p_full, 256); mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -144,7 +146,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       constexpr unsigned idesc_qk = umma_idesc(128, BN);
-      constexpr unsigned idesc_pv = umma_idesc_b_mn(128, 64);
+      constexpr unsigned idesc_pv = umma_idesc_b_mn(128, HD);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(status, 32);
       auto issue_qk = [&](int j) {
@@ -173,23 +175,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!mbar_wait(&v_full[s], (unsigned)(j / NST) & 1)) { atomicExch(status, 36); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned char* v_src = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
+        // One MMA per 16 positions over the whole head dim: operand B MN-major, its 64-column
+        // chunks CHUNK_BYTES apart (the leading offset), groups of eight positions 1024 bytes
+        // apart (the stride offset).
+        const unsigned long long dv = umma_desc_offsets(v_src, CHUNK_BYTES, 1024);
 #pragma unroll
-        for (int c = 0; c < KCH; ++c) {
-          // MN-major operand: groups of eight positions (rows of 128 bytes) lie 1024 bytes apart = the stride offset
-          const unsigned long long dv = umma_desc_offsets(v_src + c * CHUNK_BYTES, 16, 1024);
-#pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk)   // 16 positions = 16 rows of 128 bytes further per step
-            umma_bf16_a_tmem(tmem_base + COL_O + c * 64, tmem_base + COL_P + kk * 8, dv + (unsigned long long)(kk * 128),
-                             idesc_pv, (j | kk) != 0);
-        }
+        for (int kk = 0; kk < BN / 16; ++kk)   // 16 positions = 16 rows of 128 bytes further per step
+          umma_bf16_a_tmem(tmem_base + COL_O, tmem_base + COL_P + kk * 8, dv + (unsigned long long)(kk * 128), idesc_pv,
+                           (j | kk) != 0);
         umma_commit(&kv_empty[s]);
         umma_commit(pv_done);
         if (NST == 1 && j + 1 < n_tiles) ok = issue_qk(j + 1);
       }
     }
   } else if (n_tiles > 0) {
-    // Softmax warps 2..5: TMEM lane quarter = warp % 4; thread = row.
-    const int quarter = warp & 3;
+    // Softmax warps 2..9: TMEM lane quarter = warp % 4; two threads share a row, warps 2..5
+    // taking key columns 0..63 of every tile (and the first half of the head dim of O), warps
+    // 6..9 the rest.  The pair sits on one scheduler, so one's latencies hide behind the other.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
     const bool valid = row < RT && row_first + row < rows;
@@ -201,52 +204,69 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(s_full, (unsigned)j & 1)) { if (lane == 0) atomicExch(status, 37); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      unsigned sr[4][32];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) tmem_ld32_nowait(lane_addr + COL_S + 32 * i, sr[i]);
+      unsigned sr[2][32];
+      tmem_ld32_nowait(lane_addr + COL_S + half * 64, sr[0]);
+      tmem_ld32_nowait(lane_addr + COL_S + half * 64 + 32, sr[1]);
       tmem_wait_ld();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(s_free);
-      const int key0 = (tile_first + j) * BN;
-      float mx = -INFINITY;
-      if (key0 >= lo && key0 + BN - 1 <= hi) {
+      const int key0 = (tile_first + j) * BN + half * 64;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (key0 >= lo && key0 + 63 <= hi) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 2; ++i)
 #pragma unroll
-          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sr[i][c]));
+          for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[i][c]));
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 2; ++i)
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int key = key0 + i * 32 + c;
             if (key < lo || key > hi) sr[i][c] = __float_as_uint(-INFINITY);
-            mx = fmaxf(mx, __uint_as_float(sr[i][c]));
+            mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[i][c]));
           }
       }
-      const float m_new = fmaxf(m, mx * scale_log2);           // scale > 0 keeps the order
+      // The row's maximum over both halves, through shared memory: the pair of warps meets
+      // once to publish and once more before the slots are written again.
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      row_ex[half][row] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      mx = fmaxf(mx, row_ex[half ^ 1][row]);
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      // The exponent's reference point m follows the running maximum LAZILY: it moves only when
+      // some row of the warp has outgrown it by more than 2^8 (p then stays below 256, far inside
+      // bfloat16's range), because moving it costs a pass over the row of O in tensor memory.
+      // Both threads of a row see the same numbers and decide alike.
+      const float m_row = fmaxf(m, mx * scale_log2);            // scale > 0 keeps the order
+      const bool move = m == -INFINITY ? m_row != -INFINITY : m_row - m > 8.0f;
+      const bool moved = __any_sync(0xffffffffu, move);
+      const float m_new = moved ? m_row : m;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;    // everything masked so far: every p is zero
       const float corr = ex2_approx(m - m_use);
-      float sum = 0.f;
-      unsigned pr[2][32];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned pr[32];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          sr[i][c] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(sr[i][c]), scale_log2, -m_use)));
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i][c]), scale_log2, -m_use));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i][c + 1]), scale_log2, -m_use));
-          sum += p0 + p1;
+          const float p0 = __uint_as_float(sr[i][c]), p1 = __uint_as_float(sr[i][c + 1]);
+          sum4[(c >> 1) & 3] += p0 + p1;
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          pr[i >> 1][(i & 1) * 16 + (c >> 1)] = *reinterpret_cast<unsigned*>(&h);
+          pr[i * 16 + (c >> 1)] = *reinterpret_cast<unsigned*>(&h);
         }
-      l = l * corr + sum;
+      }
+      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m = m_new;
       if (j > 0) {
         if (!mbar_wait(pv_done, (unsigned)(j - 1) & 1)) { if (lane == 0) atomicExch(status, 38); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, corr != 1.f)) {
+        if (moved) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < HD; c0 += 32) {
+          for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
             unsigned o[32];
             tmem_ld32(lane_addr + COL_O + c0, o);
 #pragma unroll
@@ -255,8 +275,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
         }
       }
-      tmem_st32(lane_addr + COL_P, pr[0]);
-      tmem_st32(lane_addr + COL_P + 32, pr[1]);
+      tmem_st32(lane_addr + COL_P + half * 32, pr);
       tmem_wait_st();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(p_full);
@@ -265,12 +284,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (!mbar_wait(pv_done, (unsigned)(n_tiles - 1) & 1)) { if (lane == 0) atomicExch(status, 39); ok = false; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
+    // The row's sum: the first half's plus the second's.
+    row_ex[half][row] = l;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
     if (ok) {
-      const float inv = 1.0f / l;
+      const float inv = 1.0f / (row_ex[0][row] + row_ex[1][row]);
       const int rr = row_first + row;
       bf16* orow = out + (size_t)(tok0 + rr / G) * out_stride + (size_t)(kvh * G + rr % G) * HD;
 #pragma unroll 1
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
         unsigned o[32];
         tmem_ld32(lane_addr + COL_O + c0, o);     // warp-collective: invalid rows read too, and skip the store
         if (valid) {
@@ -338,7 +360,7 @@ int coheryn_attention_tc_launch(const void* q, long q_stride, int total_tokens, 
     configured = true;
   }
   dim3 grid((max_rows + RT - 1) / RT, nkv, B);
-  cudaError_t le = co_launch(attn_tc_kernel, grid, dim3(192), (size_t)SMEM_BYTES, stream, mq, mk, mv, (bf16*)out, out_stride,
+  cudaError_t le = co_launch(attn_tc_kernel, grid, dim3(320), (size_t)SMEM_BYTES, stream, mq, mk, mv, (bf16*)out, out_stride,
                              block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows, window,
                              scale_log2, skip_small, rows_per_box, status);
   if (le != cudaSuccess) CO_FAIL("attention_tc: launch failed: %s", cudaGetErrorString(le));
