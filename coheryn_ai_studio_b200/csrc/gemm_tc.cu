@@ -50,7 +50,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   // float32 tile in partial[z]; splitk_reduce_kernel adds the splits in order and finishes.
   const int kt_begin = partial ? blockIdx.z * k_per_split : 0;
   const int k_tiles = partial ? min(k_per_split, (K + BK - 1) / BK - kt_begin) : (K + BK - 1) / BK;
-  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;     // a power of two >= 32
+  constexpr int TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));     // a power of two >= 32
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -66,13 +66,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
   co_pdl_launch_dependents();
-  co_pdl_wait();     // barriers and tensor memory are set up; x is the predecessor's output
-
+  // Barriers and tensor memory are set up.  W depends on no earlier kernel: the producer asks
+  // for the first stages' W tiles before it waits for the predecessor, whose output x is.
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
+      const int head = k_tiles < STAGES ? k_tiles : STAGES;
+      for (int kt = 0; kt < head; ++kt) {
+        mbar_expect_tx(&full[kt], S::STAGE_BYTES);
+        tma_load_2d(tiles + kt * S::STAGE_BYTES + S::A_BYTES, &map_w, (kt_begin + kt) * BK, n0, &full[kt]);
+      }
+      co_pdl_wait();
+      for (int kt = 0; kt < head; ++kt)
+        tma_load_2d(tiles + kt * S::STAGE_BYTES, &map_x, (kt_begin + kt) * BK, m0, &full[kt]);
+      for (int kt = head; kt < k_tiles; ++kt) {
         const int s = kt % STAGES;
-        if (kt >= STAGES && !mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) { atomicExch(status, 11); break; }
+        if (!mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1)) { atomicExch(status, 11); break; }
         unsigned char* a = tiles + s * S::STAGE_BYTES;
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
         tma_load_2d(a, &map_x, (kt_begin + kt) * BK, m0, &full[s]);
@@ -104,6 +112,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       for (int i = threadIdx.x - 64; i < BN; i += 128) bias_s[i] = n0 + i < N ? co_load_any(bias, bias_dtype, n0 + i) : 0.f;
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
+    co_pdl_wait();   // out (and the split workspace) may still be in use by the predecessor
     const bool waited = mbar_wait(accum_full, 0);
     if (!waited && lane == 0) atomicExch(status, 13);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -336,15 +345,27 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
   co_pdl_launch_dependents();
-  co_pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
       long it = 0;   // k-steps issued so far, across tiles
       bool ok = true;
+      // The first tile's first stages: W (which depends on no earlier kernel) before the wait
+      // for the predecessor, x (its output) after it.
+      const int head = k_tiles < STAGES ? k_tiles : STAGES;
+      if (blockIdx.x < num_tiles) {
+        const int m0 = (blockIdx.x % tiles_m) * BM, n0 = (blockIdx.x / tiles_m) * BN;
+        for (int kt = 0; kt < head; ++kt) {
+          mbar_expect_tx(&full[kt], S::STAGE_BYTES);
+          tma_load_2d(tiles + kt * S::STAGE_BYTES + S::A_BYTES, &map_w, kt * BK, n0, &full[kt]);
+        }
+        co_pdl_wait();
+        for (int kt = 0; kt < head; ++kt) tma_load_2d(tiles + kt * S::STAGE_BYTES, &map_x, kt * BK, m0, &full[kt]);
+        it = head;
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        for (int kt = tile == (int)blockIdx.x ? head : 0; kt < k_tiles; ++kt, ++it) {
           const int s = (int)(it % STAGES);
           if (it >= STAGES && !mbar_wait(&empty[s], (unsigned)((it / STAGES) - 1) & 1)) { atomicExch(status, 11); ok = false; break; }
           unsigned char* a = tiles + s * S::STAGE_BYTES;
@@ -381,6 +402,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   } else {
     const int quarter = warp & 3;
     int j = 0;
+    co_pdl_wait();   // out may still be in use by the predecessor
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
       const int acc = j & 1;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
@@ -482,6 +504,10 @@ CO_EXPORT void coheryn_gemm_tc_tune(int bn, int stages) { g_bn = bn; g_stages = 
 static int tile_width(int M, int N) {
   int bn = N >= 192 ? 256 : (N >= 96 ? 128 : (N >= 48 ? 64 : 32));
   const long tiles_m = (M + BM - 1) / BM;
+  // A single wave of 256-wide tiles that leaves SMs idle: 192-wide tiles if they still fit one wave.
+  if (bn == 256 && tiles_m > 1 && tiles_m * ((N + 255) / 256) < 148 && tiles_m * ((N + 191) / 192) <= 148 &&
+      tiles_m * ((N + 191) / 192) > tiles_m * ((N + 255) / 256))
+    bn = 192;
   while (tiles_m == 1 && bn > 128 && (N + bn - 1) / bn < 74) bn >>= 1;
   if (g_bn == 128 && bn > 128) bn = 128;
   return bn;
@@ -532,6 +558,7 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (bn == 256 && g_stages == 3) GO(256, 3);
   if (bn == 128 && g_stages == 3) GO(128, 3);
   if (bn == 256) GO(256, 4);
+  if (bn == 192) GO(192, 4);
   if (bn == 128) GO(128, 6);
   if (bn == 64) GO(64, 8);
   GO(32, 8);

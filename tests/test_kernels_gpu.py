@@ -199,7 +199,8 @@ def test_gemm_bf16_tc_few(shape, gated):
 
 @pytest.mark.parametrize("shape", [(128, 256, 64), (65, 32, 8), (200, 300, 136), (300, 1000, 96), (257, 96, 1000),
                                    (2048, 2048, 1536), (513, 1536, 8960), (130, 151936, 64), (1000, 48, 72),
-                                   (64, 1536, 8960), (40, 2048, 1536), (17, 100, 520), (2304, 17920, 1536)])
+                                   (64, 1536, 8960), (40, 2048, 1536), (17, 100, 520), (2304, 17920, 1536), (2048, 1536, 1536),
+                                   (1000, 1100, 264)])
 @pytest.mark.parametrize("gated", [False, True])
 def test_gemm_bf16_tc(shape, gated):
     """TMA + tcgen05 kernel against float64, with tails in M, N and K."""
