@@ -6,7 +6,7 @@
                 [--stop-token ID]... [--repetition-penalty 1] [--frequency-penalty 0]
                 [--presence-penalty 0] [--dtype bfloat16|float32] [--json]
     coheryn trace MODEL --tokens 1,2,3          teacher-forced logits as JSON Lines
-    coheryn init DIR --config CONFIG.json --seed N [--store bfloat16|float32]
+    coheryn init DIR|FILE.gguf --config CONFIG.json --seed N [--store bfloat16|float32]
     coheryn models inspect MODEL
 
 Options carry the reference's names, defaults and meanings.  ``MODEL`` is a folder with
@@ -83,7 +83,7 @@ def build_parser() -> argparse.ArgumentParser:
     tr.add_argument("--dtype", default="float32", choices=["bfloat16", "float32"])
     tr.add_argument("--device", default="cuda:0")
 
-    init = sub.add_parser("init", help="write a model folder with seeded random weights")
+    init = sub.add_parser("init", help="write a model folder (or one .gguf file) with seeded random weights")
     init.add_argument("dir")
     init.add_argument("--config", required=True, help="a config.json to take the sizes from")
     init.add_argument("--seed", type=int, default=0)
@@ -170,13 +170,13 @@ def cmd_trace(args) -> int:
 def cmd_init(args) -> int:
     import torch
     from .config import architecture_for, read_config_json
-    from .engine import write_random_model
+    from .engine import write_random_gguf, write_random_model
     from .weights import InitPolicy
     obj = read_config_json(args.config)
     config = architecture_for(obj).parse_config(obj)
-    write_random_model(args.dir, config, args.seed,
-                       InitPolicy(args.matrix_std, args.bias_std, args.norm_jitter),
-                       store=torch.bfloat16 if args.store == "bfloat16" else torch.float32)
+    write = write_random_gguf if args.dir.lower().endswith(".gguf") else write_random_model
+    write(args.dir, config, args.seed, InitPolicy(args.matrix_std, args.bias_std, args.norm_jitter),
+          store=torch.bfloat16 if args.store == "bfloat16" else torch.float32)
     print(args.dir)
     return 0
 
@@ -185,9 +185,10 @@ def cmd_inspect(args) -> int:
     import torch
     from .config import load_config
     from .parts import DecoderModel, Runtime
-    from .weights import check_against, index_model_dir
+    from .engine.loading import gguf_rename
+    from .weights import check_against, index_model
     config, spec = load_config(args.model)
-    entries = index_model_dir(args.model)
+    entries = index_model(args.model, gguf_rename(args.model))
     model = DecoderModel(spec, Runtime(torch.bfloat16, torch.device("cpu")))
     check_against(model.tensor_specs(), entries)
     kv = sum(2 * r.num_kv_heads * r.head_dim for r in model.cache_requirements() if hasattr(r, "num_kv_heads"))

@@ -1,10 +1,11 @@
 from .qwen2 import ConfigError, Qwen2Config, qwen2_model_spec, read_config_json
-from .registry import (Architecture, architecture_for, load_config, register_architecture,
+from .registry import (Architecture, GgufFace, architecture_for, architecture_for_gguf, is_gguf, load_config,
+                       register_architecture,
                        registered_architectures, unregister_architecture)
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 __all__ = [
-    "ConfigError", "Qwen2Config", "qwen2_model_spec", "read_config_json", "Architecture",
+    "ConfigError", "GgufFace", "architecture_for_gguf", "is_gguf", "Qwen2Config", "qwen2_model_spec", "read_config_json", "Architecture",
     "architecture_for", "load_config", "register_architecture", "registered_architectures",
     "unregister_architecture", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
 ]

@@ -188,6 +188,96 @@ class Qwen2Config:
         return d
 
 
+# GGUF: metadata keys of general.architecture = "qwen2" and the tensor names
+# (crates/coheryn-engine/src/compat.rs:54-159 for the keys, 161-221 for the tensors).
+_GGUF_KEYS = {
+    "qwen2.block_count": "num_hidden_layers", "qwen2.embedding_length": "hidden_size",
+    "qwen2.feed_forward_length": "intermediate_size", "qwen2.attention.head_count": "num_attention_heads",
+    "qwen2.attention.head_count_kv": "num_key_value_heads", "qwen2.context_length": "max_position_embeddings",
+    "qwen2.rope.freq_base": "rope_theta", "qwen2.attention.layer_norm_rms_epsilon": "rms_norm_eps",
+}
+_GGUF_HEAD_DIM_KEYS = ("qwen2.attention.key_length", "qwen2.attention.value_length", "qwen2.rope.dimension_count")
+_GGUF_LAYER_NAMES = {
+    "attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm",
+    "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
+    "attn_output": "self_attn.o_proj", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj",
+    "ffn_down": "mlp.down_proj",
+}
+_GGUF_TOP_NAMES = {"token_embd": "model.embed_tokens", "output_norm": "model.norm", "output": "lm_head"}
+
+
+def qwen2_config_from_gguf(meta: Dict[str, Any], tensor_names) -> Qwen2Config:
+    """The typed configuration from GGUF metadata.  Keys of the architecture that are not
+    implemented are refused (rope scaling, sliding window, anything else under "qwen2."), as
+    compat.rs:66-89 and 132-146 do; the vocabulary is the tokenizer's token count
+    (compat.rs:96-101), the output is tied when the file holds no "output.weight"."""
+    if meta.get("split.count", 1) not in (0, 1):
+        raise ConfigError("split GGUF files are not read")
+    known = set(_GGUF_KEYS) | set(_GGUF_HEAD_DIM_KEYS)
+    unknown = sorted(k for k in meta if k.startswith("qwen2.") and k not in known)
+    if unknown:
+        raise ConfigError("unimplemented GGUF key(s): " + ", ".join(unknown))
+    d: Dict[str, Any] = {"architectures": [Qwen2Config.architecture], "model_type": "qwen2"}
+    for key, name in _GGUF_KEYS.items():
+        if key in meta:
+            d[name] = meta[key]
+    tokens = meta.get("tokenizer.ggml.tokens")
+    if not isinstance(tokens, list) or not tokens:
+        raise ConfigError("tokenizer.ggml.tokens is required: its length is the vocabulary")
+    d["vocab_size"] = len(tokens)
+    d["tie_word_embeddings"] = "output.weight" not in set(tensor_names)
+    if "tokenizer.ggml.eos_token_id" in meta:
+        d["eos_token_id"] = meta["tokenizer.ggml.eos_token_id"]
+    config = Qwen2Config.from_dict(d)
+    for key in _GGUF_HEAD_DIM_KEYS:
+        if key in meta and meta[key] != config.head_dim:
+            raise ConfigError(f"{key} = {meta[key]!r} differs from the head size {config.head_dim} "
+                              "(partial rotation and separate key/value sizes are not implemented)")
+    return config
+
+
+def qwen2_gguf_tensor_name(name: str) -> str:
+    """GGUF tensor name -> checkpoint (HF) name; names outside the table come back unchanged
+    and are then reported as unexpected."""
+    stem, dot, kind = name.rpartition(".")
+    if not dot or kind not in ("weight", "bias"):
+        return name
+    if stem in _GGUF_TOP_NAMES:
+        return f"{_GGUF_TOP_NAMES[stem]}.{kind}"
+    parts = stem.split(".")
+    if len(parts) == 3 and parts[0] == "blk" and parts[1].isdigit() and parts[2] in _GGUF_LAYER_NAMES:
+        return f"model.layers.{int(parts[1])}.{_GGUF_LAYER_NAMES[parts[2]]}.{kind}"
+    return name
+
+
+def qwen2_gguf_metadata(c: Qwen2Config) -> Dict[str, Any]:
+    """GGUF metadata for a configuration (the random-weights mode): the inverse of
+    ``qwen2_config_from_gguf``, with a placeholder token table of the vocabulary's length."""
+    meta: Dict[str, Any] = {"general.architecture": "qwen2", "general.alignment": 32}
+    for key, name in _GGUF_KEYS.items():
+        meta[key] = getattr(c, name)
+    for key in _GGUF_HEAD_DIM_KEYS:
+        meta[key] = c.head_dim
+    meta["tokenizer.ggml.tokens"] = [f"<{i}>" for i in range(c.vocab_size)]
+    if c.eos_token_ids:
+        meta["tokenizer.ggml.eos_token_id"] = c.eos_token_ids[0]
+    return meta
+
+
+def qwen2_gguf_name_of(hf_name: str) -> str:
+    """Checkpoint (HF) name -> GGUF tensor name (for writing)."""
+    stem, _, kind = hf_name.rpartition(".")
+    for g, h in _GGUF_TOP_NAMES.items():
+        if stem == h:
+            return f"{g}.{kind}"
+    parts = stem.split(".", 3)       # model, layers, i, rest
+    if len(parts) == 4 and parts[:2] == ["model", "layers"]:
+        for g, h in _GGUF_LAYER_NAMES.items():
+            if parts[3] == h:
+                return f"blk.{parts[2]}.{g}.{kind}"
+    raise ConfigError(f"tensor {hf_name} has no GGUF name")
+
+
 def qwen2_model_spec(c: Qwen2Config) -> ModelSpec:
     """Qwen2: every layer is pre-norm residual over GQA attention (q/k/v bias, no o
     bias, rotate-half RoPE over the whole head) and a SwiGLU feed-forward

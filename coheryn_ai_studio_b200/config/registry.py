@@ -10,10 +10,22 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Tuple
+from typing import Any, Callable, Dict, Optional, Tuple
 
-from .qwen2 import ConfigError, Qwen2Config, qwen2_model_spec, read_config_json
+from .qwen2 import (ConfigError, Qwen2Config, qwen2_config_from_gguf, qwen2_gguf_metadata, qwen2_gguf_name_of,
+                    qwen2_gguf_tensor_name, qwen2_model_spec, read_config_json)
 from .spec import ModelSpec
+
+
+@dataclass(frozen=True)
+class GgufFace:
+    """How an architecture reads (and writes) a GGUF file: its ``general.architecture`` id,
+    metadata -> typed config, GGUF tensor name -> checkpoint name, and the two inverses."""
+    name: str
+    parse_metadata: Callable[[Dict[str, Any], Any], Any]
+    tensor_name: Callable[[str], str]
+    metadata_of: Optional[Callable[[Any], Dict[str, Any]]] = None
+    gguf_name_of: Optional[Callable[[str], str]] = None
 
 
 @dataclass(frozen=True)
@@ -21,17 +33,22 @@ class Architecture:
     name: str
     parse_config: Callable[[Dict[str, Any]], Any]   # config.json object -> typed config
     model_spec: Callable[[Any], ModelSpec]          # typed config -> layer layout
+    gguf: Optional[GgufFace] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config, model_spec, *, replace: bool = False) -> None:
+def register_architecture(name: str, parse_config, model_spec, *, gguf: Optional[GgufFace] = None,
+                          replace: bool = False) -> None:
     if not name:
         raise ValueError("an architecture needs a non-empty name")
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = Architecture(name, parse_config, model_spec)
+    if gguf is not None and any(a.gguf is not None and a.gguf.name == gguf.name and a.name != name
+                                for a in _ARCHITECTURES.values()):
+        raise ValueError(f"GGUF architecture {gguf.name!r} is already registered")
+    _ARCHITECTURES[name] = Architecture(name, parse_config, model_spec, gguf)
 
 
 def unregister_architecture(name: str) -> None:
@@ -54,14 +71,36 @@ def architecture_for(config_object: Dict[str, Any]) -> Architecture:
             f"{', '.join(registered_architectures()) or 'none'})") from None
 
 
-def load_config(model_dir: str):
-    """Read ``model_dir/config.json``; return (typed config, ModelSpec)."""
-    obj = read_config_json(os.path.join(model_dir, "config.json"))
-    arch = architecture_for(obj)
-    config = arch.parse_config(obj)
+def is_gguf(model_path: str) -> bool:
+    return os.path.isfile(model_path) and model_path.lower().endswith(".gguf")
+
+
+def architecture_for_gguf(metadata: Dict[str, Any]) -> Architecture:
+    name = metadata.get("general.architecture")
+    for arch in _ARCHITECTURES.values():
+        if arch.gguf is not None and arch.gguf.name == name:
+            return arch
+    known = sorted(a.gguf.name for a in _ARCHITECTURES.values() if a.gguf is not None)
+    raise ConfigError(f"GGUF architecture {name!r} is not registered (registered: {', '.join(known) or 'none'})")
+
+
+def load_config(model_path: str):
+    """Read ``model_path/config.json``, or the metadata of a ``.gguf`` file; return (typed
+    config, ModelSpec)."""
+    if is_gguf(model_path):
+        from ..weights.gguf_io import read_gguf
+        meta, entries = read_gguf(model_path)
+        arch = architecture_for_gguf(meta)
+        config = arch.gguf.parse_metadata(meta, entries.keys())
+    else:
+        obj = read_config_json(os.path.join(model_path, "config.json"))
+        arch = architecture_for(obj)
+        config = arch.parse_config(obj)
     spec = arch.model_spec(config)
     spec.validate()
     return config, spec
 
 
-register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_model_spec)
+register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_model_spec,
+                      gguf=GgufFace("qwen2", qwen2_config_from_gguf, qwen2_gguf_tensor_name,
+                                    qwen2_gguf_metadata, qwen2_gguf_name_of))

@@ -24,16 +24,42 @@ def parse_dtype(name) -> torch.dtype:
         raise ValueError(f"dtype {name!r} is not supported (bfloat16 or float32)") from None
 
 
-def load_model(model_dir: str, dtype="bfloat16", device="cuda:0"):
-    """Read config.json, pick the model by its architecture name, load the weights by
-    tensor name.  Returns (typed config, DecoderModel)."""
+def gguf_rename(model_path: str):
+    """For a ``.gguf`` file the function that turns its tensor names into the checkpoint's."""
+    from ..config.registry import architecture_for_gguf, is_gguf
+    if not is_gguf(model_path):
+        return None
+    from ..weights.gguf_io import read_gguf
+    return architecture_for_gguf(read_gguf(model_path)[0]).gguf.tensor_name
+
+
+def load_model(model_path: str, dtype="bfloat16", device="cuda:0"):
+    """Read config.json of a model folder (or the metadata of a ``.gguf`` file), pick the
+    model by its architecture name, load the weights by tensor name.  Returns (typed config,
+    DecoderModel)."""
     ops.require_gpu()
     runtime = Runtime(parse_dtype(dtype), torch.device(device))
-    config, spec = load_config(model_dir)
+    config, spec = load_config(model_path)
     model = DecoderModel(spec, runtime)
-    tensors = load_tensors(model_dir, model.tensor_specs(), runtime.dtype, runtime.device)
+    rename = gguf_rename(model_path)
+    tensors = load_tensors(model_path, model.tensor_specs(), runtime.dtype, runtime.device, rename=rename)
     model.bind(tensors)
     return config, model
+
+
+def write_random_gguf(path: str, config, seed: int, policy: InitPolicy = InitPolicy(),
+                      store: torch.dtype = torch.bfloat16) -> None:
+    """The random-weights mode as one GGUF file (the same values as ``write_random_model``)."""
+    from ..config.registry import architecture_for
+    from ..weights.gguf_io import write_gguf
+    obj = config.to_dict()
+    arch = architecture_for(obj)
+    if arch.gguf is None or arch.gguf.metadata_of is None:
+        raise ValueError(f"architecture {arch.name} has no GGUF face")
+    typed = arch.parse_config(obj)
+    model = DecoderModel(arch.model_spec(typed), Runtime(store, torch.device("cpu")))
+    tensors = random_tensors(model.tensor_specs(), seed, policy, store=store)
+    write_gguf(path, arch.gguf.metadata_of(typed), [(arch.gguf.gguf_name_of(n), tensors[n]) for n in sorted(tensors)])
 
 
 def write_random_model(model_dir: str, config, seed: int, policy: InitPolicy = InitPolicy(),

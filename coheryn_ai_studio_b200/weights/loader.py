@@ -67,12 +67,27 @@ def check_against(expected: Dict[str, TensorSpec], entries) -> None:
         raise WeightError(sorted(missing), sorted(unexpected), wrong_shape, wrong_dtype)
 
 
-def load_tensors(model_dir: str, expected: Dict[str, TensorSpec], compute: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
+def index_model(model_path: str, rename=None):
+    """Tensor index by checkpoint name of a folder of safetensors, or of a ``.gguf`` file whose
+    tensor names ``rename`` turns into the checkpoint's."""
+    if not os.path.isfile(model_path):
+        return index_model_dir(model_path)
+    from .gguf_io import read_gguf
+    entries = {}
+    for name, e in read_gguf(model_path)[1].items():
+        new = rename(name) if rename is not None else name
+        if new in entries:
+            raise ValueError(f"tensor {name} and another both map to {new}")
+        entries[new] = e
+    return entries
+
+
+def load_tensors(model_path: str, expected: Dict[str, TensorSpec], compute: torch.dtype,
+                 device, rename=None) -> Dict[str, torch.Tensor]:
     """Read every expected tensor, cast it to the dtype it is kept in, move it to
-    ``device``.  Raises :class:`WeightError` before reading any payload if the set of
-    names or any shape is wrong."""
-    entries = index_model_dir(model_dir)
+    ``device`` (``model_path`` and ``rename`` as for :func:`index_model`).  Raises
+    :class:`WeightError` before reading any payload if the set of names or any shape is wrong."""
+    entries = index_model(model_path, rename)
     check_against(expected, entries)
     reader = TensorReader(entries)
     out: Dict[str, torch.Tensor] = {}
