@@ -420,8 +420,17 @@ def norm_linear(resid: torch.Tensor, delta: Optional[torch.Tensor], norm_weight:
     return out, new_resid
 
 
+# ... and up to this many rows when the weight matrix is small (a few MB: the q/k/v and output
+# products of a decode batch), where one launch of the mma.sync kernel beats the tcgen05 kernel
+# plus the kernel that adds its K splits.
+SMALL_M_SHORT = int(os.environ.get("COHERYN_SMALL_M_SHORT", "32"))
+SMALL_WEIGHT_ELEMENTS = 4 << 20
+
+
 def _small_ok(x, w) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SMALL_M
+    M = x.shape[0]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and (0 < M <= SMALL_M or (0 < M <= SMALL_M_SHORT and w.numel() <= SMALL_WEIGHT_ELEMENTS))
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0)
 
