@@ -329,6 +329,127 @@ gemm_small_norm_kernel(const float* __restrict__ resid_in, const __nv_bfloat16* 
   }
 }
 
+// The q/k/v product of a decode batch (at most 16 rows) with the rotation and the cache write
+// in its epilogue, which saves the kernel that would otherwise re-read q/k/v.  A CTA owns 8
+// features of a head's first half and the 8 that pair with them in the second half (two MMA
+// tiles), so that both elements of every rotate-half pair meet in one thread:
+//   q heads: rotated, to q_out[m, head * hd + ...];  k heads: rotated, to the cache slot of
+//   token m;  v heads: as they are, to the cache.
+// The sums (+ bias) are rounded to bfloat16 BEFORE the rotation, as the two-kernel path stores
+// them, so both paths give the same bits.  Rotation in float32 from the (cos, sin) table:
+// out_a = fma(a, cos, -(b sin)), out_b = fma(a, sin, b cos).
+__global__ void __launch_bounds__(512)
+gemm_small_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                       const void* __restrict__ bias, int bias_dtype, __nv_bfloat16* __restrict__ q_out, long ldq,
+                       const int* __restrict__ positions, const float2* __restrict__ cos_sin,
+                       const int* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache,
+                       __nv_bfloat16* __restrict__ v_cache, int M, int K, long ldx, int nh, int nkv, int hd,
+                       int page_size) {
+  extern __shared__ float red[];  // [warps][2 tiles][4][32]
+  constexpr int NT = 2, U = 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int blocks_per_head = hd >> 4, half = hd >> 1;
+  const int head = blockIdx.x / blocks_per_head, jb = blockIdx.x % blocks_per_head;
+  const int row0 = head * hd + jb * 8, row1 = row0 + half;
+  const __nv_bfloat16* wrow[NT] = {w + (size_t)(row0 + g) * K, w + (size_t)(row1 + g) * K};
+  const int nblk = (K + 63) >> 6;
+  uint4 wv[U][NT][2];
+  auto load_w = [&](int blk0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = ((blk0 + u * warps) << 6) + (t << 4);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+          wv[u][nt][p] = (k + 8 * p < K) ? ld_stream(wrow[nt] + k + 8 * p) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  load_w(warp);                  // weights depend on no earlier kernel
+  co_pdl_launch_dependents();
+  co_pdl_wait();                 // x is the predecessor's output
+
+  const bool xok0 = g < M, xok1 = g + 8 < M;
+  const __nv_bfloat16* xr0 = x + (size_t)min(g, M - 1) * ldx;
+  const __nv_bfloat16* xr1 = x + (size_t)min(g + 8, M - 1) * ldx;
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+  for (int blk0 = warp; blk0 < nblk; blk0 += warps * U) {
+    if (blk0 != warp) load_w(blk0);
+    uint4 xa[U][2], xb[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = ((blk0 + u * warps) << 6) + (t << 4);
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        const bool valid = k + 8 * p < K;
+        xa[u][p] = (valid && xok0) ? __ldg((const uint4*)(xr0 + k + 8 * p)) : make_uint4(0, 0, 0, 0);
+        xb[u][p] = (valid && xok1) ? __ldg((const uint4*)(xr1 + k + 8 * p)) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int p = 0; p < 2; ++p)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 a = xa[u][p], b = xb[u][p], c = wv[u][nt][p];
+          mma_bf16(acc[nt], a.x, b.x, a.y, b.y, c.x, c.y);
+          mma_bf16(acc[nt], a.z, b.z, a.w, b.w, c.z, c.w);
+        }
+  }
+  constexpr int E = NT * 4 * 32;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[warp * E + (nt * 4 + i) * 32 + lane] = acc[nt][i];
+  __syncthreads();
+
+  // One thread per (token m, pair j of this CTA's eight): fragment element (row m, column j) of
+  // tile nt sits in lane (m % 8) * 4 + j / 2, register (m / 8) * 2 + (j & 1).
+  for (int e = threadIdx.x; e < M * 8; e += blockDim.x) {
+    const int m = e >> 3, j = e & 7;
+    const int src = ((m >> 3) * 2 + (j & 1)) * 32 + (m & 7) * 4 + (j >> 1);
+    float a = 0.f, b = 0.f;
+    for (int wi = 0; wi < warps; ++wi) {
+      a += red[wi * E + src];
+      b += red[wi * E + 4 * 32 + src];
+    }
+    if (bias) {
+      a += co_load_any(bias, bias_dtype, row0 + j);
+      b += co_load_any(bias, bias_dtype, row1 + j);
+    }
+    a = __bfloat162float(__float2bfloat16_rn(a));
+    b = __bfloat162float(__float2bfloat16_rn(b));
+    const int d = jb * 8 + j;
+    __nv_bfloat16 ra, rb;
+    if (head < nh + nkv) {
+      const float2 c = cos_sin[(size_t)positions[m] * half + d];
+      ra = __float2bfloat16_rn(fmaf(a, c.x, -(b * c.y)));
+      rb = __float2bfloat16_rn(fmaf(a, c.y, b * c.x));
+    } else {
+      ra = __float2bfloat16_rn(a);
+      rb = __float2bfloat16_rn(b);
+    }
+    __nv_bfloat16* dst;
+    if (head < nh) {
+      dst = q_out + (size_t)m * ldq + (size_t)head * hd;
+    } else {
+      const int slot = slots[m];
+      if (slot < 0) continue;
+      const int page = slot / page_size, off = slot - page * page_size;
+      const int kvh = head < nh + nkv ? head - nh : head - nh - nkv;
+      dst = (head < nh + nkv ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+    }
+    dst[d] = ra;
+    dst[d + half] = rb;
+  }
+}
+
 template <int NT>
 int launch_small_norm(const float* resid_in, const void* delta, const void* norm_w, int norm_dtype, float eps,
                       float* resid_out, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
@@ -393,6 +514,33 @@ CO_EXPORT int coheryn_gemm_bf16_small(const void* x, const void* w, const void* 
   if (nt == 2) GO(4, 2);
   GO(4, 1);
 #undef GO
+}
+
+// x: [M, K] bfloat16 rows of stride ldx, M <= 16; w: [(nh + 2 nkv) * hd, K] (q, k, v rows
+// stacked); q_out: [M, nh * hd] rows of stride ldq; caches [page][kv head][slot][hd]; positions
+// and slots per row (slot < 0: nothing is written for that row); cos_sin: float2
+// [max_pos][hd / 2].  The whole head is rotated; hd a multiple of 16, K of 8.
+CO_EXPORT int coheryn_qkv_rope_bf16_small(const void* x, const void* w, const void* bias, int bias_dtype, void* q_out,
+                                          long ldq, const int* positions, const float* cos_sin, const int* slots,
+                                          void* k_cache, void* v_cache, int M, int K, long ldx, int nh, int nkv,
+                                          int hd, int page_size, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 16) CO_FAIL("qkv_rope_bf16_small: M = %d exceeds 16", M);
+  if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("qkv_rope_bf16_small: K = %d and the row stride %ld must be multiples of 8", K, ldx);
+  if (hd <= 0 || (hd & 15) || nh <= 0 || nkv <= 0 || page_size <= 0)
+    CO_FAIL("qkv_rope_bf16_small: head size %d must be a multiple of 16 (heads %d, kv heads %d, page %d)", hd, nh, nkv, page_size);
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("qkv_rope_bf16_small: operands must be 16-byte aligned");
+  const int nblk = (K + 63) / 64;
+  const int warps = nblk >= 64 ? 16 : (nblk >= 8 ? 8 : (nblk >= 4 ? 4 : (nblk >= 2 ? 2 : 1)));
+  const size_t smem = (size_t)warps * 2 * 4 * 32 * sizeof(float);
+  const int grid = (nh + 2 * nkv) * (hd / 16);
+  cudaError_t e = co_launch_ex(true /* x is re-read through L1 */, gemm_small_rope_kernel, dim3(grid), dim3(warps * 32), smem,
+                               stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype,
+                               (__nv_bfloat16*)q_out, ldq, positions, (const float2*)cos_sin, slots,
+                               (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, M, K, ldx, nh, nkv, hd, page_size);
+  if (e != cudaSuccess) CO_FAIL("qkv_rope_bf16_small: launch failed: %s", cudaGetErrorString(e));
+  CO_CHECK_LAUNCH("qkv_rope_small");
+  return 0;
 }
 
 // The product above with the preceding residual-add + RMSNorm folded in, for M <= 16:

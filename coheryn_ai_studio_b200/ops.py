@@ -176,6 +176,40 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Ten
         c_int(rotary_dim), c_int(page_size), c_int(1 if write else 0), _stream()))
 
 
+# Up to this many rows the q/k/v product rotates and writes the cache in its own epilogue.
+QKV_ROPE_M = int(os.environ.get("COHERYN_QKV_ROPE_M", "16"))
+
+
+def qkv_rope_ok(x, w_qkv, k_cache, rotary_dim: int, head_dim: int) -> bool:
+    return (0 < x.shape[0] <= QKV_ROPE_M and x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+            and k_cache is not None and k_cache.dtype == torch.bfloat16 and rotary_dim == head_dim
+            and head_dim % 16 == 0 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w_qkv.is_contiguous() and w_qkv.data_ptr() % 16 == 0)
+
+
+def qkv_rope_small(x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], positions: torch.Tensor,
+                   cos_sin: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> torch.Tensor:
+    """q, k, v = x @ w_qkv.T (+ b) for at most 16 rows with the rotation of q and k and the
+    cache write of k and v in the product's epilogue (see ``rope_kv_write`` for the layout).
+    Returns the rotated q ``[T, num_heads * head_dim]``; the whole head is rotated."""
+    _dev(x, w_qkv, b_qkv, positions, cos_sin, slots, k_cache, v_cache)
+    _i32(positions, "positions"); _i32(slots, "slots")
+    T, K = x.shape
+    assert w_qkv.shape == ((num_heads + 2 * num_kv_heads) * head_dim, K)
+    assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1:] == (head_dim // 2, 2)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+    q = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    lib = core()
+    _check(lib, lib.coheryn_qkv_rope_bf16_small(
+        _ptr(x), _ptr(w_qkv), _ptr(b_qkv), c_int(_code(b_qkv) if b_qkv is not None else F32), _ptr(q),
+        c_long(q.stride(0)), _ptr(positions), _ptr(cos_sin), _ptr(slots), _ptr(k_cache), _ptr(v_cache), c_int(T),
+        c_int(K), c_long(x.stride(0)), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+        _stream()))
+    return q
+
+
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out = x @ w.T (+ bias) with float32 FMA accumulation (no tensor cores)."""
     _dev(x, w, bias, out)

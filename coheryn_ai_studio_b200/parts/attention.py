@@ -64,8 +64,20 @@ class Attention(Mixer):
         self.w_o = tensors["o_proj.weight"]
         self.b_o = tensors.get("o_proj.bias")
 
+    def _fused_rope(self, x: torch.Tensor, cache: LayerCache) -> bool:
+        """Few rows (decoding): the q/k/v product rotates and writes the cache itself."""
+        return (cache.writes and self.position is not None
+                and ops.qkv_rope_ok(x, self.w_qkv, cache.k, self.position.rotary_dim, self.head_dim))
+
+    def _project_rotate_write(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        return ops.qkv_rope_small(x, self.w_qkv, self.b_qkv, step.positions, self.position.cos_sin(),
+                                  step.slots[cache.group], cache.k, cache.v, self.num_heads, self.num_kv_heads,
+                                  self.head_dim, cache.page_size)
+
     def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
         self._check(cache)
+        if self._fused_rope(x, cache):
+            return self._attend_q(self._project_rotate_write(x, step, cache), step, cache)
         if cache.writes:
             qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         else:   # this execution reads keys and values another one wrote: only q is made
@@ -76,6 +88,12 @@ class Attention(Mixer):
         """The same with the preceding norm folded into the q/k/v projection where a kernel
         exists for it; returns (y, residual after the add)."""
         self._check(cache)
+        if (cache.writes and residual.shape[0] <= ops.QKV_ROPE_M and self.position is not None
+                and self.w_qkv.dtype == torch.bfloat16):
+            x = norm.forward(residual, delta)
+            if self._fused_rope(x, cache):
+                return self._attend_q(self._project_rotate_write(x, step, cache), step, cache), residual
+            return self._attend(ops.linear(x, self.w_qkv, self.b_qkv), step, cache), residual
         if cache.writes:
             qkv, residual = norm.fused_linear(residual, delta, self.w_qkv, self.b_qkv)
         else:
@@ -100,8 +118,12 @@ class Attention(Mixer):
         else:
             q = qkv
             ops.rope_kv_write(q, step.positions, cos_sin, None, None, None, nh, 0, hd, rot, cache.page_size)
-        o = torch.empty((T, self.q_size), dtype=qkv.dtype, device=qkv.device)
-        ops.attention(q, o, cache.k, cache.v, step, cache.group, nh, self.num_kv_heads, hd,
+        return self._attend_q(q, step, cache)
+
+    def _attend_q(self, q: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        """Attention of rotated queries over the cache, then the output projection."""
+        o = torch.empty((q.shape[0], self.q_size), dtype=q.dtype, device=q.device)
+        ops.attention(q, o, cache.k, cache.v, step, cache.group, self.num_heads, self.num_kv_heads, self.head_dim,
                       cache.page_size, self.window, self.scale)
         return ops.linear(o, self.w_o, self.b_o, partial_ok=self.partial_output)
 

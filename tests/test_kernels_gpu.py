@@ -403,6 +403,36 @@ def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window):
     assert np.all(err <= tol), (float(err.max()), np.argwhere(err > tol)[:5].tolist())
 
 
+@pytest.mark.parametrize("nh,nkv,hd,K,page", [(12, 2, 128, 1536, 16), (4, 2, 16, 64, 16), (3, 1, 32, 96, 8), (5, 5, 48, 200, 32)])
+@pytest.mark.parametrize("T", [1, 7, 16])
+def test_qkv_product_with_rotation_and_cache_write(nh, nkv, hd, K, page, T):
+    """The decode product that rotates and writes the cache in its epilogue gives the bits of the
+    product followed by the rotation kernel."""
+    rng = np.random.default_rng(nh + hd + T)
+    N = (nh + 2 * nkv) * hd
+    x = t32(rng.standard_normal((T, K)).astype(np.float32)).to(torch.bfloat16)
+    w = t32((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
+    b = t32(rng.standard_normal(N).astype(np.float32))
+    max_pos = 300
+    ang = rng.uniform(0, 6.28, size=(max_pos, hd // 2)).astype(np.float32)
+    cos_sin = t32(np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32))
+    positions = t32(rng.integers(0, max_pos, size=T).astype(np.int32))
+    pages = 40
+    slots_np = rng.permutation(pages * page)[:T].astype(np.int32)
+    if T > 2:
+        slots_np[1] = -1                               # a row that writes nothing
+    slots = t32(slots_np)
+    kc = torch.zeros(pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = ops().qkv_rope_small(x, w, b, positions, cos_sin, slots, kc, vc, nh, nkv, hd, page)
+    qkv = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_bf16_small(x, w, b, qkv)               # the same kernel family: the same order of summation
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    ops().rope_kv_write(qkv, positions, cos_sin, slots, kc2, vc2, nh, nkv, hd, hd, page)
+    assert torch.equal(q, qkv[:, :nh * hd])
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+
+
 @pytest.mark.parametrize("split", [128, 256, 512, 0])
 @pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 64), (3, 1, 32, 16), (14, 2, 64, 8)])
 def test_decode_attention_split_sizes(split, nh, nkv, hd, page):
