@@ -284,10 +284,11 @@ CO_EXPORT int coheryn_gemm_bf16_tc_few(const void* x, const void* w, const void*
   if (!make_map(&mw, w, N, K, K, BF) || !make_map(&mx, x, M, K, ldx, bt))
     CO_FAIL("gemm_bf16_tc_few: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%ld)", M, N, K, ldx);
 #define GO(BT_, ST_) return launch_few<BT_, ST_>(mw, mx, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, workspace, splits, defer, stream)
-  // One CTA per SM at most: a deeper ring keeps more of the stream in flight (and still leaves
-  // room beside it for the next product's CTAs to fetch their first tiles early).
+  // One CTA per SM at most: a deeper ring keeps more of the stream in flight.  Six stages
+  // (111 KB) leave room on the SM for a CTA of the NEXT few-rows product, which then fetches
+  // its first tiles while this one still runs (gate/up followed by down).
   const bool one_wave = (long)((N + BF - 1) / BF) * splits <= 148;
-  if (bt == 16 && one_wave) GO(16, 7);
+  if (bt == 16 && one_wave) GO(16, 6);
   if (bt == 16) GO(16, 5);
   if (bt == 32 && one_wave) GO(32, 7);
   if (bt == 32) GO(32, 5);
