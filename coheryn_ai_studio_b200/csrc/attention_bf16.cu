@@ -487,17 +487,16 @@ constexpr int SPLIT_FLOATS = 16 * HD + 32;
 // into element offsets (one division and one block-table entry from shared memory per row),
 // and the copy loop then moves consecutive 16-byte pieces with consecutive lanes, so a warp
 // instruction covers whole 128-byte lines.
+// Two ring depths are built: three stages (two CTAs per SM at head size 128: the deepest
+// prefetch, for batches whose CTAs all fit the GPU at once) and two stages (three CTAs per SM:
+// more warps to hide each other's latencies, for batches whose CTAs queue up).
 constexpr int STILE = 64;
-#ifndef CO_ATTN_STREAM_STAGES
-#define CO_ATTN_STREAM_STAGES 3
-#endif
-constexpr int SSTAGES = CO_ATTN_STREAM_STAGES;
-constexpr size_t STREAM_SMEM = (size_t)(16 + SSTAGES * 2 * STILE) * LDS * sizeof(bf16);
-static_assert(SSTAGES >= 2, "tile i is worked on while tile i + 1 is copied");
-static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)SSTAGES * 2 * STILE * LDS * sizeof(bf16),
+constexpr size_t stream_smem(int stages) { return (size_t)(16 + stages * 2 * STILE) * LDS * sizeof(bf16); }
+static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)2 * 2 * STILE * LDS * sizeof(bf16),
               "the merge area fits the ring");
-static_assert(STREAM_SMEM + 6 * 1024 <= 227 * 1024, "the ring fits shared memory at every head size");
+static_assert(stream_smem(3) + 6 * 1024 <= 227 * 1024, "the ring fits shared memory at every head size");
 
+template <int SSTAGES>
 __global__ void __launch_bounds__(128)
 attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__ scratch, int max_splits,
                    const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -506,7 +505,7 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
                    int split) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long long rowoff[SSTAGES][STILE];   // element offset of a tile's rows in a cache tensor, -1: not read
-  __shared__ int pages_s[SPLIT_MAX + 2];         // block-table entries of the split's pages
+  __shared__ int pages_s[SPLIT_MAX / 2 + 2];     // block-table entries of the split's pages (pages of one position: splits of at most 256)
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][LDS]
   bf16* ring = Qs + 16 * LDS;                                   // [SSTAGES][K, V][STILE][LDS]
   float* merge = reinterpret_cast<float*>(ring);               // reused after the tiles: [4][16][PART]
@@ -743,37 +742,62 @@ static_assert((size_t)(KG - 1) * 4 * 16 * (HD + 2) * sizeof(float) <= (size_t)4 
 // 256 | 512 in the environment, read at first use) fixes it; otherwise the largest of the
 // three whose grid still fills the GPU (two CTAs per SM), else the smallest.
 int g_forced_split = -1;
-int split_keys(int B, int nkv, int max_kv_len) {
+int split_keys(int B, int nkv, int max_kv_len, int page_size) {
   if (g_forced_split < 0) {
     const char* e = getenv("COHERYN_ATTN_SPLIT");
     const int v = e ? atoi(e) : 0;
     g_forced_split = (v == 128 || v == 256 || v == 512) ? v : 0;
   }
-  if (g_forced_split) return g_forced_split;
-  const long slots = (STREAM_SMEM + 1024 <= 227 * 1024 / 2 ? 2 : 1) * 148L;
-  for (int s = SPLIT_MAX; s > SPLIT_MIN; s >>= 1)
+  const int cap = page_size >= 2 ? SPLIT_MAX : SPLIT_MAX / 2;   // the kernel keeps split / page_size + 2 table entries
+  if (g_forced_split) return g_forced_split < cap ? g_forced_split : cap;
+  const long slots = (stream_smem(3) + 4 * 1024 <= 227 * 1024 / 2 ? 2 : 1) * 148L;
+  for (int s = cap; s > SPLIT_MIN; s >>= 1)
     if ((long)B * nkv * ((max_kv_len + s - 1) / s) >= slots) return s;
   return SPLIT_MIN;
+}
+
+template <int SSTAGES>
+int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_stride, float* scratch, int max_splits,
+                         const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks,
+                         const int* cu_q, const int* kv_lens, int nh, int nkv, int page_size, int window,
+                         float scale_log2, int split) {
+  constexpr size_t SMEM = stream_smem(SSTAGES);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_stream_kernel<SSTAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  co_launch(attn_stream_kernel<SSTAGES>, grid, dim3(128), SMEM, stream, (const bf16*)q, q_stride, scratch, max_splits,
+            (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
+            window, scale_log2, split);
+  CO_CHECK_LAUNCH("attn_stream");
+  return 0;
 }
 
 int launch_stream(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
                   const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
                   int page_size, int window, float scale_log2, int max_kv_len, int max_rows, float* scratch,
                   long scratch_floats, cudaStream_t stream) {
-  const int split = split_keys(B, nkv, max_kv_len);
+  const int split = split_keys(B, nkv, max_kv_len, page_size);
   const int max_splits = (max_kv_len + split - 1) / split + 1;
   if (!scratch || scratch_floats < (long)B * nkv * max_splits * SPLIT_FLOATS)
     CO_FAIL("attention_bf16: scratch of %ld floats is too small", scratch_floats);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM);
-    if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", STREAM_SMEM, cudaGetErrorString(e));
-    configured = true;
+  const dim3 grid(max_splits, nkv, B);
+  // CTAs that queue up (more than two per SM): the shallower ring, three CTAs per SM.
+  static int forced_stages = -1;
+  if (forced_stages < 0) {
+    const char* e = getenv("COHERYN_ATTN_STAGES");
+    forced_stages = e ? atoi(e) : 0;
   }
-  co_launch(attn_stream_kernel, dim3(max_splits, nkv, B), dim3(128), STREAM_SMEM, stream, (const bf16*)q, q_stride,
-            scratch, max_splits, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens,
-            nh, nkv, page_size, window, scale_log2, split);
-  CO_CHECK_LAUNCH("attn_stream");
+  const bool shallow = forced_stages ? forced_stages == 2 : (long)B * nkv * ((max_kv_len + split - 1) / split) > 3 * 148L;
+  const int rc = shallow ? launch_stream_kernel<2>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache,
+                                                   block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, window,
+                                                   scale_log2, split)
+                         : launch_stream_kernel<3>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache,
+                                                   block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, window,
+                                                   scale_log2, split);
+  if (rc) return rc;
   const int threads = 32 * (max_rows < 16 ? max_rows : 16);
   co_launch(attn_combine_kernel, dim3(nkv, B), dim3(threads), 0, stream, (const float*)scratch, max_splits,
             (bf16*)out, out_stride, cu_q, kv_lens, nh, nkv, window, split);
