@@ -41,6 +41,7 @@ class _Request:
     length: int = 0                      # tokens whose keys/values are committed
     tokens: List[int] = field(default_factory=list)    # committed + reserved token ids
     tables: List[List[int]] = field(default_factory=list)   # per group: page per block, -1 once given back
+    unknown_at: Optional[int] = None     # index of a token whose id is not known yet (a step launched ahead)
     hashed_blocks: int = 0
     last_hash: bytes = b""
     reused: int = 0
@@ -198,7 +199,8 @@ class CacheManager:
         r.length = len(r.tokens)
         ps = self.page_size
         if self.prefix_reuse:
-            while (r.hashed_blocks + 1) * ps <= r.length:
+            known = r.length if r.unknown_at is None else min(r.length, r.unknown_at)   # hashing waits for the id
+            while (r.hashed_blocks + 1) * ps <= known:
                 b = r.hashed_blocks
                 r.last_hash = self._block_hash(r.last_hash, r.tokens[b * ps:(b + 1) * ps])
                 for g, t in zip(self.groups, r.tables):
@@ -211,6 +213,18 @@ class CacheManager:
                 if t[b] >= 0:
                     g.pool.release(t[b])
                     t[b] = -1
+
+    def mark_unknown(self, req_id: str, index: int) -> None:
+        """Token ``index`` of the request was reserved with a placeholder id: the step that runs
+        it was launched before the id was read back.  Pages holding it are not hashed until
+        ``patch_token`` supplies the id."""
+        self.requests[req_id].unknown_at = index
+
+    def patch_token(self, req_id: str, index: int, token: int) -> None:
+        r = self.requests[req_id]
+        r.tokens[index] = int(token)
+        if r.unknown_at == index:
+            r.unknown_at = None
 
     def rollback(self, req_id: str) -> None:
         """Drop a reservation that was not committed (pages beyond the committed length

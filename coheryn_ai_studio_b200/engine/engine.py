@@ -47,15 +47,27 @@ class _Timing:
     end: Optional[float] = None
 
 
+@dataclass
+class _InFlight:
+    """A step that has been launched and whose chosen ids have not been read yet."""
+    plan: list
+    sampling: List[Request]
+    pending: object
+
+
 class Engine:
     def __init__(self, model, *, dtype="bfloat16", context: int = 4096, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 2048, page_size: int = 16,
                  num_pages: Optional[int] = None, kv_cache_tokens: Optional[int] = None,
-                 prefix_reuse: bool = True, eos_token_ids: Sequence[int] = (), use_graphs: bool = True):
+                 prefix_reuse: bool = True, eos_token_ids: Sequence[int] = (), use_graphs: bool = True,
+                 lookahead: bool = True):
         """``model`` is a DecoderModel on the device.  The cache pool holds ``num_pages``
         pages per group, or enough for ``kv_cache_tokens`` tokens, or by default enough for
         ``max_num_seqs`` requests of ``context`` tokens.  ``use_graphs`` replays decode steps
-        from CUDA graphs (one per batch size, captured at first use)."""
+        from CUDA graphs (one per batch size, captured at first use).  ``lookahead`` launches
+        the next decode step before the host has read the ids the current one chose (they go
+        from step to step on the device), so the GPU does not idle while the host keeps its
+        books; the tokens a request receives are the same."""
         self.model = model
         spec = model.spec
         if context < 1 or context > spec.max_positions:
@@ -76,6 +88,8 @@ class Engine:
         self._timing: Dict[str, _Timing] = {}
         self._requests: Dict[str, Request] = {}
         self._counter = 0
+        self.lookahead = bool(lookahead)
+        self._inflight: Optional[_InFlight] = None
 
     @classmethod
     def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0", **kwargs) -> "Engine":
@@ -117,24 +131,45 @@ class Engine:
         return self.scheduler.has_work()
 
     # ------------------------------------------------------------------ one step
-    def step(self) -> List[tuple]:
-        """Schedule, run, sample.  Returns (request_id, token, finished) for every token
-        sampled in this step."""
-        plan = self.scheduler.schedule()
-        if not plan:
-            if self.scheduler.has_work():
-                raise RuntimeError("the scheduler found nothing to run although requests are pending")
-            return []
+    def _launch(self, plan, ids_device=None) -> _InFlight:
+        """Run a plan's batch and start the selection of its tokens; nothing waits."""
         entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.samples else [])
                    for s in plan]
-        logits = self.runner.step(entries)
+        if ids_device is not None:      # the entries' ids are placeholders until the previous step's are read
+            for s in plan:
+                self.cache.mark_unknown(s.request.request_id, self.cache.length(s.request.request_id))
+        logits = self.runner.step(entries, ids_device=ids_device)
         self.scheduler.advance(plan)
         sampling = [s.request for s in plan if s.samples]
-        tokens = self.sampler.sample(logits, [r.sampler for r in sampling])
-        self.runner.check_status()
+        pending = self.sampler.launch(logits, [r.sampler for r in sampling], extra_status=[self.model.status])
+        return _InFlight(plan, sampling, pending)
+
+    def step(self) -> List[tuple]:
+        """Schedule, run, sample.  Returns (request_id, token, finished) for every token
+        sampled in the step that this call completes."""
+        cur, self._inflight = self._inflight, None
+        if cur is None:
+            plan = self.scheduler.schedule()
+            if not plan:
+                if self.scheduler.has_work():
+                    raise RuntimeError("the scheduler found nothing to run although requests are pending")
+                return []
+            cur = self._launch(plan)
+        # The step after this one, when it can be planned without this one's tokens: launched now,
+        # fed on the device with the ids being chosen, it runs while the host keeps its books.
+        if self.lookahead and cur.pending.ids is not None and len(cur.sampling) == len(cur.plan):
+            ahead = self.scheduler.lookahead(cur.plan)
+            if ahead is not None:
+                self._inflight = self._launch(ahead, ids_device=cur.pending.ids)
+        tokens = self.sampler.finish(cur.pending)
         now = time.perf_counter()
         events = []
-        for req, tok in zip(sampling, tokens):
+        for req, tok in zip(cur.sampling, tokens):
+            if req.finished:           # ended (or aborted) while this step was in flight: its token is dropped
+                continue
+            if self._inflight is not None:
+                # the step launched ahead reserved this id's place with a placeholder
+                self.cache.patch_token(req.request_id, req.num_tokens, tok)
             tm = self._timing[req.request_id]
             if tm.first_token is None:
                 tm.first_token = now
@@ -142,6 +177,8 @@ class Engine:
             if done:
                 tm.end = now
             events.append((req.request_id, tok, done))
+        if not self.scheduler.has_work():
+            self._inflight = None      # what was launched ahead has nobody left to serve
         return events
 
     # ------------------------------------------------------------------ results

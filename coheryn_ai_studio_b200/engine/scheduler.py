@@ -30,6 +30,7 @@ from ..cache.manager import CacheManager
 from ..sampling.sampler import RequestSampler, SamplingParams
 
 FINISH_STOP, FINISH_LENGTH, FINISH_CANCELLED = "stop", "length", "cancelled"
+PLACEHOLDER_TOKEN = 0     # stands for an id that is still on the device (see Scheduler.lookahead)
 
 
 class RequestRefused(ValueError):
@@ -204,6 +205,32 @@ class Scheduler:
         self.stats["scheduled_tokens"] += sum(len(s.tokens) for s in plan)
         self.stats["max_batch_width"] = max(self.stats["max_batch_width"], len(plan))
         return plan
+
+    def lookahead(self, plan: Sequence[Scheduled]) -> Optional[List[Scheduled]]:
+        """The plan of the step AFTER ``plan`` when that can be said before ``plan``'s tokens
+        are known: ``plan`` decodes every running request, nobody waits, none of the requests can
+        end by length or context with the token ``plan`` yields, and the pages are there.  The
+        entries carry a placeholder id (the real one is still on the device).  Call after
+        ``advance(plan)``.  None when the ordinary ``schedule`` has to decide."""
+        if self.waiting or not plan or len(plan) != len(self.running) or len(plan) > self.max_num_batched_tokens:
+            return None
+        reserved = [0] * len(self.cache.groups)
+        avail = self.cache.available_pages()
+        out: List[Scheduled] = []
+        for s in plan:
+            req = s.request
+            if req.finished or not s.samples or len(s.tokens) != 1 or req not in self.running:
+                return None
+            if len(req.output) + 2 > req.max_tokens or req.num_tokens + 2 > self.context:
+                return None
+            if req.sampler is None or req.sampler.params.penalised:
+                return None     # the penalties of the next step need this step's id
+            for i, x in enumerate(self.cache.pages_needed(req.request_id, 1)):
+                reserved[i] += x
+            out.append(Scheduled(req, [PLACEHOLDER_TOKEN], True))
+        if any(r > a for r, a in zip(reserved, avail)):
+            return None
+        return out
 
     # ------------------------------------------------------------------ after the step
     def advance(self, plan: Sequence[Scheduled]) -> None:

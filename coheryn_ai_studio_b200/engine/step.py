@@ -261,10 +261,13 @@ class StepRunner:
                 and all(list(e.want) == [0] for e in entries)
                 and int(lay.kv_lens.max()) <= self.graph_max_kv_len)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], ids_device: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the batch; returns float32 logits ``[wanted, vocab]`` on the device, in the
         order of the entries and of their ``want`` lists.  (With graphs the tensor is a
-        static buffer that the next decode step of the same size overwrites.)"""
+        static buffer that the next decode step of the same size overwrites.)
+        ``ids_device`` (int32, one id per token of the step) replaces the entries' token ids on
+        the device: a step launched before the host has read the ids that the previous step
+        chose; the entries then carry placeholders."""
         self._check(entries)
         self._reserve(entries)
         self.h2d_bytes = 0
@@ -276,9 +279,13 @@ class StepRunner:
                     g = self._graphs[lay.B] = _DecodeGraph(self, lay.B)
                 g.fill(lay, [self.cache.serial(e.request_id) for e in entries])
                 self.h2d_bytes += g.host.numel() * 4
+                if ids_device is not None:
+                    g.d["ids"].copy_(ids_device, non_blocking=True)
                 logits = g.run(self)
             else:
                 ctx, rows = self._context(lay)
+                if ids_device is not None:
+                    ctx.token_ids = ids_device
                 logits = self.model.forward(ctx, self.layer_caches, rows)
         except Exception:
             for e in entries:

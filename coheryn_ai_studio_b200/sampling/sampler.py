@@ -106,10 +106,16 @@ class DeviceSampler:
         """logits: float32 [R, V] (modified in place when penalties apply).  Returns the
         chosen ids; advances each sampled request's random stream by one draw and records
         the chosen id in its counts."""
+        return self.finish(self.launch(logits, samplers))
+
+    def launch(self, logits: torch.Tensor, samplers: Sequence[RequestSampler], extra_status=()) -> "PendingSample":
+        """Start the selection and the copy of its result to pinned host memory; nothing waits.
+        ``extra_status``: further device status words (int32[1]) copied along.  The chosen ids
+        stay on the device in ``PendingSample.ids`` (the next step may read them there)."""
         R = logits.shape[0]
         assert R == len(samplers)
         if R == 0:
-            return []
+            return PendingSample(None, None, None, list(samplers), [])
         rows, ids, counts, rep, freq, pres = [], [], [], [], [], []
         for r, s in enumerate(samplers):
             if s.params.penalised and s.counts:
@@ -138,13 +144,53 @@ class DeviceSampler:
                 out = picked
             else:
                 out[self._dev(np.asarray(hot, np.int64))] = picked
-        chosen = out.cpu().tolist()
-        if int(self.status.item()):
-            self.status.zero_()
-            raise RuntimeError("empty or non-finite logits")
-        for s, tok in zip(samplers, chosen):
+        words = [self.status] + list(extra_status)
+        host = self._pinned(R + len(words))
+        host[:R].copy_(out, non_blocking=True)
+        for i, w in enumerate(words):
+            host[R + i:R + i + 1].copy_(w, non_blocking=True)
+        event = torch.cuda.Event() if self.device.type == "cuda" else None
+        if event is not None:
+            event.record()
+        return PendingSample(out, host, event, list(samplers), words)
+
+    def _pinned(self, n: int) -> torch.Tensor:
+        """One of a few pinned buffers handed out in turn (at most two selections are in
+        flight at a time)."""
+        if self.device.type != "cuda":
+            return torch.empty(n, dtype=torch.int32)
+        self._turn = (getattr(self, "_turn", -1) + 1) % 4
+        pool = self.__dict__.setdefault("_pool", [None] * 4)
+        if pool[self._turn] is None or pool[self._turn].numel() < n:
+            pool[self._turn] = torch.empty(max(n, 256), dtype=torch.int32).pin_memory()
+        return pool[self._turn][:n]
+
+    def finish(self, pending: "PendingSample") -> List[int]:
+        """Wait for a launched selection (and for nothing launched after it); returns the ids."""
+        if pending.host is None:
+            return []
+        if pending.event is not None:
+            pending.event.synchronize()
+        values = pending.host.tolist()
+        R = len(pending.samplers)
+        chosen, status = values[:R], values[R:]
+        if any(status):
+            for w in pending.words:
+                w.zero_()
+            if status[0]:
+                raise RuntimeError("empty or non-finite logits")
+            raise RuntimeError({1: "a token id was outside the embedding table",
+                                2: "non-finite logits"}.get(max(status[1:]), f"device status {status[1:]}"))
+        for s, tok in zip(pending.samplers, chosen):
             s.observe(tok)
         return chosen
+
+
+class PendingSample:
+    """A selection in flight: ids on the device, their pinned host copy and its event."""
+
+    def __init__(self, ids, host, event, samplers, words):
+        self.ids, self.host, self.event, self.samplers, self.words = ids, host, event, samplers, words
 
 
 class HostSampler:

@@ -107,6 +107,35 @@ def test_stop_token_and_penalties(folders):
     assert got == plain_generate(folders["A"], p, 8, s)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_step_launched_ahead_changes_nothing(folders, dtype):
+    """The decode step that is launched before the previous step's ids are read (they pass from
+    step to step on the device): the same tokens and reasons as without it, with requests that
+    end at different times by length and by a stop token, sampled and greedy, with prefix reuse
+    on; no page is lost."""
+    from coheryn_ai_studio_b200.engine import Engine
+    from coheryn_ai_studio_b200.sampling import SamplingParams
+    shared = tiny.prompt(95, 33, 512)
+    prompts = [shared + tiny.prompt(96 + i, 2 + 3 * i, 512) for i in range(4)]
+    params = [SamplingParams(), SamplingParams(temperature=0.9, seed=3), SamplingParams(), SamplingParams(temperature=0.5, seed=8, top_k=20)]
+    def run(lookahead, stop=()):
+        eng = Engine.from_folder(folders["A"], dtype, context=128, max_num_seqs=4, page_size=16, lookahead=lookahead)
+        ids = [eng.add_request(p, max_tokens=m, params=pr, stop_tokens=stop) for p, m, pr in zip(prompts, (5, 30, 17, 22), params)]
+        steps = 0
+        while eng.has_work():
+            eng.step(); steps += 1
+        res = [eng.result(i) for i in ids]
+        eng.cache.check()
+        assert sum(eng.cache.available_pages()) + sum(len(g.pool._idle) if hasattr(g.pool, "_idle") else 0 for g in eng.cache.groups) >= 0
+        again = eng.generate(prompts[:2], max_tokens=4)      # the engine goes on after the pipeline drained
+        return [(r.token_ids, r.finish_reason) for r in res], [r.token_ids for r in again]
+    base, base2 = run(False)
+    ahead, ahead2 = run(True)
+    assert ahead == base and ahead2 == base2
+    stop_tok = base[1][0][6]
+    assert run(True, stop=[stop_tok]) == run(False, stop=[stop_tok])
+
+
 def test_refusals(folders):
     from coheryn_ai_studio_b200.engine import Engine, RequestRefused
     eng = Engine.from_folder(folders["A"], "float32", context=64, max_num_seqs=2)
