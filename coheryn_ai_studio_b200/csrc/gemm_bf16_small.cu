@@ -172,163 +172,6 @@ gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   }
 }
 
-// The same product with the preceding residual-add + RMSNorm folded in (at most 16 rows):
-//   x = resid_in (+ delta);  h = x / sqrt(mean(x^2) + eps) * norm_w;  out = h . W^T ...
-// Every CTA normalises all rows by itself into shared memory (the rows are few, and this
-// saves a kernel and a round trip through memory); CTA 0 also writes the updated residual
-// stream to resid_out, a buffer distinct from resid_in, which other CTAs are still reading.
-template <int NT>
-__global__ void __launch_bounds__(512)
-gemm_small_norm_kernel(const float* __restrict__ resid_in, const __nv_bfloat16* __restrict__ delta,
-                       const void* __restrict__ norm_w, int norm_dtype, float eps, float* __restrict__ resid_out,
-                       const __nv_bfloat16* __restrict__ w, const void* __restrict__ bias, int bias_dtype,
-                       void* __restrict__ out, int out_dtype, int M, int N, int K, long ldo, int epilogue) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int ldxs = K + 8;                                        // 16 bytes of padding per row
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][K + 8]
-  float* red = reinterpret_cast<float*>(smem_raw + (size_t)16 * ldxs * sizeof(__nv_bfloat16));
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const int n_base = blockIdx.x * NT * 8;
-
-  const __nv_bfloat16* wrow[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) wrow[nt] = w + (size_t)min(n_base + nt * 8 + g, N - 1) * K;
-  constexpr int U = NT >= 8 ? 1 : (NT >= 4 ? 2 : 4);
-  const int nblk = (K + 63) >> 6;
-  uint4 wv[U][NT][2];
-  auto load_w = [&](int blk0) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int k = ((blk0 + u * warps) << 6) + (t << 4);
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int p = 0; p < 2; ++p)
-          wv[u][nt][p] = (k + 8 * p < K) ? ld_stream(wrow[nt] + k + 8 * p) : make_uint4(0, 0, 0, 0);
-    }
-  };
-  load_w(warp);
-  co_pdl_launch_dependents();
-  co_pdl_wait();
-
-  // Norm: a warp takes rows warp, warp + warps, ...; K is a multiple of 8.
-  for (int m = warp; m < 16; m += warps) {
-    __nv_bfloat16* xrow = xs + (size_t)m * ldxs;
-    if (m >= M) {
-      for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(xrow + k) = make_uint4(0, 0, 0, 0);
-      continue;
-    }
-    const float* r = resid_in + (size_t)m * K;
-    const __nv_bfloat16* d = delta ? delta + (size_t)m * K : nullptr;
-    float ss = 0.f;
-    for (int k = lane * 8; k < K; k += 256) {
-      float v[8];
-      *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(r + k);
-      *reinterpret_cast<float4*>(v + 4) = *reinterpret_cast<const float4*>(r + k + 4);
-      if (d) {
-        __nv_bfloat16 dv[8];
-        *reinterpret_cast<uint4*>(dv) = *reinterpret_cast<const uint4*>(d + k);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] += __bfloat162float(dv[i]);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
-    }
-    ss = co_warp_sum(ss);
-    const float scale = 1.0f / sqrtf(ss / (float)K + eps);
-    for (int k = lane * 8; k < K; k += 256) {
-      float v[8];
-      *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(r + k);
-      *reinterpret_cast<float4*>(v + 4) = *reinterpret_cast<const float4*>(r + k + 4);
-      if (d) {
-        __nv_bfloat16 dv[8];
-        *reinterpret_cast<uint4*>(dv) = *reinterpret_cast<const uint4*>(d + k);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] += __bfloat162float(dv[i]);
-        if (blockIdx.x == 0 && resid_out) {
-          *reinterpret_cast<float4*>(resid_out + (size_t)m * K + k) = *reinterpret_cast<float4*>(v);
-          *reinterpret_cast<float4*>(resid_out + (size_t)m * K + k + 4) = *reinterpret_cast<float4*>(v + 4);
-        }
-      }
-      __nv_bfloat16 h[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) h[i] = __float2bfloat16_rn((v[i] * scale) * co_load_any(norm_w, norm_dtype, k + i));
-      *reinterpret_cast<uint4*>(xrow + k) = *reinterpret_cast<uint4*>(h);
-    }
-  }
-  __syncthreads();
-
-  float acc[NT][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-  const __nv_bfloat16* xa_row = xs + (size_t)g * ldxs;
-  const __nv_bfloat16* xb_row = xs + (size_t)(g + 8) * ldxs;
-  for (int blk0 = warp; blk0 < nblk; blk0 += warps * U) {
-    if (blk0 != warp) load_w(blk0);
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int k = ((blk0 + u * warps) << 6) + (t << 4);
-#pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        const bool valid = k + 8 * p < K;
-        const uint4 a = valid ? *reinterpret_cast<const uint4*>(xa_row + k + 8 * p) : make_uint4(0, 0, 0, 0);
-        const uint4 b = valid ? *reinterpret_cast<const uint4*>(xb_row + k + 8 * p) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint4 c = wv[u][nt][p];
-          mma_bf16(acc[nt], a.x, b.x, a.y, b.y, c.x, c.y);
-          mma_bf16(acc[nt], a.z, b.z, a.w, b.w, c.z, c.w);
-        }
-      }
-    }
-  }
-
-  constexpr int E = NT * 4 * 32;
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) red[warp * E + (nt * 4 + i) * 32 + lane] = acc[nt][i];
-  __syncthreads();
-  constexpr int PAIRS = NT * 2 * 32;
-  for (int e = threadIdx.x; e < PAIRS; e += blockDim.x) {
-    const int l = e & 31, half = (e >> 5) & 1, nt = e >> 6;
-    const int m = half * 8 + (l >> 2);
-    const int n = n_base + nt * 8 + (l & 3) * 2;
-    if (m >= M || n >= N) continue;
-    const int base = (nt * 4 + half * 2) * 32 + l;
-    float v0 = 0.f, v1 = 0.f;
-    for (int wi = 0; wi < warps; ++wi) {
-      v0 += red[wi * E + base];
-      v1 += red[wi * E + base + 32];
-    }
-    if (epilogue == EPI_GATED_SILU) {
-      const float r = (v0 / (1.0f + __expf(-v0))) * v1;
-      const size_t o = (size_t)m * ldo + (n >> 1);
-      if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
-      else ((float*)out)[o] = r;
-      continue;
-    }
-    const bool has1 = n + 1 < N;
-    if (bias) {
-      v0 += co_load_any(bias, bias_dtype, n);
-      if (has1) v1 += co_load_any(bias, bias_dtype, n + 1);
-    }
-    const size_t o = (size_t)m * ldo + n;
-    if (out_dtype == CO_BF16) {
-      __nv_bfloat16* p = (__nv_bfloat16*)out + o;
-      if (has1 && ((o & 1) == 0)) *(__nv_bfloat162*)p = __floats2bfloat162_rn(v0, v1);
-      else { p[0] = __float2bfloat16_rn(v0); if (has1) p[1] = __float2bfloat16_rn(v1); }
-    } else {
-      float* p = (float*)out + o;
-      p[0] = v0;
-      if (has1) p[1] = v1;
-    }
-  }
-}
-
 // The q/k/v product of a decode batch (at most 16 rows) with the rotation and the cache write
 // in its epilogue, which saves the kernel that would otherwise re-read q/k/v.  A CTA owns 8
 // features of a head's first half and the 8 that pair with them in the second half (two MMA
@@ -450,26 +293,6 @@ gemm_small_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   }
 }
 
-template <int NT>
-int launch_small_norm(const float* resid_in, const void* delta, const void* norm_w, int norm_dtype, float eps,
-                      float* resid_out, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
-                      int M, int N, int K, long ldo, int epilogue, int warps, cudaStream_t stream) {
-  const size_t smem = (size_t)16 * (K + 8) * sizeof(__nv_bfloat16) + (size_t)warps * NT * 4 * 32 * sizeof(float);
-  auto kernel = gemm_small_norm_kernel<NT>;
-  if (smem > 227 * 1024) CO_FAIL("gemm_small_norm: K = %d needs %zu bytes of shared memory", K, smem);
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) CO_FAIL("gemm_small_norm: shared memory %zu: %s", smem, cudaGetErrorString(e));
-  }
-  const int grid = (N + NT * 8 - 1) / (NT * 8);
-  cudaError_t e = co_launch_ex(true /* x is re-read through L1 */, kernel, dim3(grid), dim3(warps * 32), smem, stream, resid_in, (const __nv_bfloat16*)delta,
-                            norm_w, norm_dtype, eps, resid_out, (const __nv_bfloat16*)w, bias, bias_dtype, out,
-                            out_dtype, M, N, K, ldo, epilogue);
-  if (e != cudaSuccess) CO_FAIL("gemm_small_norm: launch failed: %s", cudaGetErrorString(e));
-  CO_CHECK_LAUNCH("gemm_small_norm");
-  return 0;
-}
-
 template <int MT, int NT>
 int launch_small(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
                  int M, int N, int K, long ldx, long ldo, int epilogue, int warps, cudaStream_t stream) {
@@ -541,31 +364,4 @@ CO_EXPORT int coheryn_qkv_rope_bf16_small(const void* x, const void* w, const vo
   if (e != cudaSuccess) CO_FAIL("qkv_rope_bf16_small: launch failed: %s", cudaGetErrorString(e));
   CO_CHECK_LAUNCH("qkv_rope_small");
   return 0;
-}
-
-// The product above with the preceding residual-add + RMSNorm folded in, for M <= 16:
-// resid_in [M, K] float32; delta [M, K] bfloat16 or null; norm_w [K]; resid_out [M, K]
-// float32 (written when delta is given; must not alias resid_in); w [N, K]; K a multiple of 8.
-CO_EXPORT int coheryn_norm_gemm_bf16_small(const float* resid_in, const void* delta, const void* norm_w,
-                                           int norm_dtype, float eps, float* resid_out, const void* w,
-                                           const void* bias, int bias_dtype, void* out, int out_dtype, int M, int N,
-                                           int K, long ldo, int epilogue, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 16) CO_FAIL("norm_gemm_bf16_small: M = %d exceeds 16", M);
-  if (K <= 0 || (K & 7)) CO_FAIL("norm_gemm_bf16_small: K = %d must be a multiple of 8", K);
-  if (delta && (!resid_out || resid_out == resid_in)) CO_FAIL("norm_gemm_bf16_small: resid_out must be a buffer of its own");
-  if (((uintptr_t)resid_in & 15) || ((uintptr_t)delta & 15) || ((uintptr_t)w & 15) || ((uintptr_t)resid_out & 15))
-    CO_FAIL("norm_gemm_bf16_small: operands must be 16-byte aligned");
-  if (epilogue == 1 && (N & 1)) CO_FAIL("norm_gemm_bf16_small: gated epilogue needs an even number of rows");
-  if (epilogue != 0 && epilogue != 1) CO_FAIL("norm_gemm_bf16_small: unknown epilogue %d", epilogue);
-  int nt = 8;
-  while (nt > 1 && (N + nt * 8 - 1) / (nt * 8) < 296) nt >>= 1;
-  const int nblk = (K + 63) / 64;
-  const int warps = nblk >= 64 ? 16 : (nblk >= 8 ? 8 : (nblk >= 4 ? 4 : (nblk >= 2 ? 2 : 1)));
-#define GO(NT_) return launch_small_norm<NT_>(resid_in, delta, norm_w, norm_dtype, eps, resid_out, w, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, warps, stream)
-  if (nt == 8) GO(8);
-  if (nt == 4) GO(4);
-  if (nt == 2) GO(2);
-  GO(1);
-#undef GO
 }

@@ -303,11 +303,6 @@ def gemm_bf16_small(x, w, bias, out, gated: bool = False) -> None:
 # Up to this many rows the weight-streaming mma.sync kernel runs; beyond it the TMA/tcgen05
 # kernel (which re-reads nothing of x through L2 and so scales to many rows).
 SMALL_M = 16
-# Up to this many rows the residual-add + RMSNorm is folded into the following product.
-# 0 = never: measured on a B200, the fused kernel (every CTA normalises all rows itself)
-# lengthens each product's critical path by more than the separate norm kernel costs.
-FUSED_NORM_M = 0
-
 _tc_status = {}
 
 
@@ -423,35 +418,6 @@ def _tc_ok(x, w) -> bool:
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > SMALL_M
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0)
-
-
-def norm_linear(resid: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
-                w: torch.Tensor, bias: Optional[torch.Tensor] = None, gated: bool = False):
-    """(resid + delta) -> RMSNorm -> linear (or gated SiLU linear) in one kernel when there are
-    at most FUSED_NORM_M rows of bfloat16 work (every CTA of the fused kernel normalises all
-    rows by itself, which only pays for very few); otherwise the norm kernel and the product.
-    Returns (y, residual): the residual stream after the add (a new buffer in the fused case,
-    ``resid`` updated in place otherwise)."""
-    M, K = resid.shape
-    N = w.shape[0]
-    fused = (w.dtype == torch.bfloat16 and 0 < M <= FUSED_NORM_M and K % 8 == 0 and resid.is_contiguous()
-             and (delta is None or (delta.dtype == torch.bfloat16 and delta.is_contiguous()))
-             and w.is_contiguous() and 16 * (K + 8) * 2 + 16 * 8 * 512 <= 200 * 1024)
-    if not fused:
-        h = torch.empty((M, K), dtype=w.dtype, device=resid.device)
-        if M:
-            add_rmsnorm(resid, delta, norm_weight, eps, h)
-        return (gated_silu_linear(h, w) if gated else linear(h, w, bias)), resid
-    _dev(resid, delta, norm_weight, w, bias)
-    out = torch.empty((M, N // 2 if gated else N), dtype=torch.bfloat16, device=resid.device)
-    new_resid = torch.empty_like(resid) if delta is not None else resid
-    lib = core()
-    _check(lib, lib.coheryn_norm_gemm_bf16_small(
-        _ptr(resid), _ptr(delta), _ptr(norm_weight), c_int(_code(norm_weight)), c_float(eps),
-        _ptr(new_resid if delta is not None else None), _ptr(w), _ptr(bias),
-        c_int(_code(bias) if bias is not None else F32), _ptr(out), c_int(BF16), c_int(M), c_int(N), c_int(K),
-        c_long(out.stride(0)), c_int(1 if gated else 0), _stream()))
-    return out, new_resid
 
 
 # ... and up to this many rows when the weight matrix is small (a few MB: the q/k/v and output

@@ -84,23 +84,6 @@ class Attention(Mixer):
             qkv = ops.linear(x, self.w_qkv[:self.q_size], self.b_qkv[:self.q_size] if self.b_qkv is not None else None)
         return self._attend(qkv, step, cache)
 
-    def forward_with_norm(self, residual, delta, norm, step: StepContext, cache: LayerCache):
-        """The same with the preceding norm folded into the q/k/v projection where a kernel
-        exists for it; returns (y, residual after the add)."""
-        self._check(cache)
-        if (cache.writes and residual.shape[0] <= ops.QKV_ROPE_M and self.position is not None
-                and self.w_qkv.dtype == torch.bfloat16):
-            x = norm.forward(residual, delta)
-            if self._fused_rope(x, cache):
-                return self._attend_q(self._project_rotate_write(x, step, cache), step, cache), residual
-            return self._attend(ops.linear(x, self.w_qkv, self.b_qkv), step, cache), residual
-        if cache.writes:
-            qkv, residual = norm.fused_linear(residual, delta, self.w_qkv, self.b_qkv)
-        else:
-            qkv, residual = norm.fused_linear(residual, delta, self.w_qkv[:self.q_size],
-                                              self.b_qkv[:self.q_size] if self.b_qkv is not None else None)
-        return self._attend(qkv, step, cache), residual
-
     @staticmethod
     def _check(cache) -> None:
         if cache is None or cache.kind != "paged":

@@ -7,10 +7,7 @@ them (:meth:`Part.bind`) and runs on the device.  Roles:
 
 * mixer         – ``forward(x, step, cache) -> y``; moves information between the tokens
                   of a request; says what cache it needs (:meth:`Mixer.cache_requirement`).
-                  Optionally ``forward_with_norm(residual, delta, norm, step, cache) ->
-                  (y, residual)`` when its first linear map can absorb the norm.
-* feed_forward  – ``forward(x, step) -> y``; token-wise (optionally ``forward_with_norm``
-                  likewise, without the cache).
+* feed_forward  – ``forward(x, step) -> y``; token-wise.
 * norm          – ``forward(residual, delta, out_rows=None) -> normed``; adds ``delta`` to
                   the float32 residual stream in place and normalises.
 * position      – owns what a mixer needs to encode positions (here: a rotation table).
@@ -138,15 +135,6 @@ class Norm(Part):
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
-
-    def fused_linear(self, residual: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor,
-                     bias: Optional[torch.Tensor] = None, gated: bool = False):
-        """norm(residual + delta) followed by a linear map (``gated``: SiLU-gated over
-        interleaved rows of ``w``).  Returns (y, residual after the add).  A norm that has a
-        kernel for the combination overrides this; the default runs the two steps."""
-        from .. import ops
-        h = self.forward(residual, delta)
-        return (ops.gated_silu_linear(h, w) if gated else ops.linear(h, w, bias)), residual
 
 
 class Position(Part):

@@ -3,9 +3,7 @@
 ``prenorm_residual`` is the layout of crates/coheryn-engine/src/inference.rs:440-540:
 x += mixer(norm(x)); x += feed_forward(norm(x)).  The residual stream is float32; each
 sub-layer's output is handed on as a pending ``delta`` that the NEXT norm adds to the
-stream while it normalises, so the sum and the norm cost one pass over the row.  A mixer
-or feed-forward that offers ``forward_with_norm`` takes the norm over as well (for a few
-rows the norm is folded into its first matrix product).
+stream while it normalises, so the sum and the norm cost one pass over the row.
 """
 from __future__ import annotations
 
@@ -20,16 +18,8 @@ class PreNormResidual(Arrangement):
                 "post_attention_layernorm": self.feed_forward_norm, "mlp": self.feed_forward}
 
     def forward(self, residual, delta, step, cache):
-        fused = getattr(self.mixer, "forward_with_norm", None)
-        if fused is not None:
-            mixed, residual = fused(residual, delta, self.mixer_norm, step, cache)
-        else:
-            mixed = self.mixer.forward(self.mixer_norm.forward(residual, delta), step, cache)
-        fused = getattr(self.feed_forward, "forward_with_norm", None)
-        if fused is not None:
-            out, residual = fused(residual, mixed, self.feed_forward_norm, step)
-        else:
-            out = self.feed_forward.forward(self.feed_forward_norm.forward(residual, mixed), step)
+        mixed = self.mixer.forward(self.mixer_norm.forward(residual, delta), step, cache)
+        out = self.feed_forward.forward(self.feed_forward_norm.forward(residual, mixed), step)
         return residual, out
 
 

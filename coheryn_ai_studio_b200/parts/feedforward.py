@@ -38,11 +38,4 @@ class GatedMLP(FeedForward):
         return ops.linear(act, self.w_down, partial_ok=self.partial_output)
 
 
-    def forward_with_norm(self, residual, delta, norm, step: StepContext):
-        """The same with the preceding norm folded into the gate/up projection where a kernel
-        exists for it; returns (y, residual after the add)."""
-        act, residual = norm.fused_linear(residual, delta, self.w_gate_up, gated=True)
-        return ops.linear(act, self.w_down, partial_ok=self.partial_output), residual
-
-
 register_feed_forward("gated_mlp", GatedMLP)

@@ -38,8 +38,4 @@ class RMSNorm(Norm):
         return out
 
 
-    def fused_linear(self, residual, delta, w, bias=None, gated=False):
-        return ops.norm_linear(residual, delta, self.weight, self.eps, w, bias, gated)
-
-
 register_norm("rmsnorm", RMSNorm)
