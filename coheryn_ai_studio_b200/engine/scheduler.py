@@ -230,6 +230,9 @@ class Scheduler:
             out.append(Scheduled(req, [PLACEHOLDER_TOKEN], True))
         if any(r > a for r, a in zip(reserved, avail)):
             return None
+        self.stats["steps"] += 1
+        self.stats["scheduled_tokens"] += len(out)
+        self.stats["max_batch_width"] = max(self.stats["max_batch_width"], len(out))
         return out
 
     # ------------------------------------------------------------------ after the step
