@@ -14,6 +14,13 @@ token ids out, every step.
 The cache of the timed requests is filled with random keys and values (their prompts are
 not run); weights and caches are far larger than the 126 MB L2, so every step streams
 them from HBM.  One JSON line is printed.
+
+``--workload serving-7b`` and ``--workload long-14b`` run the two further workloads that the
+baseline names instead (their own JSON line, through ``Engine.generate``): continuous
+batching of 64 requests at the 7B layer sizes (prompts uniform in [128, 2048], 256 output
+tokens each, context 8,192, pages of 16), and a 16,384-token context at the 14B layer sizes
+whose prefix 8 requests share (prefill in 2,048-token portions, prefix pages reused), then
+decoding at batch 8.
 """
 from __future__ import annotations
 
@@ -34,6 +41,13 @@ SIZES = dict(vocab_size=151936, hidden_size=1536, intermediate_size=8960, num_hi
              max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6,
              tie_word_embeddings=True)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# BASELINE.json configs[3] and configs[4]: Qwen2.5-7B and 14B layer sizes.
+SIZES_7B = dict(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                num_attention_heads=28, num_key_value_heads=4, head_dim=128, max_position_embeddings=32768,
+                rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+SIZES_14B = dict(vocab_size=152064, hidden_size=5120, intermediate_size=13824, num_hidden_layers=48,
+                 num_attention_heads=40, num_key_value_heads=8, head_dim=128, max_position_embeddings=32768,
+                 rms_norm_eps=1e-5, rope_theta=1e6, tie_word_embeddings=False)
 
 
 def peaks():
@@ -120,6 +134,68 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+def other_workload(args) -> int:
+    """configs[3] (serving-7b) or configs[4] (long-14b) of the baseline through Engine.generate."""
+    import numpy as np
+    import torch
+
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.engine import Engine, random_model_on_device
+    serving = args.workload == "serving-7b"
+    sizes = dict(SIZES_7B if serving else SIZES_14B)
+    full_layers = sizes["num_hidden_layers"]
+    if args.layers != SIZES["num_hidden_layers"]:
+        sizes["num_hidden_layers"] = args.layers
+    cfg = Qwen2Config(**sizes)
+    model = random_model_on_device(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    rng = np.random.default_rng(0)
+    V = cfg.vocab_size
+    if serving:
+        eng = Engine(model, context=8192, max_num_seqs=64, max_num_batched_tokens=2048, page_size=16,
+                     kv_cache_tokens=64 * 2400, prefix_reuse=False, use_graphs=not args.no_graphs)
+        prompts = [rng.integers(0, V, int(n)).tolist() for n in rng.integers(128, 2049, 64)]
+        outs = 256
+        eng.generate(prompts, max_tokens=outs)             # untimed: compilation, a graph per batch width met
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = eng.generate(prompts, max_tokens=outs)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        out_tokens = sum(r.completion_tokens for r in res)
+        line = {"metric": "serving_output_tokens_per_s", "value": round(out_tokens / dt, 1), "unit": "tok/s",
+                "seconds": round(dt, 3), "prompt_tokens": sum(len(p) for p in prompts), "output_tokens": out_tokens,
+                "total_tokens_per_s": round((sum(len(p) for p in prompts) + out_tokens) / dt, 1),
+                "preemptions": eng.scheduler.stats["preemptions"]}
+        what = "Qwen2.5-7B layer sizes, 64 requests, prompts uniform[128,2048], 256 outputs, context 8192, page 16"
+    else:
+        ctx, outs = 16384, 64
+        eng = Engine(model, context=ctx + outs + 16, max_num_seqs=8, max_num_batched_tokens=2048, page_size=16,
+                     kv_cache_tokens=3 * ctx, prefix_reuse=True, use_graphs=not args.no_graphs)
+        warm = rng.integers(0, V, 2100).tolist()
+        eng.generate([warm], max_tokens=4)                  # first-use compilation and graph capture
+        shared = rng.integers(0, V, ctx - 256).tolist()
+        prompts = [shared + rng.integers(0, V, 256).tolist() for _ in range(8)]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.generate(prompts[:1], max_tokens=1)             # the shared prefix is computed once
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        res = eng.generate(prompts, max_tokens=outs)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        decode_s = max(r.decode_ms for r in res) / 1e3
+        line = {"metric": "long_context_decode_tokens_per_s", "value": round(8 * (outs - 1) / decode_s, 1), "unit": "tok/s",
+                "prefill_tokens_per_s": round(ctx / (t1 - t0), 1), "prefill_seconds": round(t1 - t0, 3),
+                "shared_prefix_seconds": round(t2 - t1, 3),
+                "reused_prompt_tokens": [r.reused_prompt_tokens for r in res]}
+        what = "Qwen2.5-14B layer sizes, 16384-token context, prefix shared by 8 requests, decode at batch 8"
+    eng.cache.check()
+    line.update({"n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                 "config": {"model": what, "layers": cfg.num_hidden_layers, "layers_of_config": full_layers}})
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -134,6 +210,8 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b"],
+                    help="decode: the contract's line (default); the others: see the header")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -146,6 +224,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload != "decode":
+        return other_workload(args)
 
     import numpy as np
     import torch
