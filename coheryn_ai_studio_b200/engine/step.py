@@ -143,7 +143,7 @@ class StepRunner:
         self.device = model.runtime.device
         self.layer_caches = cache.layer_caches()
         self.steps_run = 0
-        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and model.capturable
         self.graph_max_kv_len = int(graph_max_kv_len or model.spec.max_positions)
         self.graph_table_width = max(1, -(-self.graph_max_kv_len // cache.page_size))
         self._graphs: Dict[int, _DecodeGraph] = {}

@@ -96,6 +96,10 @@ class StepContext:
 
 # ------------------------------------------------------------------------------- parts
 class Part:
+    # False if ``forward`` waits for the device (reads a result on the host) or launches work whose
+    # shape depends on data: a model with such a part is never replayed from a CUDA graph.
+    capturable = True
+
     def __init__(self, runtime: Runtime):
         self.runtime = runtime
 
@@ -138,7 +142,10 @@ class Norm(Part):
 
 
 class Position(Part):
-    pass
+    """What the stock attention asks of an encoding that turns pairs (i, i + rotary_dim / 2) of a
+    head's first ``rotary_dim`` elements: the attribute ``rotary_dim`` and ``cos_sin()``, a float32
+    device table [positions, rotary_dim / 2, 2] of (cos, sin).  A mixer of another kind may ask its
+    position part for anything else."""
 
 
 class Arrangement:

@@ -47,6 +47,8 @@ class DecoderModel:
             for layer in self.layers:
                 layer.mixer.partial_output = True
                 layer.feed_forward.partial_output = True
+        self.capturable = all(part.capturable for _, part in self._named_parts()) and all(
+            p.capturable for p in self._positions.values())
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.status = None

@@ -1,7 +1,8 @@
 """Each part of a layer alone against the plain implementation, and the generality of
 the assembly: a model whose schedule names a layer twice, lets an entry read another
-entry's cache, uses a window in some layers, and holds a toy mixer with state of its own
-that is defined HERE and registered without touching the framework's files."""
+entry's cache, uses a window in some layers, and holds a toy mixer with state of its own, a
+toy feed-forward that routes tokens to experts and a second position encoding, all defined
+HERE and registered without touching the framework's files."""
 import json
 import os
 
@@ -130,6 +131,7 @@ def toy_decay_mixer_class():
 
     class DecayMixer(Mixer):
         """State of its own: s_t = decay * s_{t-1} + x_t per request; y_t = W s_t."""
+        capturable = False   # reads the step's layout on the host
 
         def __init__(self, runtime, hidden_size, decay, position=None):
             super().__init__(runtime)
@@ -158,6 +160,81 @@ def toy_decay_mixer_class():
     return DecayMixer
 
 
+def toy_routed_ff_class():
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.parts import FeedForward
+    from coheryn_ai_studio_b200.weights import TensorSpec
+
+    class HashRoutedFF(FeedForward):
+        """Routing: token id modulo the number of experts picks the expert; each expert is
+        down(relu(up x)).  The tokens of an expert are gathered, run and scattered back."""
+        capturable = False   # the number of rows per expert is read on the host
+
+        def __init__(self, runtime, hidden_size, intermediate_size, experts):
+            super().__init__(runtime)
+            self.hidden_size, self.intermediate_size, self.experts = hidden_size, intermediate_size, experts
+
+        def tensor_specs(self):
+            specs = {}
+            for e in range(self.experts):
+                specs[f"experts.{e}.up.weight"] = TensorSpec((self.intermediate_size, self.hidden_size))
+                specs[f"experts.{e}.down.weight"] = TensorSpec((self.hidden_size, self.intermediate_size))
+            return specs
+
+        def bind(self, tensors):
+            self.up = [tensors[f"experts.{e}.up.weight"] for e in range(self.experts)]
+            self.down = [tensors[f"experts.{e}.down.weight"] for e in range(self.experts)]
+
+        def forward(self, x, step):
+            route = step.token_ids.long() % self.experts
+            out = torch.zeros_like(x)
+            for e in range(self.experts):
+                rows = torch.nonzero(route == e).flatten()
+                if rows.numel():
+                    h = torch.relu(ops.linear(x.index_select(0, rows).contiguous(), self.up[e]))
+                    out.index_copy_(0, rows, ops.linear(h, self.down[e]))
+            return out
+    return HashRoutedFF
+
+
+def toy_position_class():
+    from coheryn_ai_studio_b200.parts import Position
+
+    class LinearAngles(Position):
+        """Another encoding behind the same interface (rotary_dim, cos_sin()): pair i of the
+        first rotary_dim elements turns by position * rate * (i + 1); the rest of the head
+        is left as it is."""
+
+        def __init__(self, runtime, head_dim, rotary_dim, rate, max_positions):
+            super().__init__(runtime)
+            self.head_dim, self.rotary_dim, self.rate, self.max_positions = head_dim, rotary_dim, rate, max_positions
+            self._table = None
+
+        def cos_sin(self):
+            if self._table is None:
+                ang = linear_angles(np.arange(self.max_positions), self.rotary_dim, self.rate)
+                t = np.stack([np.cos(ang, dtype=np.float32), np.sin(ang, dtype=np.float32)], axis=-1)
+                self._table = torch.from_numpy(np.ascontiguousarray(t)).to(self.runtime.device)
+            return self._table
+    return LinearAngles
+
+
+def linear_angles(positions, rotary_dim, rate):
+    i = np.arange(1, rotary_dim // 2 + 1, dtype=np.float32)
+    return (np.asarray(positions, dtype=np.float32)[:, None] * np.float32(rate) * i[None, :]).astype(np.float32)
+
+
+def plain_linear_rope(x, positions, head_dim, rotary_dim, rate):
+    T, half = x.shape[0], rotary_dim // 2
+    h = x.astype(np.float32).reshape(T, -1, head_dim).copy()
+    ang = linear_angles(positions, rotary_dim, rate)
+    c, s = np.cos(ang, dtype=np.float32)[:, None, :], np.sin(ang, dtype=np.float32)[:, None, :]
+    a, b = h[:, :, :half].copy(), h[:, :, half:rotary_dim].copy()
+    h[:, :, :half] = a * c - b * s
+    h[:, :, half:rotary_dim] = a * s + b * c
+    return h.reshape(T, -1)
+
+
 def toy_spec(c):
     from coheryn_ai_studio_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
     H = c["hidden_size"]
@@ -170,10 +247,13 @@ def toy_spec(c):
                                       "qkv_bias": True, "o_bias": False, "window": window,
                                       "scale": c["head_dim"] ** -0.5})
     ff = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": c["intermediate_size"], "activation": "silu"})
+    routed = PartSpec("test_hash_routed", {"hidden_size": H, "intermediate_size": c["expert_size"], "experts": c["experts"]})
+    linear = PartSpec("test_linear_angles", {"head_dim": c["head_dim"], "rotary_dim": c["toy_rotary_dim"],
+                                             "rate": c["toy_rate"], "max_positions": c["max_position_embeddings"]})
     layers = [
         LayerSpec("model.layers.0", "prenorm_residual", attn(None), ff, norm, norm, rope),
-        LayerSpec("model.layers.1", "prenorm_residual", PartSpec("test_decay", {"hidden_size": H, "decay": 0.5}), ff, norm, norm),
-        LayerSpec("model.layers.2", "prenorm_residual", attn(c["window"]), ff, norm, norm, rope),
+        LayerSpec("model.layers.1", "prenorm_residual", PartSpec("test_decay", {"hidden_size": H, "decay": 0.5}), routed, norm, norm),
+        LayerSpec("model.layers.2", "prenorm_residual", attn(c["window"]), ff, norm, norm, linear),
     ]
     # layer 0 twice (two caches), the toy layer, the windowed layer, then layer 0 a third
     # time reading the cache its FIRST run wrote
@@ -189,7 +269,7 @@ class ToyConfig(dict):
 
 TOY = ToyConfig(architectures=["ToyStateForCausalLM"], hidden_size=48, num_attention_heads=3, num_key_value_heads=1,
                 head_dim=16, intermediate_size=80, vocab_size=130, rms_norm_eps=1e-5, rope_theta=1e4,
-                max_position_embeddings=128, window=11)
+                max_position_embeddings=128, window=11, experts=3, expert_size=40, toy_rotary_dim=8, toy_rate=0.01)
 
 
 def toy_plain_forward(cfg, w, ids):
@@ -200,12 +280,17 @@ def toy_plain_forward(cfg, w, ids):
     x = plain.embedding(w["model.embed_tokens.weight"], ids)
     kept = {}
 
+    def turn(x, i):
+        if i == 2:
+            return plain_linear_rope(x, positions, hd, cfg["toy_rotary_dim"], cfg["toy_rate"])
+        return plain.rope(x, positions, hd, cfg["rope_theta"])
+
     def attention_layer(x, i, window, entry, cache_from=None):
         p = f"model.layers.{i}."
         y = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
-        q = plain.rope(plain.linear(y, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]), positions, hd, cfg["rope_theta"])
+        q = turn(plain.linear(y, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]), i)
         if cache_from is None:
-            k = plain.rope(plain.linear(y, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]), positions, hd, cfg["rope_theta"])
+            k = turn(plain.linear(y, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]), i)
             v = plain.linear(y, w[p + "self_attn.v_proj.weight"], w[p + "self_attn.v_proj.bias"])
             kept[entry] = (k, v)
         else:
@@ -228,8 +313,18 @@ def toy_plain_forward(cfg, w, ids):
         a = plain.swiglu(plain.linear(y, w[p + "mlp.gate_proj.weight"]), plain.linear(y, w[p + "mlp.up_proj.weight"]))
         return (x + plain.linear(a, w[p + "mlp.down_proj.weight"])).astype(np.float32)
 
+    def routed(x, i):
+        p = f"model.layers.{i}."
+        y = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        out = np.zeros_like(y)
+        for t, tok in enumerate(ids):
+            e = int(tok) % cfg["experts"]
+            h = np.maximum(plain.linear(y[t:t + 1], w[p + f"mlp.experts.{e}.up.weight"]), 0)
+            out[t] = plain.linear(h, w[p + f"mlp.experts.{e}.down.weight"])[0]
+        return (x + out).astype(np.float32)
+
     x = mlp(attention_layer(x, 0, None, 0), 0)
-    x = mlp(decay_layer(x, 1), 1)
+    x = routed(decay_layer(x, 1), 1)
     x = mlp(attention_layer(x, 0, None, 2), 0)
     x = mlp(attention_layer(x, 2, cfg["window"], 3), 2)
     x = mlp(attention_layer(x, 0, None, 4, cache_from=0), 0)
@@ -240,15 +335,20 @@ def toy_plain_forward(cfg, w, ids):
 def toy_folder(tmp_path_factory):
     from coheryn_ai_studio_b200.config import register_architecture, unregister_architecture
     from coheryn_ai_studio_b200.engine import write_random_model
-    from coheryn_ai_studio_b200.parts import MIXERS, register_mixer
+    from coheryn_ai_studio_b200.parts import (FEED_FORWARDS, MIXERS, POSITIONS, register_feed_forward, register_mixer,
+                                              register_position)
     from coheryn_ai_studio_b200.weights import InitPolicy
     register_mixer("test_decay", toy_decay_mixer_class())
+    register_feed_forward("test_hash_routed", toy_routed_ff_class())
+    register_position("test_linear_angles", toy_position_class())
     register_architecture("ToyStateForCausalLM", lambda obj: ToyConfig(obj), toy_spec)
     d = str(tmp_path_factory.mktemp("toy") / "model")
     write_random_model(d, TOY, 7, InitPolicy(0.08, 0.2, 0.05))
     yield d
     unregister_architecture("ToyStateForCausalLM")
     MIXERS.pop("test_decay", None)
+    FEED_FORWARDS.pop("test_hash_routed", None)
+    POSITIONS.pop("test_linear_angles", None)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -258,6 +358,7 @@ def test_toy_architecture_steps_through_the_engine(toy_folder, dtype):
     from replay import Replay
     cfg, w = plain.read_model(toy_folder)
     assert "model.layers.1.self_attn.mix.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+    assert "model.layers.1.mlp.experts.2.up.weight" in w and "model.layers.1.mlp.gate_proj.weight" not in w
     rng = np.random.default_rng(3)
     seqs = {"a": rng.integers(0, 130, 45).tolist(), "b": rng.integers(0, 130, 30).tolist()}
     r = Replay(toy_folder, dtype, max_tokens=128, page_size=8)
@@ -278,3 +379,17 @@ def test_toy_architecture_steps_through_the_engine(toy_folder, dtype):
                 assert np.abs(row - ref[pos]).max() <= tol, (rid, pos)
     r.cache.free("a"); r.cache.free("b"); r.cache.check()
     assert r.cache.available_pages() == [16, 16]
+
+
+def test_toy_architecture_generates_through_the_entry_point(toy_folder):
+    """The same folder through the Python entry point (scheduler, sampler, graphs requested):
+    its parts are not capturable, so the engine steps it without graphs; greedy tokens equal
+    the plain implementation's."""
+    from coheryn_ai_studio_b200.api import generate
+    cfg, w = plain.read_model(toy_folder)
+    prompt = np.random.default_rng(5).integers(0, 130, 9).tolist()
+    out = generate(toy_folder, [prompt], max_tokens=6, dtype="float32", context=64)
+    seq = list(prompt)
+    for _ in range(6):
+        seq.append(int(np.argmax(toy_plain_forward(cfg, w, seq)[-1])))
+    assert list(out[0]["token_ids"]) == seq[len(prompt):]
