@@ -356,7 +356,12 @@ def main() -> int:
             eng.cache.free(rid)
             if r > 0:
                 best = ms if best is None else min(best, ms)
-        flops = 2.0 * tokens * L * layer_params + 2.0 * V * H + L * 4.0 * nh * hd * tokens * (tokens + 1) / 2
+        # What the step computes: every layer in full but the last, which projects q/k/v for all
+        # tokens (their keys and values go to the cache) and runs the rest for the one wanted row.
+        full = 2.0 * tokens * layer_params + 4.0 * nh * hd * tokens * (tokens + 1) / 2
+        last = (2.0 * tokens * (nh + 2 * nkv) * hd * H + 2.0 * (H * nh * hd + 3 * H * I) + 4.0 * nh * hd * tokens
+                if eng.runner.tail_shortcut else full)
+        flops = (L - 1) * full + last + 2.0 * V * H
         peak = pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]) * 1e12
         del eng
         torch.cuda.empty_cache()

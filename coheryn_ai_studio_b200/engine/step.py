@@ -14,6 +14,7 @@ static index buffers, and a step then costs one host-to-device copy and one grap
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
@@ -147,6 +148,9 @@ class StepRunner:
         self.graph_max_kv_len = int(graph_max_kv_len or model.spec.max_positions)
         self.graph_table_width = max(1, -(-self.graph_max_kv_len // cache.page_size))
         self._graphs: Dict[int, _DecodeGraph] = {}
+        # Steps that want at most half of their rows run the last entry of the schedule for the
+        # wanted rows only (COHERYN_TAIL=0 in the environment switches it off).
+        self.tail_shortcut = os.environ.get("COHERYN_TAIL", "1") != "0"
         self.graph_launches = 0       # kernel launches replayed from graphs
         self.h2d_bytes = 0            # bytes copied to the device by the last step
 
@@ -247,7 +251,25 @@ class StepRunner:
             cu_q=self._to_device(lay.cu), kv_lens=self._to_device(lay.kv_lens), block_tables=tables,
             slots=[self._to_device(s) for s in lay.slots], state_slots=self._to_device(lay.state_slots),
             q_lens=lay.q_lens, kv_lens_host=kv, max_q_len=max(lay.q_lens), max_kv_len=max(kv))
-        return ctx, self._to_device(lay.rows)
+        rows = self._to_device(lay.rows)
+        R = len(lay.rows)
+        if self.tail_shortcut and 2 * R <= lay.T:
+            # Few rows are wanted: they also stand as a step of their own, one row per
+            # "request" at its own position, for the last entry of the schedule.
+            req = lay.req[lay.rows]
+            ar = np.arange(R + 1, dtype=np.int32)
+            kv_r = (lay.pos[lay.rows] + 1).astype(np.int32)
+            long_rows = rows.long()
+            ctx.tail = StepContext(
+                num_tokens=R, num_requests=R, token_ids=ctx.token_ids.index_select(0, long_rows),
+                positions=ctx.positions.index_select(0, long_rows), token_req=self._to_device(ar[:R]),
+                cu_q=self._to_device(ar), kv_lens=self._to_device(kv_r),
+                block_tables=[t.index_select(0, self._to_device(req).long()) for t in tables] if R else tables,
+                slots=[s.index_select(0, long_rows) for s in ctx.slots],
+                state_slots=self._to_device(lay.state_slots[req]),
+                q_lens=[1] * R, kv_lens_host=kv_r.tolist(), max_q_len=1, max_kv_len=int(kv_r.max()) if R else 0)
+            ctx.tail_rows = rows
+        return ctx, rows
 
     def build_context(self, entries: Sequence[StepEntry]):
         """Check, reserve pages and lay the batch out on the device (no graph)."""
@@ -286,6 +308,8 @@ class StepRunner:
                 ctx, rows = self._context(lay)
                 if ids_device is not None:
                     ctx.token_ids = ids_device
+                    if ctx.tail is not None:
+                        ctx.tail.token_ids = ids_device.index_select(0, ctx.tail_rows.long())
                 logits = self.model.forward(ctx, self.layer_caches, rows)
         except Exception:
             for e in entries:

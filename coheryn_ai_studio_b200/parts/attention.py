@@ -84,6 +84,29 @@ class Attention(Mixer):
             qkv = ops.linear(x, self.w_qkv[:self.q_size], self.b_qkv[:self.q_size] if self.b_qkv is not None else None)
         return self._attend(qkv, step, cache)
 
+    supports_tail = True
+
+    def forward_tail(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> Optional[torch.Tensor]:
+        """Keys and values of every row go to the cache; only the wanted rows attend."""
+        self._check(cache)
+        rows, tail = step.tail_rows, step.tail
+        if self._fused_rope(x, cache):
+            q = self._project_rotate_write(x, step, cache)
+            return self._attend_q(q.index_select(0, rows), tail, cache) if tail.num_tokens else None
+        if not cache.writes:   # nothing to write: the wanted rows alone make their queries
+            if not tail.num_tokens:
+                return None
+            b = self.b_qkv[:self.q_size] if self.b_qkv is not None else None
+            return self._attend(ops.linear(x.index_select(0, rows), self.w_qkv[:self.q_size], b), tail, cache)
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        rot = self.position.rotary_dim if self.position is not None else 0
+        cos_sin = self.position.cos_sin() if self.position is not None else None
+        ops.rope_kv_write(qkv, step.positions, cos_sin, step.slots[cache.group], cache.k, cache.v, self.num_heads,
+                          self.num_kv_heads, self.head_dim, rot, cache.page_size)
+        if not tail.num_tokens:
+            return None
+        return self._attend_q(qkv[:, :self.q_size].index_select(0, rows), tail, cache)
+
     @staticmethod
     def _check(cache) -> None:
         if cache is None or cache.kind != "paged":

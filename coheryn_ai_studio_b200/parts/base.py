@@ -92,6 +92,13 @@ class StepContext:
     kv_lens_host: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_kv_len: int = 0
+    # When few of the step's rows are wanted: the wanted rows as a step of their own (one row
+    # per "request": one query at its position over the same pages) and their indices among the
+    # step's tokens.  The LAST entry of the schedule then computes only these rows after it has
+    # updated its cache for all of them (crates/coheryn-engine/src/inference.rs:481-485: a row
+    # that needs no logits stops after the append in the last layer).  tail.num_tokens may be 0.
+    tail: Optional["StepContext"] = None
+    tail_rows: Optional[torch.Tensor] = None   # [R] int32
 
 
 # ------------------------------------------------------------------------------- parts
@@ -115,6 +122,15 @@ class Mixer(Part):
     # Set by the model when every norm takes partial sums: the part may then return its output
     # as a float32 stack [splits, T, H] whose sum is the output (see Norm.accepts_partial_sums).
     partial_output = False
+
+    # True if the part implements forward_tail.
+    supports_tail = False
+
+    def forward_tail(self, x: torch.Tensor, step: StepContext, cache) -> Optional[torch.Tensor]:
+        """Update the cache (or state) for ALL rows of ``x`` as ``forward`` does, but return the
+        output only for the rows ``step.tail_rows``, in that order (None when there are none);
+        ``step.tail`` describes those rows as a step of their own."""
+        raise NotImplementedError
 
     def cache_requirement(self):
         """PagedKV, FixedState or None."""
@@ -162,6 +178,14 @@ class Arrangement:
         raise NotImplementedError
 
     def forward(self, residual, delta, step: StepContext, cache: Optional[LayerCache]):
+        raise NotImplementedError
+
+    # True if forward_tail may be called (the arrangement has one and its mixer can do it).
+    supports_tail = False
+
+    def forward_tail(self, residual, delta, step: StepContext, cache: Optional[LayerCache]):
+        """As ``forward`` for the last entry of the schedule when ``step.tail`` is set: the
+        returned pair holds only the rows ``step.tail_rows`` (or (None, None) without rows)."""
         raise NotImplementedError
 
 

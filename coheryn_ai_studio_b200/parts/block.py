@@ -22,5 +22,17 @@ class PreNormResidual(Arrangement):
         out = self.feed_forward.forward(self.feed_forward_norm.forward(residual, mixed), step)
         return residual, out
 
+    @property
+    def supports_tail(self):
+        return self.mixer.supports_tail
+
+    def forward_tail(self, residual, delta, step, cache):
+        mixed = self.mixer.forward_tail(self.mixer_norm.forward(residual, delta), step, cache)
+        if mixed is None:
+            return None, None
+        kept = residual.index_select(0, step.tail_rows)
+        out = self.feed_forward.forward(self.feed_forward_norm.forward(kept, mixed), step.tail)
+        return kept, out
+
 
 register_arrangement("prenorm_residual", PreNormResidual)

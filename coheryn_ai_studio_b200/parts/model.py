@@ -99,10 +99,17 @@ class DecoderModel:
         residual = torch.empty((T, H), dtype=torch.float32, device=self.runtime.device)
         ops.embed_gather(self.embedding, step.token_ids, residual, self.status)
         delta = None
-        for entry, cache in zip(self.spec.schedule, caches):
-            residual, delta = self.layers[entry.layer].forward(residual, delta, step, cache)
+        last = len(self.spec.schedule) - 1
+        tailed = False
+        for i, (entry, cache) in enumerate(zip(self.spec.schedule, caches)):
+            layer = self.layers[entry.layer]
+            if i == last and step.tail is not None and layer.supports_tail:
+                residual, delta = layer.forward_tail(residual, delta, step, cache)
+                tailed = True
+            else:
+                residual, delta = layer.forward(residual, delta, step, cache)
         R = logit_rows.numel()
         if R == 0:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
-        h = self.final_norm.forward(residual, delta, rows=logit_rows)
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
+        h = self.final_norm.forward(residual, delta, rows=None if tailed else logit_rows)
         return ops.linear(h, self.head, out_dtype=torch.float32)

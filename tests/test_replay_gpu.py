@@ -203,3 +203,28 @@ def test_trace_run_program(dtype, folders, tmp_path):
     assert np.abs(got[1] - ref_a[[31]]).max() <= tol
     assert np.abs(got[2] - ref_b[[18, 19]]).max() <= tol
     assert np.abs(got[3] - ref_a[[36]]).max() <= tol
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_few_wanted_rows_take_the_last_layers_shortcut(name, dtype, folders, models):
+    """Steps that want few rows (or none) run the last layer for those rows only: the logits
+    equal the plain implementation's, the cache that later steps read is complete, and
+    switching the shortcut off changes nothing beyond rounding."""
+    n = 77 if name == "A" else 131
+    seq = tiny.prompt(33, n, vocab(name))
+    other = tiny.prompt(34, 40, vocab(name))
+    runs = {}
+    for shortcut in (True, False):
+        r = Replay(folders[name], dtype, max_tokens=256, model=models(name, dtype))
+        r.runner.tail_shortcut = shortcut
+        r.step([("r", seq[:30], [])])                                   # nothing wanted
+        r.step([("r", seq[30:60], [29, 3]), ("o", other[:20], [19])])    # few rows, out of order, two requests
+        r.step([("r", seq[60:n - 5], [0]), ("o", other[20:], [])])
+        r.step([("r", seq[n - 5:], list(range(5)))])                     # everything wanted: no shortcut
+        assert set(k for k in r.rows if k[0] == "r") == {("r", p) for p in [59, 33, 60] + list(range(n - 5, n))}
+        compare(r, folders[name], {"r": seq, "o": other}, f"shortcut {shortcut}")
+        runs[shortcut] = r.rows
+    for key, row in runs[True].items():
+        tol = 1e-4 if dtype == "float32" else 0.04 * max(1.0, float(np.abs(row).max()))
+        assert np.abs(row - runs[False][key]).max() <= tol, key
