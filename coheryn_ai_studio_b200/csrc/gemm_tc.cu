@@ -439,6 +439,198 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   }
 }
 
+// ------------------------------------------------------------------------------------
+// Pair variant: two CTAs of a cluster (two SMs) share one 256 x BN tile.  CTA r of the pair
+// stages rows [128 r, 128 r + 128) of the x tile and rows [BN/2 r, BN/2 (r + 1)) of the W tile,
+// so each SM pulls 128 + BN/2 rows of 128 bytes per k-step from L2 instead of 128 + BN for the
+// same number of MMA cycles; the leader (rank 0) issues tcgen05.mma.cta_group::2, which reads
+// both CTAs' shared memory and writes rows [128 r, ..) of the accumulator into CTA r's tensor
+// memory.  Barriers:
+//   full[s]       in the leader: armed by the leader's producer with the bytes of BOTH CTAs;
+//                 the peer's TMA loads complete on it (cp.async.bulk.tensor ... cta_group::2);
+//   empty[s]      in each CTA: the leader's tcgen05.commit arrives on both (multicast);
+//   acc_full[a]   in each CTA: likewise, after a tile's last MMA;
+//   acc_empty[a]  in the leader: the eight epilogue warps of both CTAs arrive on it.
+// The pair walks the tiles t = pair, pair + pairs, ... (row tiles fastest) with two accumulators.
+__device__ __forceinline__ unsigned cluster_ctarank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned map_to_cta(const void* local, unsigned rank) {
+  unsigned ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local)), "r"(rank));
+  return ra;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion is counted on a barrier of the pair's leader (cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, unsigned bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_d, unsigned long long da, unsigned long long db,
+                                               unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, once the MMAs issued so far are complete, on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
+  const unsigned short mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int BN, int STAGES, int ACCS>
+struct PairSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + ACCS * BN * 4 /* bias */;
+};
+
+template <int BN, int STAGES, int ACCS>
+__global__ void __launch_bounds__(192)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype,
+                    int M, int N, int K, long ldo, int epilogue, int* __restrict__ status) {
+  using S = PairSmem<BN, STAGES, ACCS>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned long long* full = (unsigned long long*)(tiles + STAGES * S::STAGE_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* acc_full = empty + STAGES;      // [ACCS]
+  unsigned long long* acc_empty = acc_full + ACCS;    // [ACCS]
+  unsigned* tmem_slot = (unsigned*)(acc_empty + ACCS);
+  float* bias_s = (float*)(tiles + STAGES * S::STAGE_BYTES + 256);   // [ACCS][BN]
+  static_assert(2 * STAGES * 8 + 2 * ACCS * 8 + 4 <= 256, "barriers fit their slot");
+  static_assert(ACCS * BN <= 512 && BN % 32 == 0 && BN <= 256, "accumulators fit tensor memory");
+  constexpr int TMEM_COLS = ACCS * BN <= 32 ? 32 : (ACCS * BN <= 64 ? 64 : (ACCS * BN <= 128 ? 128 : (ACCS * BN <= 256 ? 256 : 512)));
+  constexpr int PM = 2 * BM;   // rows of a pair's tile
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_ctarank();   // 0: the leader
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int tiles_m = (M + PM - 1) / PM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_tiles = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < ACCS; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {   // the same warp of both CTAs allocates (and frees) the pair's columns
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers are initialised before anything is counted on them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  co_pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      long it = 0;
+      bool ok = true;
+      const int head = k_tiles < STAGES ? k_tiles : STAGES;
+      // W of the first tile's first stages before the wait for the predecessor, x after it.
+      if (pair < num_tiles) {
+        const int m0 = (pair % tiles_m) * PM + (int)rank * BM, n0 = (pair / tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kt = 0; kt < head; ++kt) {
+          if (rank == 0) mbar_expect_tx(&full[kt], 2 * S::STAGE_BYTES);
+          tma_load_2d_pair(tiles + kt * S::STAGE_BYTES + S::A_BYTES, &map_w, kt * BK, n0, map_to_cta(&full[kt], 0));
+        }
+        co_pdl_wait();
+        for (int kt = 0; kt < head; ++kt)
+          tma_load_2d_pair(tiles + kt * S::STAGE_BYTES, &map_x, kt * BK, m0, map_to_cta(&full[kt], 0));
+        it = head;
+      }
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+        const int m0 = (tile % tiles_m) * PM + (int)rank * BM, n0 = (tile / tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kt = tile == pair ? head : 0; kt < k_tiles; ++kt, ++it) {
+          const int s = (int)(it % STAGES);
+          if (it >= STAGES && !mbar_wait(&empty[s], (unsigned)((it / STAGES) - 1) & 1)) { atomicExch(status, 11); ok = false; break; }
+          unsigned char* a = tiles + s * S::STAGE_BYTES;
+          const unsigned bar = map_to_cta(&full[s], 0);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * S::STAGE_BYTES);
+          tma_load_2d_pair(a, &map_x, kt * BK, m0, bar);
+          tma_load_2d_pair(a + S::A_BYTES, &map_w, kt * BK, n0, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr unsigned idesc = umma_idesc(PM, BN);
+      long it = 0;
+      int j = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++j) {
+        const int acc = j % ACCS;
+        if (j >= ACCS && !mbar_wait(&acc_empty[acc], (unsigned)((j / ACCS) - 1) & 1)) { atomicExch(status, 14); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned d = tmem_base + (unsigned)(acc * BN);
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = (int)(it % STAGES);
+          if (!mbar_wait(&full[s], (unsigned)(it / STAGES) & 1)) { atomicExch(status, 12); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned char* a = tiles + s * S::STAGE_BYTES;
+          const unsigned long long da = umma_desc(a), db = umma_desc(a + S::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(d, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+          umma_commit_pair(&empty[s]);
+        }
+        if (ok) umma_commit_pair(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int j = 0;
+    co_pdl_wait();   // out may still be in use by the predecessor
+    for (int tile = pair; tile < num_tiles; tile += pairs, ++j) {
+      const int acc = j % ACCS;
+      const int m0 = (tile % tiles_m) * PM + (int)rank * BM, n0 = (tile / tiles_m) * BN;
+      const int row = m0 + quarter * 32 + lane;
+      float* bias_t = bias_s + acc * BN;
+      if (bias) {
+        for (int i = threadIdx.x - 64; i < BN; i += 128) bias_t[i] = n0 + i < N ? co_load_any(bias, bias_dtype, n0 + i) : 0.f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (!mbar_wait(&acc_full[acc], (unsigned)(j / ACCS) & 1)) {
+        if (lane == 0) atomicExch(status, 13);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        unsigned r[32];
+        tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), r);
+        if (row < M) store_piece(r, row, n0 + c0, bias ? bias_t + c0 : nullptr, out, out_dtype, N, ldo, epilogue);
+      }
+      // This warp has read its part of the accumulator: tell the leader's MMA issuer.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
+    }
+  }
+
+  // Wind down: both CTAs meet (nothing of the pair is in flight any more), then free the columns.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+  }
+}
+
 template <int BN, int STAGES>
 int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, int bias_dtype, void* out,
               int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status, cudaStream_t stream,
@@ -492,12 +684,80 @@ int launch_tc_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const voi
   CO_CHECK_LAUNCH("gemm_tc_persistent");
   return 0;
 }
+// Pairs that can be resident at once (a cluster needs two free SMs of one GPC); 0 if unknown.
+template <int BN, int STAGES, int ACCS>
+int pair_slots() {
+  static int slots = -1;
+  if (slots < 0) {
+    auto kernel = gemm_tc_pair_kernel<BN, STAGES, ACCS>;
+    constexpr int smem = PairSmem<BN, STAGES, ACCS>::TOTAL;
+    slots = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return slots;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms > 1 ? (sms & ~1) : 2);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, (void*)kernel, &cfg) == cudaSuccess && clusters > 0) slots = clusters;
+    else (void)cudaGetLastError();
+    if (slots > sms / 2) slots = sms / 2;
+  }
+  return slots;
+}
+
+template <int BN, int STAGES, int ACCS>
+int launch_tc_pair(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, int bias_dtype, void* out,
+                   int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status, cudaStream_t stream) {
+  auto kernel = gemm_tc_pair_kernel<BN, STAGES, ACCS>;
+  constexpr int smem = PairSmem<BN, STAGES, ACCS>::TOTAL;
+  const int slots = pair_slots<BN, STAGES, ACCS>();
+  if (slots <= 0) CO_FAIL("gemm_tc_pair: no pair of CTAs with %d bytes of shared memory fits the device", smem);
+  const long tiles = (long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
+  const int pairs = (int)(tiles < slots ? tiles : slots);
+  cudaError_t le = co_launch_cluster(2, kernel, dim3(2 * pairs), dim3(192), (size_t)smem, stream, mx, mw, bias, bias_dtype,
+                                     out, out_dtype, M, N, K, ldo, epilogue, status);
+  if (le != cudaSuccess) CO_FAIL("gemm_tc_pair: launch failed: %s", cudaGetErrorString(le));
+  CO_CHECK_LAUNCH("gemm_tc_pair");
+  return 0;
+}
+
+// Whether pairs with 256 x 256 tiles suit an [M, N] output: if its tiles fill whole rounds of the
+// resident pairs to three quarters or more (COHERYN_GEMM_PAIR=0 in the environment: never).
+int g_pairs = -1;   // -1: not decided yet; coheryn_gemm_tc_set_pairs overrides the environment
+bool pair_enabled() {
+  if (g_pairs < 0) {
+    const char* e = getenv("COHERYN_GEMM_PAIR");
+    g_pairs = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pairs == 1;
+}
+bool pair_suits(int M, int N) {
+  if (!pair_enabled() || M <= BM) return false;
+  const int slots = pair_slots<256, 6, 2>();
+  if (slots <= 0) return false;
+  const long tiles = (long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+  const long rounds = (tiles + slots - 1) / slots;
+  // useful rows and columns over those the rounds pay for
+  return (double)M * N / ((double)rounds * slots * 2 * BM * 256) >= 0.75;
+}
 }  // namespace
 
 // Tuning knobs for experiments: tile width (0 = by shape, 128 caps it) and stage count
 // (0 = the default of the tile width).
 static int g_bn = 0, g_stages = 0;
 CO_EXPORT void coheryn_gemm_tc_tune(int bn, int stages) { g_bn = bn; g_stages = stages; }
+// Whether coheryn_gemm_bf16_tc may hand suitable shapes to pairs of CTAs (default: yes).
+CO_EXPORT void coheryn_gemm_tc_set_pairs(int on) { g_pairs = on ? 1 : 0; }
 
 // Tile width by shape: 256 columns where the output is wide; with a single row tile (a decode
 // batch, a short portion) narrower tiles put more CTAs on the weight stream.
@@ -527,9 +787,14 @@ static int splits_for(int M, int N, int K, int bn) {
 // shape is not split).  Without the workspace the product runs unsplit.
 CO_EXPORT long coheryn_gemm_tc_workspace_floats(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (pair_suits(M, N)) return 0;
   const int s = splits_for(M, N, K, tile_width(M, N));
   return s > 1 ? (long)s * M * N : 0;
 }
+
+CO_EXPORT int coheryn_gemm_bf16_tc_pair(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
+                                        int out_dtype, int M, int N, int K, long ldx, long ldo, int epilogue,
+                                        int* status, cudaStream_t stream);
 
 // x: [M, K] bfloat16 with row stride ldx; w: [N, K] bfloat16 contiguous; K and ldx multiples
 // of 8, bases 16-byte aligned.  epilogue 0: out[M, N] (+ bias); 1: gated SiLU over
@@ -544,6 +809,8 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc: operands must be 16-byte aligned");
   if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc: gated epilogue needs an even number of rows");
   if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
+  if (status && pair_suits(M, N))
+    return coheryn_gemm_bf16_tc_pair(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, ldo, epilogue, status, stream);
   const int bn = tile_width(M, N);
   const long tiles_m = (M + BM - 1) / BM;
   int splits = splits_for(M, N, K, bn);
@@ -563,4 +830,21 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (bn == 64) GO(64, 8);
   GO(32, 8);
 #undef GO
+}
+
+// The same product by pairs of CTAs (see gemm_tc_pair_kernel): 256 x 256 tiles, for many rows.
+// status receives 11 / 12 / 13 / 14 as above.
+CO_EXPORT int coheryn_gemm_bf16_tc_pair(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
+                                        int out_dtype, int M, int N, int K, long ldx, long ldo, int epilogue,
+                                        int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc_pair: K = %d and the row stride %ld must be multiples of 8", K, ldx);
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc_pair: operands must be 16-byte aligned");
+  if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc_pair: gated epilogue needs an even number of rows");
+  if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_tc_pair: unknown epilogue %d", epilogue);
+  if (!status) CO_FAIL("gemm_bf16_tc_pair: a status word is required");
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, K, 128))
+    CO_FAIL("gemm_bf16_tc_pair: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%ld)", M, N, K, ldx);
+  return launch_tc_pair<256, 6, 2>(mx, mw, bias, bias_dtype, out, out_dtype, M, N, K, ldo, epilogue, status, stream);
 }

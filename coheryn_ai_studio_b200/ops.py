@@ -339,6 +339,33 @@ def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
         c_int(1 if gated else 0), _ptr(tc_status(x.device)), _ptr(workspace), c_long(floats), _stream()))
 
 
+def set_gemm_pairs(on: bool) -> None:
+    """Whether ``gemm_bf16_tc`` hands suitable shapes to the kernel of CTA pairs (default: yes)."""
+    core().coheryn_gemm_tc_set_pairs(c_int(1 if on else 0))
+
+
+def gemm_tc_splits(M: int, N: int, K: int) -> int:
+    """K splits that ``gemm_bf16_tc`` uses for this shape (1: none; a shape run by CTA pairs: 1)."""
+    lib = core()
+    lib.coheryn_gemm_tc_workspace_floats.restype = ctypes.c_long
+    return max(1, int(lib.coheryn_gemm_tc_workspace_floats(c_int(M), c_int(N), c_int(K))) // (M * N))
+
+
+def gemm_bf16_tc_pair(x, w, bias, out, gated: bool = False) -> None:
+    """The many-rows product by pairs of CTAs sharing 256 x 256 tiles (tcgen05 cta_group::2);
+    see gemm_tc_pair_kernel in csrc/gemm_tc.cu."""
+    _dev(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == K
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N // 2 if gated else N)
+    lib = core()
+    _check(lib, lib.coheryn_gemm_bf16_tc_pair(
+        _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
+        c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)),
+        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _stream()))
+
+
 _few_workspaces = {}
 _few_retired = []     # outgrown workspaces stay alive: captured graphs may still name them
 

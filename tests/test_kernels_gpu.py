@@ -197,6 +197,43 @@ def test_gemm_bf16_tc_few(shape, gated):
     ops().check_tc_status(DEV)
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 512, 256), (300, 1000, 200), (1000, 520, 1096), (2048, 2048, 1536),
+                                   (129, 40, 8), (2304, 4000, 328), (4096, 1536, 520)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_gemm_bf16_tc_pairs_of_ctas(shape, gated):
+    """The product by pairs of CTAs (tcgen05 cta_group::2, 256 x 256 tiles, two accumulators)
+    against float64, with tails in M, N and K and more tiles than pairs; and the same bits as
+    the single-CTA kernel, which sums K in the same order."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    x = t32(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
+    w = t32((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
+    acc = x.double().cpu() @ w.double().cpu().T
+    if gated:
+        g, u = acc[:, 0::2], acc[:, 1::2]
+        ref = g / (1 + torch.exp(-g)) * u
+        out = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_tc_pair(x, w, None, out, gated=True)
+        ops().check_tc_status(DEV)
+        assert (out.double().cpu() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max()) + 1e-3
+    else:
+        b = t32(rng.standard_normal(N).astype(np.float32))
+        ref = acc + b.double().cpu()
+        out = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc_pair(x, w, b, out)
+        ops().check_tc_status(DEV)
+        assert (out.double().cpu() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+        ops().set_gemm_pairs(False)
+        try:
+            single = torch.empty(M, N, dtype=torch.float32, device=DEV)
+            ops().gemm_bf16_tc(x, w, b, single)
+            unsplit = ops().gemm_tc_splits(M, N, K) == 1
+        finally:
+            ops().set_gemm_pairs(True)
+        if unsplit:
+            assert torch.equal(out, single)
+
+
 @pytest.mark.parametrize("shape", [(128, 256, 64), (65, 32, 8), (200, 300, 136), (300, 1000, 96), (257, 96, 1000),
                                    (2048, 2048, 1536), (513, 1536, 8960), (130, 151936, 64), (1000, 48, 72),
                                    (64, 1536, 8960), (40, 2048, 1536), (17, 100, 520), (2304, 17920, 1536), (2048, 1536, 1536),
