@@ -427,6 +427,9 @@ FEW_DEFER_M = int(os.environ.get("COHERYN_FEW_DEFER_M", "64"))
 # rows: for K = 1536 (12 slices of two steps) the norm that adds twelve parts loses more than
 # the product gains over the mma.sync kernel; for K = 8960 the pair is 5 us faster.
 DEFER_MIN_K = 4096
+# With more than SMALL_M_SHORT rows the alternative is the many-rows kernel plus the kernel that adds
+# its K splits: there the slices pay from K = 1024 on (1 % of a decode step at 40 and 64 rows).
+DEFER_MIN_K_WIDE = int(os.environ.get("COHERYN_DEFER_MIN_K_WIDE", "1024"))
 
 
 def _few_ok(x, w, partial_ok: bool = False) -> bool:
@@ -471,7 +474,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     result may come as a float32 stack [splits, M, N] of partial sums whose addition is left
     to the consumer (``add_rmsnorm`` takes such a stack as its delta)."""
     M, N = x.shape[0], w.shape[0]
-    if partial_ok and out is None and M and w.shape[1] >= DEFER_MIN_K and _few_shape_ok(x, w, FEW_DEFER_M):
+    if (partial_ok and out is None and M and w.shape[1] >= (DEFER_MIN_K_WIDE if M > SMALL_M_SHORT else DEFER_MIN_K)
+            and _few_shape_ok(x, w, FEW_DEFER_M)):
         splits = few_splits(N, w.shape[1])
         if splits > 1:
             parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
