@@ -167,3 +167,33 @@ def test_command_line_and_python_entry(folders, dtype):
                           "--tokens", "1,2", "--max-tokens", "6", "--context", "4"], capture_output=True, text=True)
     assert bad.returncode == 2 and json.loads(bad.stderr.strip().splitlines()[-1])["code"] == "invalid_request"
     assert api.generate(folders["A"], [p], max_tokens=6, context=64, dtype=dtype)[0]["token_ids"] == out["token_ids"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_zero_matrices_generate_token_zero(tmp_path, dtype):
+    """The reference's synthetic model (crates/coheryn-engine/tests/common/mod.rs:99-118,
+    tests/engine.rs:35-59): embeddings 1, every matrix 0, so all logits are 0 and greedy
+    generation emits token 0 for ever (the first maximum)."""
+    import torch
+    from coheryn_ai_studio_b200.api import generate
+    from coheryn_ai_studio_b200.weights.loader import write_model_folder
+    H, V, I = 32, 259, 48
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=1, hidden_size=H,
+               num_attention_heads=2, num_key_value_heads=1, intermediate_size=I, vocab_size=V, rms_norm_eps=1e-6,
+               rope_theta=1e6, max_position_embeddings=64, hidden_act="silu", tie_word_embeddings=False)
+    bf = torch.bfloat16
+    w = {"model.embed_tokens.weight": torch.ones(V, H, dtype=bf), "model.norm.weight": torch.ones(H),
+         "lm_head.weight": torch.zeros(V, H, dtype=bf)}
+    p = "model.layers.0."
+    for n, shape in [("self_attn.q_proj.weight", (H, H)), ("self_attn.k_proj.weight", (H // 2, H)),
+                     ("self_attn.v_proj.weight", (H // 2, H)), ("self_attn.o_proj.weight", (H, H)),
+                     ("mlp.gate_proj.weight", (I, H)), ("mlp.up_proj.weight", (I, H)), ("mlp.down_proj.weight", (H, I))]:
+        w[p + n] = torch.zeros(shape, dtype=bf)
+    for n, size in [("self_attn.q_proj.bias", H), ("self_attn.k_proj.bias", H // 2), ("self_attn.v_proj.bias", H // 2)]:
+        w[p + n] = torch.zeros(size)
+    w[p + "input_layernorm.weight"] = torch.ones(H)
+    w[p + "post_attention_layernorm.weight"] = torch.ones(H)
+    folder = str(tmp_path / "zeros")
+    write_model_folder(folder, cfg, w)
+    out = generate(folder, [[5], [7, 8, 9]], max_tokens=4, dtype=dtype, context=32)
+    assert [r["token_ids"] for r in out] == [[0, 0, 0, 0], [0, 0, 0, 0]]
