@@ -29,9 +29,59 @@ struct Smem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 2 * BN * 4 /* bias */;
 };
 
+// Sixty-four bfloat16 output columns of a warp's 32 rows (lane = row) through shared memory and
+// one TMA store: the accumulator columns come from tensor memory (64 of them, or 128 gate/up
+// columns in the gated case), bias or gate is applied, the 128 bytes of a row go to `stage`
+// (4 KB, 1024-byte aligned) in the 128-byte swizzle of the output tensor map, and lane 0 sends
+// the 32 x 64 box.  Rows and columns beyond the tensor are clipped by the copy.
+// bias_chunk: the bias of the chunk's first accumulator column (or null).
+__device__ __forceinline__ void store_chunk_tma(unsigned tmem_chunk, const float* bias_chunk, bool gated,
+                                                unsigned char* stage, const CUtensorMap* map_out, int out_col,
+                                                int out_row, int lane) {
+  uint4 pk[8];
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(pk);
+  if (gated) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      unsigned r[32];
+      tmem_ld32(tmem_chunk + 32 * q, r);
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        const float g0 = __uint_as_float(r[2 * j]), u0 = __uint_as_float(r[2 * j + 1]);
+        const float g1 = __uint_as_float(r[2 * j + 2]), u1 = __uint_as_float(r[2 * j + 3]);
+        h[q * 8 + (j >> 1)] = __floats2bfloat162_rn(__fdividef(g0, 1.0f + __expf(-g0)) * u0,
+                                                    __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      unsigned r[32];
+      tmem_ld32(tmem_chunk + 32 * q, r);
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float a = __uint_as_float(r[j]), b = __uint_as_float(r[j + 1]);
+        if (bias_chunk) { a += bias_chunk[32 * q + j]; b += bias_chunk[32 * q + j + 1]; }
+        h[q * 16 + (j >> 1)] = __floats2bfloat162_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = pk[c];
+  fence_proxy_async();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(map_out, stage, out_col, out_row);
+    tma_store_commit();
+  }
+}
+constexpr int STAGING_BYTES = 4 * 2 * 4096;   // four epilogue warps, two chunks each
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_out, int tma_out,
                const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype, int M, int N,
                int K, long ldo, int epilogue, int* __restrict__ status, float* __restrict__ partial, int k_per_split) {
   using S = Smem<BN, STAGES>;
@@ -116,7 +166,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const bool waited = mbar_wait(accum_full, 0);
     if (!waited && lane == 0) atomicExch(status, 13);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (waited) {
+    if (waited && tma_out && !partial) {
+      // bfloat16 output through shared memory and TMA stores: every MMA is complete, so the
+      // stages are free and serve as the staging area (two 4 KB chunks per warp).
+      const bool gated = epilogue == EPI_GATED_SILU;
+      const int step = gated ? 128 : 64;
+      unsigned char* stage = tiles + quarter * 8192;
+      int chunk = 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += step, ++chunk) {
+        if (n0 + c0 >= N) break;
+        if (chunk >= 2) {
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        store_chunk_tma(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, bias && !gated ? bias_s + c0 : nullptr,
+                        gated, stage + (chunk & 1) * 4096, &map_out, gated ? (n0 + c0) >> 1 : n0 + c0, m0 + quarter * 32, lane);
+      }
+      if (lane == 0) tma_store_wait_all();
+    } else if (waited) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= N) break;
@@ -490,25 +558,32 @@ struct PairSmem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = (BN / 2) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + ACCS * BN * 4 /* bias */;
+  // Staging chunks per epilogue warp: two where shared memory allows, else one.
+  static constexpr int SBUF = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + 256 + ACCS * BN * 4 <= 227 * 1024 ? 2 : 1;
+  static constexpr int STAGING = SBUF * 4 * 4096;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING + 1024 /* alignment slack */ + 256 /* barriers */ + ACCS * BN * 4 /* bias */;
+  static_assert(TOTAL <= 227 * 1024, "stages, staging area and barriers fit shared memory");
 };
 
 template <int BN, int STAGES, int ACCS>
 __global__ void __launch_bounds__(192)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_out, int tma_out,
                     const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype,
                     int M, int N, int K, long ldo, int epilogue, int* __restrict__ status) {
   using S = PairSmem<BN, STAGES, ACCS>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned long long* full = (unsigned long long*)(tiles + STAGES * S::STAGE_BYTES);
+  unsigned char* staging = tiles + STAGES * S::STAGE_BYTES;      // [4 warps][SBUF][4 KB], 1024-byte aligned
+  unsigned long long* full = (unsigned long long*)(staging + S::STAGING);
   unsigned long long* empty = full + STAGES;
   unsigned long long* acc_full = empty + STAGES;      // [ACCS]
   unsigned long long* acc_empty = acc_full + ACCS;    // [ACCS]
   unsigned* tmem_slot = (unsigned*)(acc_empty + ACCS);
-  float* bias_s = (float*)(tiles + STAGES * S::STAGE_BYTES + 256);   // [ACCS][BN]
+  float* bias_s = (float*)(staging + S::STAGING + 256);   // [ACCS][BN]
   static_assert(2 * STAGES * 8 + 2 * ACCS * 8 + 4 <= 256, "barriers fit their slot");
-  static_assert(ACCS * BN <= 512 && BN % 32 == 0 && BN <= 256, "accumulators fit tensor memory");
+  static_assert(ACCS * BN <= 512 && BN % 128 == 0 && BN <= 256, "accumulators fit tensor memory, chunks of 128 divide them");
+  static_assert(S::STAGE_BYTES % 1024 == 0, "the staging area stays 1024-byte aligned");
   constexpr int TMEM_COLS = ACCS * BN <= 32 ? 32 : (ACCS * BN <= 64 ? 64 : (ACCS * BN <= 128 ? 128 : (ACCS * BN <= 256 ? 256 : 512)));
   constexpr int PM = 2 * BM;   // rows of a pair's tile
 
@@ -591,7 +666,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
   } else {
     const int quarter = warp & 3;
-    int j = 0;
+    int j = 0, chunk = 0;
     co_pdl_wait();   // out may still be in use by the predecessor
     for (int tile = pair; tile < num_tiles; tile += pairs, ++j) {
       const int acc = j % ACCS;
@@ -607,18 +682,36 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (tma_out) {
+        const bool gated = epilogue == EPI_GATED_SILU;
+        const int step = gated ? 128 : 64;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= N) break;
-        unsigned r[32];
-        tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), r);
-        if (row < M) store_piece(r, row, n0 + c0, bias ? bias_t + c0 : nullptr, out, out_dtype, N, ldo, epilogue);
+        for (int c0 = 0; c0 < BN; c0 += step, ++chunk) {
+          if (n0 + c0 >= N) break;
+          if (chunk >= S::SBUF) {   // the chunk that used this staging buffer has left it
+            if (lane == 0) tma_store_wait_read<S::SBUF - 1>();
+            __syncwarp();
+          }
+          store_chunk_tma(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0),
+                          bias && !gated ? bias_t + c0 : nullptr, gated,
+                          staging + (quarter * S::SBUF + chunk % S::SBUF) * 4096, &map_out,
+                          gated ? (n0 + c0) >> 1 : n0 + c0, m0 + quarter * 32, lane);
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= N) break;
+          unsigned r[32];
+          tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), r);
+          if (row < M) store_piece(r, row, n0 + c0, bias ? bias_t + c0 : nullptr, out, out_dtype, N, ldo, epilogue);
+        }
       }
       // This warp has read its part of the accumulator: tell the leader's MMA issuer.
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
     }
+    if (tma_out && lane == 0) tma_store_wait_all();
   }
 
   // Wind down: both CTAs meet (nothing of the pair is in flight any more), then free the columns.
@@ -631,10 +724,24 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   }
 }
 
+// The tensor map of a bfloat16 output [M, n_out] with row stride ldo for the TMA-store epilogue
+// (boxes of 32 rows x 64 columns); false if the output does not qualify (another dtype, a base
+// or a row pitch off the 16-byte grid) or COHERYN_TMA_STORE=0 is in the environment.
+bool make_out_map(CUtensorMap* map, const void* out, int out_dtype, int M, int n_out, long ldo) {
+  static const bool enabled = !(getenv("COHERYN_TMA_STORE") && getenv("COHERYN_TMA_STORE")[0] == '0');
+  if (!enabled || out_dtype != CO_BF16 || !out || ((uintptr_t)out & 15) || (ldo & 7) || n_out <= 0) return false;
+  return make_map(map, out, M, n_out, ldo, 32);
+}
+
 template <int BN, int STAGES>
 int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, int bias_dtype, void* out,
               int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status, cudaStream_t stream,
               float* partial = nullptr, int splits = 1) {
+  // bfloat16 output leaves through shared memory and TMA stores where whole chunks of 64 output
+  // columns divide the tile.
+  CUtensorMap mo = mx;
+  const int tma_out = !(partial && splits > 1) && BN % (epilogue == EPI_GATED_SILU ? 128 : 64) == 0 &&
+                      make_out_map(&mo, out, out_dtype, M, epilogue == EPI_GATED_SILU ? N / 2 : N, ldo) ? 1 : 0;
   auto kernel = gemm_tc_kernel<BN, STAGES>;
   constexpr int smem = Smem<BN, STAGES>::TOTAL;
   static bool configured = false;
@@ -647,7 +754,7 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
   const int k_per_split = partial ? (k_tiles + splits - 1) / splits : k_tiles;
   const int used = partial ? (k_tiles + k_per_split - 1) / k_per_split : 1;    // no split is left empty
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, used);
-  cudaError_t le = co_launch(kernel, grid, dim3(192), (size_t)smem, stream, mx, mw, bias, bias_dtype, out, out_dtype, M, N,
+  cudaError_t le = co_launch(kernel, grid, dim3(192), (size_t)smem, stream, mx, mw, mo, tma_out, bias, bias_dtype, out, out_dtype, M, N,
                              K, ldo, epilogue, status, used > 1 ? partial : (float*)nullptr, k_per_split);
   if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("gemm_tc");
@@ -724,7 +831,9 @@ int launch_tc_pair(const CUtensorMap& mx, const CUtensorMap& mw, const void* bia
   if (slots <= 0) CO_FAIL("gemm_tc_pair: no pair of CTAs with %d bytes of shared memory fits the device", smem);
   const long tiles = (long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
   const int pairs = (int)(tiles < slots ? tiles : slots);
-  cudaError_t le = co_launch_cluster(2, kernel, dim3(2 * pairs), dim3(192), (size_t)smem, stream, mx, mw, bias, bias_dtype,
+  CUtensorMap mo = mx;
+  const int tma_out = make_out_map(&mo, out, out_dtype, M, epilogue == EPI_GATED_SILU ? N / 2 : N, ldo) ? 1 : 0;
+  cudaError_t le = co_launch_cluster(2, kernel, dim3(2 * pairs), dim3(192), (size_t)smem, stream, mx, mw, mo, tma_out, bias, bias_dtype,
                                      out, out_dtype, M, N, K, ldo, epilogue, status);
   if (le != cudaSuccess) CO_FAIL("gemm_tc_pair: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("gemm_tc_pair");

@@ -41,6 +41,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
+// A tile in shared memory (as the tensor map's box, 128-byte swizzled) to global memory; rows and
+// columns beyond the tensor are not written.  The copies of a thread form bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's groups still READ their shared memory / are still in flight.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's ordinary shared-memory writes before later copies of the async proxy.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
 // 128-byte mode: start address >> 4, leading byte offset 1 (unused with a swizzle), stride
 // byte offset 1024 >> 4 between groups of eight rows, descriptor version 1, layout type 2.
