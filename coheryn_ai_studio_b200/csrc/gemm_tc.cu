@@ -9,8 +9,11 @@
 //            issues the two TMA loads (x tile 128 x 64, W tile BN x 64);
 //   warp 1   MMA issuer: waits for a full stage, issues four m128 nBN k16 MMAs, and lets
 //            tcgen05.commit release the stage (and, after the last step, signal the epilogue);
-//   warps 2-5 epilogue: each reads its 32 lanes of the accumulator 32 columns at a time,
-//            applies bias or the gate, converts and stores.
+//   warps 2-5 epilogue: each reads its 32 lanes of the accumulator, applies bias or the gate
+//            and converts.  bfloat16 output goes 64 columns at a time into a swizzled 4 KB
+//            staging buffer in shared memory (the stages are free by then) and leaves as a
+//            32 x 64 box through a TMA store, two boxes in flight per warp; float32 output
+//            and split-K partial sums are stored from registers, 32 columns at a time.
 // Rows and columns beyond M, N and the K tail are zero filled by TMA and masked on store.
 // Every wait is bounded: on expiry the kernel records an error code and winds down.
 #include <cuda.h>
