@@ -809,6 +809,7 @@ int launch_stream(const void* q, long q_stride, void* out, long out_stride, cons
 CO_EXPORT int coheryn_attn_head_dim() { return HD; }
 CO_EXPORT int coheryn_attn_split_keys() { return SPLIT_MIN; }
 // keys = 128, 256 or 512 fixes the positions per CTA of the decode kernel; 0 restores the choice by batch size.
+CO_EXPORT void coheryn_attn_set_tc_cluster(int cluster) { coheryn_attention_tc_set_cluster(cluster); }
 CO_EXPORT void coheryn_attn_set_split(int keys) { g_forced_split = (keys == 128 || keys == 256 || keys == 512) ? keys : 0; }
 
 // Floats of scratch that coheryn_attention_bf16 needs for B requests of at most
@@ -844,7 +845,7 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
     // Prompt portions: the tcgen05 kernel where it takes the shape, else the mma.sync one.
     if (status && coheryn_attention_tc_takes(nh, nkv, page_size) && ((uintptr_t)out & 7) == 0) {
       if (coheryn_attention_tc_launch(q, q_stride, total_tokens, out, out_stride, k_cache, v_cache, num_pages, block_tables,
-                                      max_blocks, cu_q, kv_lens, B, nh, nkv, page_size, window, scale_log2, max_rows,
+                                      max_blocks, cu_q, kv_lens, B, nh, nkv, page_size, window, scale_log2, max_rows, max_kv_len,
                                       split_path ? 1 : 0, status, stream))
         return -1;
     } else {

@@ -19,6 +19,12 @@
 // S for the next key tile is issued as soon as the softmax threads hold the current one in
 // registers, so the exponentials overlap the next Q K^T.
 //
+// A short portion over a long context makes few row tiles with many key tiles each.  The kernel
+// then runs as clusters of 2, 4 or 8 CTAs along x that share a row tile: CTA r takes the key
+// tiles [N r / C, N (r + 1) / C), all but the last publish their (reference maximum, sum,
+// accumulator) in their own shared memory, and the last one, which always holds the diagonal
+// tile, adds the parts in rank order through distributed shared memory and stores the rows.
+//
 // Slots of a page beyond the request's length, and pages a window has given back (table
 // entry -1, fetched as an out-of-range box = zeros), are masked by position; the cache pool
 // must hold finite numbers everywhere (it is zeroed when made).
@@ -52,6 +58,30 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // ex2(-inf) = +0
   return y;
 }
+
+__device__ __forceinline__ unsigned cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned cluster_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Four floats from the same place in the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ float4 ld_cluster4(const float* local, unsigned rank) {
+  unsigned ra;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_cluster1(const float* local, unsigned rank) {
+  unsigned ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+constexpr int XLD = HD + 4;                       // row stride (floats) of a CTA's published accumulator
+constexpr int MAX_CLUSTER = 8;
+static_assert(!SUPPORTED || (size_t)(128 * XLD + 256) * 4 <= (size_t)Q_BYTES + (size_t)NST * 2 * KV_BYTES, "a published accumulator fits the tiles");
 
 __global__ void __launch_bounds__(320, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -94,8 +124,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   co_pdl_launch_dependents();
   co_pdl_wait();
 
-  // Late row tiles see the most keys: they are started first.
-  const int b = blockIdx.z, kvh = blockIdx.y, rt = gridDim.x - 1 - blockIdx.x;
+  // Late row tiles see the most keys: they are started first.  The CTAs of a cluster (along x)
+  // share a row tile and split its key tiles among them; the last one merges.
+  const int csize = (int)cluster_size(), crank = (int)cluster_rank();
+  const int b = blockIdx.z, kvh = blockIdx.y, rt = (int)(gridDim.x / csize) - 1 - (int)(blockIdx.x / csize);
   const int G = nh / nkv, TOK = 128 / G, RT = TOK * G;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
   const int rows = q_len * G;
@@ -104,8 +136,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const int row_first = rt * RT, row_last = min(rows, row_first + RT) - 1;
   const int pos_lo = base_pos + row_first / G, pos_hi = base_pos + row_last / G;
   const int key_first = window > 0 ? max(0, pos_lo - window + 1) : 0;
-  const int tile_first = key_first / BN;
-  const int n_tiles = active ? pos_hi / BN - tile_first + 1 : 0;
+  const int all_tiles = active ? pos_hi / BN - key_first / BN + 1 : 0;        // of the row tile
+  const int my_first = all_tiles * crank / csize;                             // rank r: tiles [N r / C, N (r + 1) / C)
+  const int n_tiles = all_tiles * (crank + 1) / csize - my_first;             // of this CTA (0 only below the last rank)
+  const int tile_first = key_first / BN + my_first;                           // this CTA's first key tile
+  const bool merger = crank == csize - 1;
+  float* xfer = reinterpret_cast<float*>(q_s);                                // [128][XLD] accumulator, then m[128], l[128]: over the tiles
+  // softmax threads' state, finished after the cluster has met
+  float m = -INFINITY, l = 0.f;
+  bool ok = true;
 
   if (warp == 0) {
     if (n_tiles > 0) {
@@ -199,8 +238,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int pos = base_pos + (row_first + row) / G;
     const int hi = valid ? pos : -1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(s_full, (unsigned)j & 1)) { if (lane == 0) atomicExch(status, 37); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -287,28 +324,89 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // The row's sum: the first half's plus the second's.
     row_ex[half][row] = l;
     asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-    if (ok) {
-      const float inv = 1.0f / (row_ex[0][row] + row_ex[1][row]);
-      const int rr = row_first + row;
-      bf16* orow = out + (size_t)(tok0 + rr / G) * out_stride + (size_t)(kvh * G + rr % G) * HD;
+    l = row_ex[0][row] + row_ex[1][row];
+    if (!merger) {
+      // Publish (reference maximum, sum, accumulator) over the Q and K/V tiles, which nothing reads
+      // any more: the last MMA is complete.
+      if (half == 0) { xfer[128 * XLD + row] = m; xfer[128 * XLD + 128 + row] = l; }
 #pragma unroll 1
       for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
         unsigned o[32];
-        tmem_ld32(lane_addr + COL_O + c0, o);     // warp-collective: invalid rows read too, and skip the store
-        if (valid) {
+        tmem_ld32(lane_addr + COL_O + c0, o);
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-            __nv_bfloat162 d = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-            uint2 raw;
-            raw.x = *reinterpret_cast<unsigned*>(&a);
-            raw.y = *reinterpret_cast<unsigned*>(&d);
-            *reinterpret_cast<uint2*>(orow + c0 + c) = raw;
-          }
+        for (int c = 0; c < 32; c += 4)
+          *reinterpret_cast<float4*>(xfer + row * XLD + c0 + c) =
+              make_float4(__uint_as_float(o[c]), __uint_as_float(o[c + 1]), __uint_as_float(o[c + 2]), __uint_as_float(o[c + 3]));
+      }
+    }
+  }
+
+  // The cluster meets: the parts are published.  (Every thread of every CTA comes here, whatever
+  // happened in its role, so nobody waits for a CTA that gave up.)
+  const bool clustered = csize > 1 && all_tiles > 0;
+  if (clustered) {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_barrier();
+  }
+  if (warp >= 2 && merger && n_tiles > 0 && ok) {
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
+    const bool valid = row < RT && row_first + row < rows;
+    // Parts of the other CTAs that had key tiles, in rank order; factors relative to the largest
+    // reference maximum.
+    float pm[MAX_CLUSTER], pl[MAX_CLUSTER];
+    float M = m;
+#pragma unroll
+    for (int p = 0; p < MAX_CLUSTER - 1; ++p) {
+      pm[p] = -INFINITY; pl[p] = 0.f;
+      if (p < csize - 1 && all_tiles * (p + 1) / csize - all_tiles * p / csize > 0) {
+        pm[p] = ld_cluster1(xfer + 128 * XLD + row, (unsigned)p);
+        pl[p] = ld_cluster1(xfer + 128 * XLD + 128 + row, (unsigned)p);
+        M = fmaxf(M, pm[p]);
+      }
+    }
+    const float M_use = M == -INFINITY ? 0.f : M;
+    const float f_own = ex2_approx(m - M_use);
+    float den = l * f_own;
+#pragma unroll
+    for (int p = 0; p < MAX_CLUSTER - 1; ++p) {
+      pm[p] = ex2_approx(pm[p] - M_use);           // now the part's factor (0 for a part without tiles)
+      den += pl[p] * pm[p];
+    }
+    const float inv = 1.0f / den;
+    const int rr = row_first + row;
+    bf16* orow = out + (size_t)(tok0 + rr / G) * out_stride + (size_t)(kvh * G + rr % G) * HD;
+#pragma unroll 1
+    for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+      unsigned o[32];
+      tmem_ld32(lane_addr + COL_O + c0, o);     // warp-collective: invalid rows read too, and skip the store
+      float v[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(o[c]) * f_own;
+#pragma unroll 1
+      for (int p = 0; p < csize - 1; ++p) {
+        if (pm[p] == 0.f) continue;
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float4 x = ld_cluster4(xfer + row * XLD + c0 + c, (unsigned)p);
+          v[c] += x.x * pm[p]; v[c + 1] += x.y * pm[p]; v[c + 2] += x.z * pm[p]; v[c + 3] += x.w * pm[p];
+        }
+      }
+      if (valid) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          __nv_bfloat162 a = __floats2bfloat162_rn(v[c] * inv, v[c + 1] * inv);
+          __nv_bfloat162 d = __floats2bfloat162_rn(v[c + 2] * inv, v[c + 3] * inv);
+          uint2 raw;
+          raw.x = *reinterpret_cast<unsigned*>(&a);
+          raw.y = *reinterpret_cast<unsigned*>(&d);
+          *reinterpret_cast<uint2*>(orow + c0 + c) = raw;
         }
       }
     }
   }
+  if (clustered) cluster_barrier();   // nobody leaves while its published part may still be read
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -319,6 +417,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 }  // namespace
+
+static int g_forced_cluster = -1;   // -1: the environment decides at the first launch; 0: by shape
+void coheryn_attention_tc_set_cluster(int cluster) { g_forced_cluster = cluster; }
 
 bool coheryn_attention_tc_takes(int nh, int nkv, int page_size) {
   if (!SUPPORTED || nkv <= 0 || nh % nkv) return false;
@@ -332,7 +433,7 @@ bool coheryn_attention_tc_takes(int nh, int nkv, int page_size) {
 int coheryn_attention_tc_launch(const void* q, long q_stride, int total_tokens, void* out, long out_stride,
                                 const void* k_cache, const void* v_cache, int num_pages, const int* block_tables,
                                 int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
-                                int page_size, int window, float scale_log2, int max_rows, int skip_small,
+                                int page_size, int window, float scale_log2, int max_rows, int max_kv_len, int skip_small,
                                 int* status, cudaStream_t stream) {
   if (!SUPPORTED) CO_FAIL("attention_tc: head size %d is not a multiple of 64 up to 256", HD);
   const int G = nh / nkv, TOK = 128 / G, RT = TOK * G;
@@ -359,10 +460,22 @@ int coheryn_attention_tc_launch(const void* q, long q_stride, int total_tokens, 
     if (e != cudaSuccess) CO_FAIL("attention_tc: %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((max_rows + RT - 1) / RT, nkv, B);
-  cudaError_t le = co_launch(attn_tc_kernel, grid, dim3(320), (size_t)SMEM_BYTES, stream, mq, mk, mv, (bf16*)out, out_stride,
-                             block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows, window,
-                             scale_log2, skip_small, rows_per_box, status);
+  // CTAs per row tile (a cluster that splits the tile's keys): more while even the split leaves SMs
+  // idle (a short portion over a long context) and every CTA still gets eight key tiles or more; a
+  // CTA's fixed cost is several key tiles' worth, so a batch that fills the GPU stays unsplit.
+  // COHERYN_ATTN_TC_CLUSTER in the environment or coheryn_attention_tc_set_cluster fixes it.
+  const int row_tiles = (max_rows + RT - 1) / RT;
+  const long ctas = (long)row_tiles * nkv * B;
+  const int key_tiles = (max_kv_len + BN - 1) / BN;
+  if (g_forced_cluster < 0) g_forced_cluster = getenv("COHERYN_ATTN_TC_CLUSTER") ? atoi(getenv("COHERYN_ATTN_TC_CLUSTER")) : 0;
+  const int forced = g_forced_cluster;
+  int cluster = 1;
+  while (cluster < MAX_CLUSTER && ctas * cluster * 2 <= 148L && key_tiles >= 16 * cluster) cluster *= 2;
+  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) cluster = forced;
+  dim3 grid(row_tiles * cluster, nkv, B);
+  cudaError_t le = co_launch_cluster(cluster, attn_tc_kernel, grid, dim3(320), (size_t)SMEM_BYTES, stream, mq, mk, mv, (bf16*)out,
+                                     out_stride, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows,
+                                     window, scale_log2, skip_small, rows_per_box, status);
   if (le != cudaSuccess) CO_FAIL("attention_tc: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("attn_tc");
   return 0;

@@ -525,6 +525,12 @@ def set_attention_split(head_dim: int, keys: int) -> None:
     attention_lib(head_dim).coheryn_attn_set_split(c_int(keys))
 
 
+def set_attention_tc_cluster(head_dim: int, cluster: int) -> None:
+    """Fix the number of CTAs (1, 2, 4 or 8) that share a row tile of the prompt-portion attention
+    kernel and split its keys; 0 restores the choice by shape.  For tests and experiments."""
+    attention_lib(head_dim).coheryn_attn_set_tc_cluster(c_int(cluster))
+
+
 def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads, num_kv_heads,
                    head_dim, page_size, window, scale, cu_q=None, kv_lens=None, q_lens=None,
                    max_kv_len=None, force_simple=False) -> None:

@@ -413,10 +413,13 @@ def test_attention_finds_a_far_key(dtype):
 @pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 16), (4, 1, 64, 8), (8, 8, 128, 64), (6, 2, 64, 128),
                                             (16, 1, 128, 256), (3, 1, 192, 32), (2, 1, 256, 16)])
 @pytest.mark.parametrize("window", [None, 200])
-def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window):
+@pytest.mark.parametrize("cluster", [0, 2, 8])
+def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window, cluster):
     """Prompt portions through the tcgen05 kernel (S and O in tensor memory, P fed back from
     it): whole prompts and tails that start inside a key tile, several key tiles, row tiles
-    that end inside a token group, a window that begins inside a tile."""
+    that end inside a token group, a window that begins inside a tile; with the key tiles of a
+    row tile split over 2 or 8 CTAs of a cluster (some of them left without a tile) and merged
+    through distributed shared memory."""
     rng = np.random.default_rng(nh + hd + page)
     lens = [300, 700, 129, 64]
     q_lens = [300, 257, 20, 64]
@@ -430,10 +433,14 @@ def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window):
     scale = 1.0 / np.sqrt(hd)
     cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     out = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
-    ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
-                         nh, nkv, hd, page, window, scale, cu_q=t32(cu), kv_lens=t32(np.asarray(lens, np.int32)),
-                         q_lens=q_lens, max_kv_len=max(lens))
-    ops().check_tc_status(DEV)
+    ops().set_attention_tc_cluster(hd, cluster)
+    try:
+        ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
+                             nh, nkv, hd, page, window, scale, cu_q=t32(cu), kv_lens=t32(np.asarray(lens, np.int32)),
+                             q_lens=q_lens, max_kv_len=max(lens))
+        ops().check_tc_status(DEV)
+    finally:
+        ops().set_attention_tc_cluster(hd, 0)
     ref = attention_reference(q.float().cpu().numpy(), ks, vs, reqs, poss, nh, nkv, hd, window, scale)
     tol = 2 ** -8 * np.abs(ref) + 2 ** -8
     err = np.abs(out.float().cpu().numpy() - ref)
