@@ -76,9 +76,11 @@ class CacheManager:
                                              device=device)
             else:
                 raise TypeError(f"schedule entry {e}: unknown cache requirement {need!r}")
+        # One page more than the pool hands out: page ``num_pages`` belongs to no request and takes
+        # the writes of padding rows (a decode batch padded up to a captured width).
         for g in self.groups:
             n = g.need
-            g.tensor = torch.zeros((len(g.entries), 2, num_pages, n.num_kv_heads, page_size, n.head_dim),
+            g.tensor = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
                                    dtype=dtype, device=device)
         self.slots = SlotPool(max_requests)
         self.requests: Dict[str, _Request] = {}
@@ -102,6 +104,15 @@ class CacheManager:
             else:
                 out.append(None)
         return out
+
+    @property
+    def spare_page(self) -> int:
+        """Index of the page that no request owns (see the constructor)."""
+        return self.num_pages
+
+    @property
+    def has_fixed_state(self) -> bool:
+        return bool(self._state)
 
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()

@@ -56,10 +56,15 @@ class _Layout:
 
 
 class _DecodeGraph:
-    """The captured launch sequence of a decode step for one batch size."""
+    """The captured launch sequence of a decode step for one batch width.  A batch of fewer
+    rows than the width is padded: the extra rows are one-token requests at position 0 whose
+    only page is the cache's spare page, and their logits are dropped."""
 
     def __init__(self, runner: "StepRunner", B: int):
         self.B = B
+        self.used = B            # rows of the last fill that were real
+        self.spare_page = runner.cache.spare_page
+        self.page_size = runner.cache.page_size
         groups = len(runner.cache.groups)
         self.width = runner.graph_table_width
         sizes = [("ids", B), ("pos", B), ("req", B), ("cu", B + 1), ("kv_lens", B), ("state_slots", B),
@@ -88,15 +93,32 @@ class _DecodeGraph:
         self.launches = 0
         self.bound = [[(None, 0)] * B for _ in range(groups)]     # per group and row: (request, pages written)
         self.windowed = [g.need.window is not None for g in runner.cache.groups]
+        self._pad(0)
+
+    def _pad(self, first: int) -> None:
+        """Rows first.. of the host buffer become padding rows."""
+        h, B = self.h, self.B
+        ar = np.arange(B + 1, dtype=np.int32)
+        h["ids"][first:] = 0; h["pos"][first:] = 0; h["req"][first:] = ar[first:B]; h["cu"][:] = ar
+        h["kv_lens"][first:] = 1; h["state_slots"][first:] = 0; h["rows"][:] = ar[:B]
+        for g in range(len(self.bound)):
+            tab = h[f"table{g}"].reshape(B, self.width)
+            tab[first:, 0] = self.spare_page
+            h[f"slots{g}"][first:] = self.spare_page * self.page_size
+            for b in range(first, B):
+                self.bound[g][b] = (None, 0)
 
     def fill(self, lay: _Layout, serials: Sequence[int]) -> None:
         """Write the batch into the pinned buffer and copy it to the device.  A row whose
         request (the same admission: ``serials``) sat there in the last step too only gets the
         pages it has gained since: block tables grow at the end and keep what they held.  (A window that
         gives pages back marks them -1 in place: such rows are written whole.)"""
-        h = self.h
-        h["ids"][:] = lay.ids; h["pos"][:] = lay.pos; h["req"][:] = lay.req; h["cu"][:] = lay.cu
-        h["kv_lens"][:] = lay.kv_lens; h["state_slots"][:] = lay.state_slots; h["rows"][:] = lay.rows
+        h, n_rows = self.h, lay.B
+        if n_rows < self.used:       # rows that held requests in the last step are padding now
+            self._pad(n_rows)
+        self.used = n_rows
+        h["ids"][:n_rows] = lay.ids; h["pos"][:n_rows] = lay.pos; h["req"][:n_rows] = lay.req
+        h["kv_lens"][:n_rows] = lay.kv_lens; h["state_slots"][:n_rows] = lay.state_slots
         for g, lists in enumerate(lay.tables):
             tab = h[f"table{g}"].reshape(self.B, self.width)
             known = self.bound[g]
@@ -109,7 +131,7 @@ class _DecodeGraph:
                 else:
                     tab[b, :n] = pages
                 known[b] = (serials[b], n)
-            h[f"slots{g}"][:] = lay.slots[g]
+            h[f"slots{g}"][:n_rows] = lay.slots[g]
         self.dev.copy_(self.host, non_blocking=True)
 
     def forget_rows(self) -> None:
@@ -131,7 +153,7 @@ class _DecodeGraph:
             self.graph = graph
         self.graph.replay()
         runner.graph_launches += self.launches
-        return self.logits
+        return self.logits[:self.used]
 
 
 class StepRunner:
@@ -277,6 +299,14 @@ class StepRunner:
         self._reserve(entries)
         return self._context(self._layout(entries))
 
+    def graph_width(self, rows: int) -> int:
+        """The captured width that a decode batch of ``rows`` requests replays: itself up to 8
+        rows, the next multiple of 8 beyond (fewer graphs to capture and keep while a batch
+        drains); no padding when a mixer keeps fixed state, whose slots padding rows would share."""
+        if rows <= 8 or self.cache.has_fixed_state:
+            return rows
+        return -(-rows // 8) * 8
+
     # ------------------------------------------------------------------ the step
     def _graphable(self, entries: Sequence[StepEntry], lay: _Layout) -> bool:
         return (self.use_graphs and all(n == 1 for n in lay.q_lens)
@@ -296,13 +326,14 @@ class StepRunner:
         try:
             lay = self._layout(entries)
             if self._graphable(entries, lay):
-                g = self._graphs.get(lay.B)
+                width = self.graph_width(lay.B)
+                g = self._graphs.get(width)
                 if g is None:
-                    g = self._graphs[lay.B] = _DecodeGraph(self, lay.B)
+                    g = self._graphs[width] = _DecodeGraph(self, width)
                 g.fill(lay, [self.cache.serial(e.request_id) for e in entries])
                 self.h2d_bytes += g.host.numel() * 4
                 if ids_device is not None:
-                    g.d["ids"].copy_(ids_device, non_blocking=True)
+                    g.d["ids"][:lay.B].copy_(ids_device, non_blocking=True)
                 logits = g.run(self)
             else:
                 ctx, rows = self._context(lay)

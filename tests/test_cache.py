@@ -58,7 +58,8 @@ def test_groups_by_need_and_shared_cache():
     full, win = PagedKV(2, 8, None), PagedKV(2, 8, 6)
     m = manager([full, win, full, None, FixedState((3,))], cache_from=[None, None, None, 0, None])
     assert [g.entries for g in m.groups] == [[0, 2], [1]]
-    assert m.groups[0].tensor.shape == (2, 2, 8, 2, 4, 8)
+    assert m.groups[0].tensor.shape == (2, 2, 8 + 1, 2, 4, 8)      # 8 pages of the pool and the spare one
+    assert m.spare_page == 8 and m.has_fixed_state
     lc = m.layer_caches()
     assert lc[3].kind == "paged" and not lc[3].writes and lc[3].k.data_ptr() == lc[0].k.data_ptr()
     assert lc[2].k.data_ptr() != lc[0].k.data_ptr() and lc[1].group == 1

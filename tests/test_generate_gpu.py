@@ -197,3 +197,30 @@ def test_zero_matrices_generate_token_zero(tmp_path, dtype):
     write_model_folder(folder, cfg, w)
     out = generate(folder, [[5], [7, 8, 9]], max_tokens=4, dtype=dtype, context=32)
     assert [r["token_ids"] for r in out] == [[0, 0, 0, 0], [0, 0, 0, 0]]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_draining_batch_replays_padded_graphs(folders, dtype):
+    """Twelve requests that end at different times: the decode batch shrinks from 12 to 1, batches of
+    9 to 12 rows replay the graph of width 16 with padding rows on the cache's spare page, and the
+    tokens equal those of an engine that steps without graphs."""
+    from coheryn_ai_studio_b200.engine import Engine
+    prompts = [tiny.prompt(70 + i, 3 + 2 * i, tiny.CONFIGS["B"][0].vocab_size) for i in range(12)]
+    limits = [3 + (5 * i) % 11 for i in range(12)]
+
+    def run(use_graphs):
+        eng = Engine.from_folder(folders["B"], dtype, context=128, max_num_seqs=12, use_graphs=use_graphs)
+        ids = [eng.add_request(p, max_tokens=n) for p, n in zip(prompts, limits)]
+        while eng.has_work():
+            eng.step()
+        eng.cache.check()
+        return [eng.result(i).token_ids for i in ids], eng
+    with_graphs, eng = run(True)
+    without, _ = run(False)
+    assert [len(t) for t in with_graphs] == limits
+    widths = sorted(eng.runner._graphs)
+    assert 16 in widths and not any(8 < w < 16 for w in widths)
+    if dtype == "float32":
+        assert with_graphs == without
+    else:   # bfloat16 kernels are chosen by the batch's width: tokens may part at a near-tie, not before the first
+        assert [t[0] for t in with_graphs] == [t[0] for t in without]
