@@ -5,11 +5,13 @@ the tokens given are run, as one batch, against what earlier steps left in the c
 logits come back only for the places asked for.  The reference's batched forward takes
 exactly one token per lane (crates/coheryn-engine/src/inference/batch.rs:64-116) and
 returns logits for every lane; here a lane carries any number of tokens and logits are
-computed for the wanted rows alone (the non-output shortcut of
-crates/coheryn-engine/src/inference.rs:481-485 taken further).
+computed for the wanted rows alone.  When at most half of the rows are wanted, the last
+entry of the schedule also runs its attention and feed-forward for the wanted rows only,
+after it has written the keys and values of all of them (the non-output shortcut of
+crates/coheryn-engine/src/inference.rs:481-485).
 
 Steps in which every request brings exactly one token and wants its logits (decoding) can
-be replayed from a CUDA graph: the launch sequence is captured once per batch size over
+be replayed from a CUDA graph: the launch sequence is captured once per batch width over
 static index buffers, and a step then costs one host-to-device copy and one graph launch.
 """
 from __future__ import annotations
