@@ -228,3 +228,45 @@ def test_few_wanted_rows_take_the_last_layers_shortcut(name, dtype, folders, mod
     for key, row in runs[True].items():
         tol = 1e-4 if dtype == "float32" else 0.04 * max(1.0, float(np.abs(row).max()))
         assert np.abs(row - runs[False][key]).max() <= tol, key
+
+
+ODD = {
+    "mha": dict(vocab_size=517, hidden_size=80, intermediate_size=136, num_hidden_layers=1, num_attention_heads=5,
+                num_key_value_heads=5, head_dim=16, tie_word_embeddings=True),
+    "group16": dict(vocab_size=640, hidden_size=256, intermediate_size=520, num_hidden_layers=2, num_attention_heads=16,
+                    num_key_value_heads=1, head_dim=16, tie_word_embeddings=False),
+    "group32": dict(vocab_size=333, hidden_size=512, intermediate_size=264, num_hidden_layers=1, num_attention_heads=32,
+                    num_key_value_heads=1, head_dim=16, tie_word_embeddings=True),
+    "width100": dict(vocab_size=211, hidden_size=100, intermediate_size=150, num_hidden_layers=1, num_attention_heads=5,
+                     num_key_value_heads=1, head_dim=32, tie_word_embeddings=True),
+    "head128": dict(vocab_size=300, hidden_size=256, intermediate_size=344, num_hidden_layers=2, num_attention_heads=2,
+                    num_key_value_heads=1, head_dim=128, tie_word_embeddings=True),
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(ODD))
+def test_other_shapes_of_the_architecture(name, dtype, tmp_path):
+    """Further shapes of the same architecture: no grouping, groups of 16 and 32 heads (more rows per
+    kv head than the decode kernel takes), a width that is no multiple of 8 (no tensor-core product
+    takes it), a head size unequal to width / heads, odd vocabularies; portions, mixed steps and
+    decoding of three requests against the plain implementation."""
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.engine import write_random_model
+    cfg = Qwen2Config(max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=1e5, **ODD[name])
+    folder = str(tmp_path / name)
+    write_random_model(folder, cfg, 3, tiny.POLICY_LOUD)
+    V = cfg.vocab_size
+    a, b, c = tiny.prompt(1, 90, V), tiny.prompt(2, 50, V), tiny.prompt(3, 30, V)
+    r = Replay(folder, dtype, max_tokens=192)
+    r.step([("a", a[:60], list(range(60)))])
+    r.step([("a", a[60:63], [0, 1, 2]), ("b", b[:33], list(range(33)))])
+    r.step([("a", a[63:70], list(range(7))), ("b", b[33:35], [0, 1]), ("c", c[:17], [16])])
+    for t in range(70, 90):
+        entries = [("a", [a[t]], [0])]
+        if 35 + t - 70 < 50:
+            entries.append(("b", [b[35 + t - 70]], [0]))
+        if t == 72:
+            entries.append(("c", c[17:], list(range(13))))
+        r.step(entries)
+    compare(r, folder, {"a": a, "b": b, "c": c}, name)
