@@ -6,15 +6,52 @@ page that was filled completely and carries a content hash stays findable after 
 last holder lets go of it: it waits in a least-recently-used list and is only wiped
 when the pool has no plain free page left.  Freed pages are handed out again last-in
 first-out, so reuse happens at once (and stale contents would show in tests).
+
+The books themselves are kept by the native host runtime (``csrc/host_pages.cpp``, plain
+C++ behind a C interface); the classes here own a handle and turn its status codes into
+exceptions.
 """
 from __future__ import annotations
 
-from collections import OrderedDict
+import ctypes
 from typing import Dict, List, Optional
+
+from ..csrc import build
 
 
 class CacheError(RuntimeError):
     """A bookkeeping invariant was broken (double free, unknown page or slot)."""
+
+
+_lib = None
+
+
+def _host():
+    global _lib
+    if _lib is None:
+        lib = build.host_library()
+        lib.coheryn_pool_new.restype = ctypes.c_void_p
+        lib.coheryn_pool_new.argtypes = [ctypes.c_int]
+        lib.coheryn_slots_new.restype = ctypes.c_void_p
+        lib.coheryn_slots_new.argtypes = [ctypes.c_int]
+        for name in ("coheryn_pool_delete", "coheryn_slots_delete", "coheryn_pool_drop_hashes"):
+            getattr(lib, name).restype = None
+            getattr(lib, name).argtypes = [ctypes.c_void_p]
+        for name in ("coheryn_pool_available", "coheryn_slots_available", "coheryn_slots_acquire"):
+            getattr(lib, name).argtypes = [ctypes.c_void_p]
+        for name in ("coheryn_pool_refcount", "coheryn_pool_retain", "coheryn_pool_release",
+                     "coheryn_slots_release", "coheryn_slots_held"):
+            getattr(lib, name).argtypes = [ctypes.c_void_p, ctypes.c_int]
+        lib.coheryn_pool_allocate.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        lib.coheryn_pool_set_hash.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_int]
+        lib.coheryn_pool_lookup.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+        lib.coheryn_pool_check.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int),
+                                           ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+        _lib = lib
+    return _lib
+
+
+UNKNOWN_PAGE, NOT_HELD, FREE_PAGE, NOT_ENOUGH, BAD_ARGUMENT = 1, 2, 3, 4, 5
 
 
 class PagePool:
@@ -22,141 +59,136 @@ class PagePool:
         if num_pages < 0:
             raise ValueError("a pool cannot have a negative number of pages")
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))   # stack; page 0 first out
-        self._refs: List[int] = [0] * num_pages
-        self._hash_of: Dict[int, bytes] = {}            # page -> content hash
-        self._page_of: Dict[bytes, int] = {}            # content hash -> page
-        self._idle: "OrderedDict[int, None]" = OrderedDict()   # hashed pages with no holder, LRU first
+        self._lib = _host()
+        self._h = self._lib.coheryn_pool_new(num_pages)
+        if not self._h:
+            raise CacheError("the native page pool could not be made")
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.coheryn_pool_delete(h)
+
+    def _fail(self, code: int, page: int, doing: str):
+        if code == UNKNOWN_PAGE:
+            raise CacheError(f"page {page} is not in the pool (0..{self.num_pages - 1})")
+        if code == NOT_HELD:
+            raise CacheError(f"page {page} is {doing} but nobody holds it")
+        if code == FREE_PAGE:
+            raise CacheError(f"page {page} is free and cannot be retained")
+        raise CacheError(f"page pool: status {code} while page {page} is {doing}")
 
     # ---- queries
     @property
     def available(self) -> int:
         """Pages that an allocation can get right now (free + idle hashed pages)."""
-        return len(self._free) + len(self._idle)
+        return self._lib.coheryn_pool_available(self._h)
 
     def refcount(self, page: int) -> int:
-        return self._refs[page]
+        r = self._lib.coheryn_pool_refcount(self._h, page)
+        if r < 0:
+            self._fail(UNKNOWN_PAGE, page, "asked for")
+        return r
 
     # ---- allocation
     def allocate(self, n: int) -> Optional[List[int]]:
         """n pages with reference count 1, or None (and no change) if fewer are available."""
         if n < 0:
             raise ValueError("cannot allocate a negative number of pages")
-        if n > self.available:
+        out = (ctypes.c_int * max(n, 1))()
+        code = self._lib.coheryn_pool_allocate(self._h, n, out)
+        if code == NOT_ENOUGH:
             return None
-        out = []
-        for _ in range(n):
-            if self._free:
-                p = self._free.pop()
-            else:
-                p, _ = self._idle.popitem(last=False)    # evict the least recently used
-                self._forget(p)
-            self._refs[p] = 1
-            out.append(p)
-        return out
+        if code:
+            raise CacheError(f"page pool: status {code} while {n} pages are allocated")
+        return list(out[:n])
 
     def retain(self, page: int) -> None:
         """One more holder of a page (a shared prefix); revives an idle hashed page."""
-        self._known(page)
-        if self._refs[page] == 0:
-            if page not in self._idle:
-                raise CacheError(f"page {page} is free and cannot be retained")
-            del self._idle[page]
-        self._refs[page] += 1
+        code = self._lib.coheryn_pool_retain(self._h, page)
+        if code:
+            self._fail(code, page, "retained")
 
     def release(self, page: int) -> None:
-        self._known(page)
-        if self._refs[page] <= 0:
-            raise CacheError(f"page {page} is released but nobody holds it")
-        self._refs[page] -= 1
-        if self._refs[page] == 0:
-            if page in self._hash_of:
-                self._idle[page] = None
-            else:
-                self._free.append(page)
+        code = self._lib.coheryn_pool_release(self._h, page)
+        if code:
+            self._fail(code, page, "released")
 
     # ---- content hashes (prefix reuse)
     def set_hash(self, page: int, digest: bytes) -> None:
         """Record that ``page`` holds the full block identified by ``digest``.  If
         another page already carries that digest the record stays with the older one."""
-        self._known(page)
-        if self._refs[page] <= 0:
+        code = self._lib.coheryn_pool_set_hash(self._h, page, digest, len(digest))
+        if code == NOT_HELD:
             raise CacheError(f"page {page} is not held")
-        if digest in self._page_of or page in self._hash_of:
-            return
-        self._hash_of[page] = digest
-        self._page_of[digest] = page
+        if code:
+            self._fail(code, page, "given a hash")
 
     def lookup(self, digest: bytes) -> Optional[int]:
-        return self._page_of.get(digest)
-
-    def _forget(self, page: int) -> None:
-        d = self._hash_of.pop(page, None)
-        if d is not None:
-            self._page_of.pop(d, None)
+        page = self._lib.coheryn_pool_lookup(self._h, digest, len(digest))
+        return None if page < 0 else page
 
     def drop_hashes(self) -> None:
         """Forget every content hash (idle pages become plain free pages)."""
-        for p in list(self._idle):
-            self._free.append(p)
-        self._idle.clear()
-        self._hash_of.clear()
-        self._page_of.clear()
-
-    def _known(self, page: int) -> None:
-        if not 0 <= page < self.num_pages:
-            raise CacheError(f"page {page} is not in the pool (0..{self.num_pages - 1})")
+        self._lib.coheryn_pool_drop_hashes(self._h)
 
     # ---- invariants
     def check(self, held: Optional[Dict[int, int]] = None) -> None:
         """Every page is in exactly one place; with ``held`` (page -> number of holders as
         the caller counts them) the reference counts must agree."""
-        seen = [0] * self.num_pages
-        for p in self._free:
-            seen[p] += 1
-        for p in self._idle:
-            seen[p] += 1
-        for p in range(self.num_pages):
-            if self._refs[p] < 0:
-                raise CacheError(f"page {p} has a negative reference count")
-            if self._refs[p] > 0:
-                seen[p] += 1
-            if seen[p] != 1:
-                raise CacheError(f"page {p} is in {seen[p]} places (free / idle / held)")
-            if p in self._idle and p not in self._hash_of:
-                raise CacheError(f"idle page {p} has no hash")
+        counts = None
         if held is not None:
-            for p in range(self.num_pages):
-                if self._refs[p] != held.get(p, 0):
-                    raise CacheError(f"page {p}: pool counts {self._refs[p]} holders, "
-                                     f"requests hold it {held.get(p, 0)} times")
+            counts = (ctypes.c_int * max(self.num_pages, 1))()
+            for page, n in held.items():
+                if not 0 <= page < self.num_pages:
+                    raise CacheError(f"page {page} is not in the pool (0..{self.num_pages - 1})")
+                counts[page] = n
+        bad, info = ctypes.c_int(-1), ctypes.c_int(0)
+        code = self._lib.coheryn_pool_check(self._h, counts, ctypes.byref(bad), ctypes.byref(info))
+        p = bad.value
+        if code == 1:
+            raise CacheError(f"page {p} has a negative reference count")
+        if code == 2:
+            raise CacheError(f"page {p} is in {info.value} places (free / idle / held)")
+        if code == 3:
+            raise CacheError(f"idle page {p} has no hash")
+        if code == 4:
+            raise CacheError(f"page {p}: pool counts {info.value} holders, "
+                             f"requests hold it {held.get(p, 0)} times")
+        if code:
+            raise CacheError(f"page pool: check returned {code}")
 
 
 class SlotPool:
     """Slots for per-request state of fixed size."""
 
     def __init__(self, num_slots: int):
+        if num_slots < 0:
+            raise ValueError("a pool cannot have a negative number of slots")
         self.num_slots = num_slots
-        self._free = list(range(num_slots - 1, -1, -1))
-        self._used = set()
+        self._lib = _host()
+        self._h = self._lib.coheryn_slots_new(num_slots)
+        if not self._h:
+            raise CacheError("the native slot pool could not be made")
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.coheryn_slots_delete(h)
 
     @property
     def available(self) -> int:
-        return len(self._free)
+        return self._lib.coheryn_slots_available(self._h)
 
     def allocate(self) -> Optional[int]:
-        if not self._free:
-            return None
-        s = self._free.pop()
-        self._used.add(s)
-        return s
+        s = self._lib.coheryn_slots_acquire(self._h)
+        return None if s < 0 else s
 
     def release(self, slot: int) -> None:
-        if slot not in self._used:
+        if self._lib.coheryn_slots_release(self._h, slot):
             raise CacheError(f"slot {slot} is released but not in use")
-        self._used.remove(slot)
-        self._free.append(slot)
 
     def check(self) -> None:
-        if len(self._free) + len(self._used) != self.num_slots or self._used & set(self._free):
+        held = sum(1 for s in range(self.num_slots) if self._lib.coheryn_slots_held(self._h, s) == 1)
+        if held + self.available != self.num_slots:
             raise CacheError("slot pool lost or duplicated a slot")

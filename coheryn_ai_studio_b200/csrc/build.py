@@ -1,5 +1,5 @@
-"""Compiles the CUDA sources of this folder for sm_100a with nvcc and loads the result
-with ctypes.
+"""Compiles the CUDA sources of this folder for sm_100a with nvcc (and the host runtime with
+the C++ compiler) and loads the result with ctypes.
 
 A library is named by a hash of its sources, headers, compile-time definitions and
 flags, so a stale build is never loaded.  Libraries live in ``<package>/_lib`` when that
@@ -160,6 +160,53 @@ def load_library(label: str, sources: Sequence[str], defines: Optional[Dict[str,
         return lib
 
 
+def host_compiler() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++); the host runtime "
+                     "of this engine cannot be built")
+
+
+HOST_SOURCES = ["host_pages.cpp"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def build_host_library() -> str:
+    """The host runtime (page and slot bookkeeping): plain C++, no CUDA, compiled in a second."""
+    h = hashlib.sha256()
+    for f in HOST_SOURCES:
+        with open(os.path.join(HERE, f), "rb") as fh:
+            h.update(f.encode())
+            h.update(fh.read())
+    h.update(repr(HOST_FLAGS).encode())
+    name = f"libcoheryn_b200_host_{h.hexdigest()[:16]}.so"
+    found = _existing_lib(name)
+    if found:
+        return found
+    out_dir = _lib_dir()
+    target = os.path.join(out_dir, name)
+    tmp_target = os.path.join(out_dir, f".{os.getpid()}_{name}")
+    cmd = [host_compiler()] + HOST_FLAGS + [os.path.join(HERE, f) for f in HOST_SOURCES] + ["-o", tmp_target]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise BuildError("the host runtime did not compile:\n" + r.stdout)
+    os.replace(tmp_target, target)
+    print(f"[coheryn-b200] built {target}", file=sys.stderr, flush=True)
+    return target
+
+
+def host_library() -> ctypes.CDLL:
+    with _lock:
+        lib = _loaded.get("host")
+        if lib is None:
+            path = build_host_library()
+            lib = ctypes.CDLL(path)
+            lib.coheryn_library_path = path  # type: ignore[attr-defined]
+            _loaded["host"] = lib
+        return lib
+
+
 def core_library() -> ctypes.CDLL:
     return load_library("core", CORE_SOURCES)
 
@@ -175,7 +222,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
 
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     """Compile everything ahead of time (no GPU needed)."""
-    paths = [build_library("core", CORE_SOURCES)]
+    paths = [build_host_library(), build_library("core", CORE_SOURCES)]
     for hd in head_dims:
         paths.append(build_library(f"attn_hd{hd}", ["attention_bf16.cu", "attention_tc.cu", "runtime.cu"],
                                    {"CO_HEAD_DIM": hd}))

@@ -1,5 +1,7 @@
 """The cache manager on the host: no page lost, held twice or freed twice, under random
 orders of requests; windows give pages back; prefixes are found again."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -159,3 +161,21 @@ def test_random_orders_keep_the_books(seed):
         m.free(rid)
     m.check()
     assert m.available_pages() == [12] * len(m.groups) and m.slots.available == 5
+
+
+def test_the_pools_are_the_native_ones():
+    """The books are kept by the C++ host library, not by Python containers."""
+    pool = PagePool(4)
+    assert pool._lib.coheryn_library_path.endswith(".so") and "host" in os.path.basename(pool._lib.coheryn_library_path)
+    a = pool.allocate(3)
+    pool.set_hash(a[0], b"x" * 32); pool.set_hash(a[1], b"y" * 32)
+    pool.release(a[0]); pool.release(a[1])                 # idle, a[0] least recently used
+    assert pool.available == 3 and pool.lookup(b"x" * 32) == a[0]
+    got = pool.allocate(2)                                  # the free page first, then the LRU idle one
+    assert got[1] == a[0] and pool.lookup(b"x" * 32) is None and pool.lookup(b"y" * 32) == a[1]
+    pool.retain(a[1])                                       # revived by its hash
+    pool.check({a[1]: 1, a[2]: 1, got[0]: 1, got[1]: 1})
+    with pytest.raises(CacheError):
+        pool.release(99)
+    with pytest.raises(CacheError):
+        pool.check({a[1]: 2, a[2]: 1, got[0]: 1, got[1]: 1})
