@@ -114,6 +114,11 @@ class CacheManager:
     def has_fixed_state(self) -> bool:
         return bool(self._state)
 
+    def state_tensors(self) -> List[torch.Tensor]:
+        """The fixed-state pools ([slots, *shape] each), for a caller that must put them back as
+        they were (the warm-up runs before a CUDA-graph capture)."""
+        return list(self._state.values())
+
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
         return sum(2 * len(g.entries) * g.need.num_kv_heads * g.need.head_dim * item for g in self.groups)

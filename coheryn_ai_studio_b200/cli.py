@@ -5,7 +5,7 @@
                 [--stream] [--temperature 0] [--top-k 0] [--top-p 1] [--seed 0]
                 [--stop-token ID]... [--repetition-penalty 1] [--frequency-penalty 0]
                 [--presence-penalty 0] [--dtype bfloat16|float32] [--json]
-    coheryn trace MODEL --tokens 1,2,3          teacher-forced logits as JSON Lines
+    coheryn trace MODEL --tokens 1,2,3          teacher-forced layer outputs and logits as JSON Lines
     coheryn init DIR|FILE.gguf --config CONFIG.json --seed N [--store bfloat16|float32]
     coheryn models inspect MODEL
 
@@ -82,6 +82,7 @@ def build_parser() -> argparse.ArgumentParser:
     tr.add_argument("--context", type=int, default=4096)
     tr.add_argument("--dtype", default="float32", choices=["bfloat16", "float32"])
     tr.add_argument("--device", default="cuda:0")
+    tr.add_argument("--logits-only", action="store_true", help="leave the layer outputs out")
 
     init = sub.add_parser("init", help="write a model folder (or one .gguf file) with seeded random weights")
     init.add_argument("dir")
@@ -152,17 +153,27 @@ def cmd_run(args) -> int:
 
 
 def cmd_trace(args) -> int:
-    """One JSON line per position: {"position", "name": "logits", "values"} (main.rs:487-506)."""
+    """Teacher-forced, token by token; per position one JSON line for every layer's output
+    ({"position", "name": "blk.<i>.output", "values"}, i counting the executions of the schedule) and one
+    for the logits ({"position", "name": "logits", "values"}), as crates/coheryn-engine/src/inference.rs:
+    541-556 hands them to its observer and crates/coheryn-cli/src/main.rs:487-506 prints them."""
     from .engine import Engine
     ids, _ = _prompt_ids(args, args.model)
     if not ids:
         raise CliError("invalid_request", "trace needs at least one token", 2)
     engine = Engine.from_folder(args.model, args.dtype, args.device, context=args.context, max_num_seqs=1,
-                                kv_cache_tokens=args.context, prefix_reuse=False)
+                                kv_cache_tokens=args.context, prefix_reuse=False, use_graphs=False)
     from .engine import StepEntry
     engine.cache.admit("trace")
+    outputs = []
+    if not args.logits_only:
+        engine.model.layer_observer = lambda entry, x: outputs.append((entry, x))
     for position, token in enumerate(ids):
+        outputs.clear()
         logits = engine.runner.step([StepEntry("trace", [token], [0])])
+        engine.runner.check_status()
+        for entry, x in outputs:
+            print(json.dumps({"position": position, "name": f"blk.{entry}.output", "values": x[0].cpu().tolist()}))
         print(json.dumps({"position": position, "name": "logits", "values": logits[0].cpu().tolist()}))
     return 0
 
@@ -182,21 +193,22 @@ def cmd_init(args) -> int:
 
 
 def cmd_inspect(args) -> int:
+    """What the adapter says of the model (capabilities, configuration, cache cost) and the
+    tensor inventory of the files, checked against what the model needs; no payload is read."""
     import torch
-    from .config import load_config
+    from .config import describe_model, load_config
     from .parts import DecoderModel, Runtime
     from .engine.loading import gguf_rename
     from .weights import check_against, index_model
-    config, spec = load_config(args.model)
+    _, spec = load_config(args.model)
     entries = index_model(args.model, gguf_rename(args.model))
     model = DecoderModel(spec, Runtime(torch.bfloat16, torch.device("cpu")))
     check_against(model.tensor_specs(), entries)
-    kv = sum(2 * r.num_kv_heads * r.head_dim for r in model.cache_requirements() if hasattr(r, "num_kv_heads"))
-    print(json.dumps({
-        "architecture": spec.architecture, "config": config.to_dict() if hasattr(config, "to_dict") else None,
+    report = describe_model(args.model)
+    report["files"] = {
         "tensors": len(entries), "tensor_bytes": sum(e.end - e.begin for e in entries.values()),
-        "dtypes": sorted({str(e.dtype).replace("torch.", "") for e in entries.values()}),
-        "kv_elements_per_token": kv, "context": spec.max_positions}, indent=1))
+        "dtypes": sorted({str(e.dtype).replace("torch.", "") for e in entries.values()})}
+    print(json.dumps(report, indent=1))
     return 0
 
 

@@ -18,7 +18,7 @@ import os
 from dataclasses import asdict, dataclass
 from typing import Any, Dict, List
 
-from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, prenorm_layer
 
 MAX_CONFIG_BYTES = 1 << 20
 MAX_CONFIG_DEPTH = 32
@@ -288,9 +288,8 @@ def qwen2_model_spec(c: Qwen2Config) -> ModelSpec:
         "max_positions": c.max_position_embeddings})
     layers: List[LayerSpec] = []
     for i in range(c.num_hidden_layers):
-        layers.append(LayerSpec(
+        layers.append(prenorm_layer(
             prefix=f"model.layers.{i}",
-            arrangement="prenorm_residual",
             mixer=PartSpec("attention", {
                 "hidden_size": c.hidden_size, "num_heads": c.num_attention_heads,
                 "num_kv_heads": c.num_key_value_heads, "head_dim": c.head_dim,

@@ -9,7 +9,7 @@ below the registry (parts, cache manager, step function, scheduler) sees only th
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Mapping, Optional
 
 
 @dataclass(frozen=True)
@@ -24,17 +24,26 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A layer = an arrangement (how the parts are wired, e.g. pre-norm residual)
-    over a mixer, a feed-forward and the norms.  ``prefix`` is the tensor-name prefix
-    of the layer's weights (``model.layers.3``)."""
+    """A layer = an arrangement (how the parts are wired, e.g. pre-norm residual) over the parts
+    that fill its slots.  ``parts`` maps a slot name of the arrangement (for the pre-norm block:
+    ``mixer``, ``feed_forward``, ``mixer_norm``, ``feed_forward_norm``) to the part that fills it;
+    which slots exist, which may stay empty and what role each has is the arrangement's business,
+    so a block without a feed-forward, with four norms or with two mixers is another arrangement
+    and nothing else.  ``position`` is handed to the layer's mixers.  ``prefix`` is the
+    tensor-name prefix of the layer's weights (``model.layers.3``)."""
 
     prefix: str
     arrangement: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Mapping[str, PartSpec]
     position: Optional[PartSpec] = None
+
+
+def prenorm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                  feed_forward_norm: PartSpec, position: Optional[PartSpec] = None) -> LayerSpec:
+    """The usual block: x += mixer(norm(x)); x += feed_forward(norm(x))."""
+    return LayerSpec(prefix, "prenorm_residual",
+                     {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": mixer_norm,
+                      "feed_forward_norm": feed_forward_norm}, position)
 
 
 @dataclass(frozen=True)
@@ -60,6 +69,12 @@ class ModelSpec:
     final_norm: PartSpec
     final_norm_name: str
     head_name: Optional[str]  # None: logits use the embedding table (tied)
+    # Options that some architectures have and this one leaves at "none": the embedding rows are
+    # multiplied by ``embedding_scale``; the logits are multiplied by ``logit_scale`` and a bias
+    # ``head_bias_name`` (full tensor name, [vocab]) is added to them.
+    embedding_scale: Optional[float] = None
+    logit_scale: Optional[float] = None
+    head_bias_name: Optional[str] = None
 
     def validate(self) -> None:
         if not self.layers:

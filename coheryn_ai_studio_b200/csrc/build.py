@@ -29,7 +29,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompil
 
 # The core library: everything that is not specialised by a compile-time size.
 CORE_SOURCES = ["runtime.cu", "elementwise.cu", "gemm_simt.cu", "attention_simple.cu",
-                "sampling.cu", "gemm_bf16_small.cu", "gemm_tc.cu", "gemm_tc_few.cu"]
+                "sampling.cu", "gemm_bf16_small.cu", "gemm_tc.cu", "gemm_tc_few.cu", "seeded_fill.cu", "selftest.cu"]
 HEADERS = ["common.cuh"]
 
 
@@ -91,6 +91,16 @@ def _progress(label: str, stop: threading.Event) -> None:
               file=sys.stderr, flush=True)
 
 
+def _drop_stale(out_dir: str, prefix: str, keep: str) -> None:
+    """Earlier builds of the same library (other source hashes) are of no use to anyone."""
+    try:
+        for f in os.listdir(out_dir):
+            if f.startswith(prefix) and f.endswith(".so") and f != keep:
+                os.unlink(os.path.join(out_dir, f))
+    except OSError:
+        pass
+
+
 def build_library(label: str, sources: Sequence[str], defines: Optional[Dict[str, object]] = None,
                   extra_flags: Iterable[str] = (), verbose: bool = False) -> str:
     """Compile ``sources`` into one shared library and return its path (cached)."""
@@ -136,6 +146,7 @@ def build_library(label: str, sources: Sequence[str], defines: Optional[Dict[str
         if r.returncode != 0:
             raise BuildError("linking failed:\n" + r.stdout)
         os.replace(tmp_target, target)
+        _drop_stale(out_dir, f"libcoheryn_b200_{label}_", name)
     finally:
         stop.set()
         shutil.rmtree(work, ignore_errors=True)
@@ -168,14 +179,15 @@ def host_compiler() -> str:
                      "of this engine cannot be built")
 
 
-HOST_SOURCES = ["host_pages.cpp"]
-HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+HOST_SOURCES = ["host_pages.cpp", "host_seeded.cpp"]
+# -ffp-contract=off: the seeded weights must round after every operation, as the CUDA kernel does.
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-ffp-contract=off", "-pthread"]
 
 
 def build_host_library() -> str:
     """The host runtime (page and slot bookkeeping): plain C++, no CUDA, compiled in a second."""
     h = hashlib.sha256()
-    for f in HOST_SOURCES:
+    for f in HOST_SOURCES + ["seeded_values.h"]:
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(f.encode())
             h.update(fh.read())
@@ -192,6 +204,7 @@ def build_host_library() -> str:
     if r.returncode != 0:
         raise BuildError("the host runtime did not compile:\n" + r.stdout)
     os.replace(tmp_target, target)
+    _drop_stale(out_dir, "libcoheryn_b200_host_", name)
     print(f"[coheryn-b200] built {target}", file=sys.stderr, flush=True)
     return target
 

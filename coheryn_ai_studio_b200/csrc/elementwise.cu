@@ -9,7 +9,7 @@
 // ---------------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int H, int V, int* __restrict__ status) {
+                                    float* __restrict__ out, int H, int V, int* __restrict__ status, float scale) {
   co_pdl_launch_dependents();
   co_pdl_wait();
   const int t = blockIdx.x;
@@ -20,20 +20,89 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
     return;
   }
   const TW* row = table + (size_t)id * H;
-  for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)t * H + j] = co_to_float(row[j]);
+  if (scale == 1.0f) {
+    for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)t * H + j] = co_to_float(row[j]);
+  } else {   // an architecture that multiplies its embedding rows by a constant
+    for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)t * H + j] = co_to_float(row[j]) * scale;
+  }
 }
 
 CO_EXPORT int coheryn_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
-                                   int T, int H, int V, int* status, cudaStream_t stream) {
+                                   int T, int H, int V, int* status, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == CO_F32)
-    co_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, status);
+    co_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, status, scale);
   else if (table_dtype == CO_BF16)
-    co_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, status);
+    co_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, status, scale);
   else
     CO_FAIL("embed_gather: unknown table dtype %d", table_dtype);
   CO_CHECK_LAUNCH("embed_gather");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Row gather: out[r, :] = src[rows[r], :] for rows of `row_bytes` bytes (any element type).
+// ---------------------------------------------------------------------------------
+template <typename Unit>
+__global__ void gather_rows_kernel(const char* __restrict__ src, long src_stride, const int* __restrict__ rows,
+                                   char* __restrict__ out, int units) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const Unit* from = (const Unit*)(src + (size_t)rows[blockIdx.x] * src_stride);
+  Unit* to = (Unit*)(out + (size_t)blockIdx.x * units * sizeof(Unit));
+  for (int j = threadIdx.x; j < units; j += blockDim.x) to[j] = from[j];
+}
+
+CO_EXPORT int coheryn_gather_rows(const void* src, long src_stride_bytes, const int* rows, void* out, int R,
+                                  int row_bytes, cudaStream_t stream) {
+  if (R <= 0 || row_bytes <= 0) return 0;
+  const bool wide = row_bytes % 16 == 0 && src_stride_bytes % 16 == 0 && ((uintptr_t)src % 16) == 0 && ((uintptr_t)out % 16) == 0;
+  const bool words = row_bytes % 4 == 0 && src_stride_bytes % 4 == 0 && ((uintptr_t)src % 4) == 0 && ((uintptr_t)out % 4) == 0;
+  if (wide)
+    co_launch(gather_rows_kernel<uint4>, dim3(R), dim3(128), 0, stream, (const char*)src, src_stride_bytes, rows, (char*)out, row_bytes / 16);
+  else if (words)
+    co_launch(gather_rows_kernel<uint32_t>, dim3(R), dim3(128), 0, stream, (const char*)src, src_stride_bytes, rows, (char*)out, row_bytes / 4);
+  else
+    co_launch(gather_rows_kernel<unsigned char>, dim3(R), dim3(128), 0, stream, (const char*)src, src_stride_bytes, rows, (char*)out, row_bytes);
+  CO_CHECK_LAUNCH("gather_rows");
+  return 0;
+}
+
+// out[rows[r]] = src[r] for 32-bit elements (the inverse of a gather of single words).
+__global__ void scatter_words_kernel(const uint32_t* __restrict__ src, const int* __restrict__ rows, uint32_t* __restrict__ out, int R) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < R) out[rows[r]] = src[r];
+}
+
+CO_EXPORT int coheryn_scatter_words(const void* src, const int* rows, void* out, int R, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  co_launch(scatter_words_kernel, dim3((R + 127) / 128), dim3(128), 0, stream, (const uint32_t*)src, rows, (uint32_t*)out, R);
+  CO_CHECK_LAUNCH("scatter_words");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Logits of an architecture that scales them or adds a bias: x[r, v] = x[r, v] * scale + bias[v].
+// ---------------------------------------------------------------------------------
+__global__ void scale_add_bias_kernel(float* __restrict__ x, long stride, int V, float scale, const void* __restrict__ bias,
+                                      int bias_dtype) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  float* row = x + (size_t)blockIdx.y * stride;
+  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < V; v += gridDim.x * blockDim.x)
+    row[v] = row[v] * scale + (bias ? co_load_any(bias, bias_dtype, v) : 0.f);
+}
+
+CO_EXPORT int coheryn_scale_add_bias(float* x, long stride, int R, int V, float scale, const void* bias, int bias_dtype,
+                                     cudaStream_t stream) {
+  if (R <= 0 || V <= 0) return 0;
+  if (R > 65535) CO_FAIL("scale_add_bias: at most 65535 rows, not %d", R);
+  const int blocks = (V + 1023) / 1024 < 64 ? (V + 1023) / 1024 : 64;
+  co_launch(scale_add_bias_kernel, dim3(blocks, R), dim3(256), 0, stream, x, stride, V, scale, bias, bias_dtype);
+  CO_CHECK_LAUNCH("scale_add_bias");
   return 0;
 }
 

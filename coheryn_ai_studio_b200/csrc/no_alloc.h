@@ -15,7 +15,8 @@
 // results, but keeps its piece buffers in a fixed array inside the library's device image.
 //
 // Limit: rows * ceil(vocab / 4096) <= COHERYN_ARGMAX_STATIC_SLOTS (65,536 slots of 8 bytes =
-// 512 KiB, e.g. 256 rows of a 1,048,576-entry vocabulary, or 1,724 rows of 151,936).  Larger
+// 512 KiB, e.g. 256 rows of a 1,048,576-entry vocabulary, or 1,724 rows of 151,936), and at most
+// 65,535 rows per call whatever the vocabulary (each row is one row of the launch grid).  Larger
 // requests are refused with an error; nothing is launched.  Every GPU that loads the library
 // holds the 512 KiB until the process exits.
 //

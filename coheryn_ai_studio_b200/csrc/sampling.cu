@@ -365,6 +365,9 @@ CO_EXPORT int coheryn_apply_penalties(float* logits, long stride, int n, const i
   return 0;
 }
 
+// The two-stage path puts the rows on the grid's y dimension, which ends at 65,535.
+constexpr int ARGMAX_MAX_ROWS = 65535;
+
 // Number of 8-byte scratch slots coheryn_argmax wants for R rows of V logits (0: none).
 CO_EXPORT long coheryn_argmax_scratch_slots(int R, int V) {
   const int pieces = (V + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
@@ -377,7 +380,7 @@ CO_EXPORT int coheryn_argmax(const float* logits, long stride, int R, int V, int
   if (R <= 0) return 0;
   if (V <= 0) CO_FAIL("argmax: empty vocabulary");
   const int pieces = (V + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
-  if (pieces >= 4 && scratch && scratch_slots >= (long)R * pieces) {
+  if (pieces >= 4 && R <= ARGMAX_MAX_ROWS && scratch && scratch_slots >= (long)R * pieces) {
     float* pv = (float*)scratch;
     int* pi = (int*)scratch + (size_t)R * pieces;
     co_launch(argmax_pieces_kernel, dim3(pieces, R), dim3(256), 0, stream, logits, stride, V, pv, pi, pieces, status);
@@ -421,6 +424,8 @@ CO_EXPORT int coheryn_argmax_static(const float* logits, long stride, int rows, 
                                     cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) CO_FAIL("argmax_static: empty vocabulary");
+  if (rows > ARGMAX_MAX_ROWS)
+    CO_FAIL("argmax_static: at most %d rows per call (one grid row each), not %d", ARGMAX_MAX_ROWS, rows);
   const long pieces = ((long)vocab + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
   if ((long)rows * pieces > COHERYN_ARGMAX_STATIC_SLOTS)
     CO_FAIL("argmax_static: %d rows of %d logits need %ld piece slots; the static scratch holds %d "

@@ -20,10 +20,10 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned coun
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+// Bounded wait for the phase with the given parity; false if `limit` tries ran out.
+__device__ __forceinline__ bool mbar_wait_limited(unsigned long long* bar, unsigned parity, unsigned limit) {
   const unsigned addr = smem_u32(bar);
-  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+  for (unsigned i = 0; i < limit; ++i) {
     unsigned done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -33,6 +33,9 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     if (done) return true;
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  return mbar_wait_limited(bar, parity, WAIT_LIMIT);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {

@@ -141,7 +141,7 @@ class Engine:
         logits = self.runner.step(entries, ids_device=ids_device)
         self.scheduler.advance(plan)
         sampling = [s.request for s in plan if s.samples]
-        pending = self.sampler.launch(logits, [r.sampler for r in sampling], extra_status=[self.model.status])
+        pending = self.sampler.launch(logits, [r.sampler for r in sampling], extra_status=self.runner.status_words())
         return _InFlight(plan, sampling, pending)
 
     def step(self) -> List[tuple]:

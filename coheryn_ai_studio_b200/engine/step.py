@@ -62,6 +62,8 @@ class _DecodeGraph:
     rows than the width is padded: the extra rows are one-token requests at position 0 whose
     only page is the cache's spare page, and their logits are dropped."""
 
+    STAGES = 3
+
     def __init__(self, runner: "StepRunner", B: int):
         self.B = B
         self.used = B            # rows of the last fill that were real
@@ -74,14 +76,21 @@ class _DecodeGraph:
         for g in range(groups):
             sizes += [(f"table{g}", B * self.width), (f"slots{g}", B)]
         total = sum(n for _, n in sizes)
-        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        # The batch is kept in an ordinary host array (rows that stay get only what they gained)
+        # and leaves through one of a few pinned staging buffers handed out in turn: an asynchronous
+        # copy reads its pinned source when the device gets to it, so a buffer is written again only
+        # after the copy that last used it has completed (its event), however far the host runs ahead.
+        self.master = np.zeros(total, dtype=np.int32)
+        self.stages = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(self.STAGES)]
+        self.stage_events: List[Optional[torch.cuda.Event]] = [None] * self.STAGES
+        self.turn = 0
         self.dev = torch.zeros(total, dtype=torch.int32, device=runner.device)
+        self.nbytes = total * 4
         self.h: Dict[str, np.ndarray] = {}
         self.d: Dict[str, torch.Tensor] = {}
         o = 0
-        host_np = self.host.numpy()
         for name, n in sizes:
-            self.h[name] = host_np[o:o + n]
+            self.h[name] = self.master[o:o + n]
             self.d[name] = self.dev[o:o + n]
             o += n
         self.ctx = StepContext(
@@ -134,18 +143,33 @@ class _DecodeGraph:
                     tab[b, :n] = pages
                 known[b] = (serials[b], n)
             h[f"slots{g}"][:n_rows] = lay.slots[g]
-        self.dev.copy_(self.host, non_blocking=True)
+        i = self.turn
+        self.turn = (i + 1) % self.STAGES
+        if self.stage_events[i] is not None:
+            self.stage_events[i].synchronize()       # the copy that last read this buffer is done
+        self.stages[i].numpy()[:] = self.master
+        self.dev.copy_(self.stages[i], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.stage_events[i] = event
 
     def forget_rows(self) -> None:
         self.bound = [[(None, 0)] * self.B for _ in self.bound]
 
     def run(self, runner: "StepRunner") -> torch.Tensor:
         if self.graph is None:
+            # The warm-up runs the step for real (it loads libraries and sets kernel attributes outside
+            # the capture).  Keys and values land in the same slots every time, but a mixer with state
+            # of its own would advance it once per run: that state is put back before the replay.
+            states = runner.cache.state_tensors()
             side = torch.cuda.Stream(device=runner.device)
             side.wait_stream(torch.cuda.current_stream(runner.device))
             with torch.cuda.stream(side):
-                for _ in range(2):     # loads libraries and sets kernel attributes outside the capture
+                kept = [t.clone() for t in states]
+                for _ in range(2):
                     runner.model.forward(self.ctx, runner.layer_caches, self.d["rows"])
+                for t, k in zip(states, kept):
+                    t.copy_(k)
             torch.cuda.current_stream(runner.device).wait_stream(side)
             before = ops.total_launch_count()
             graph = torch.cuda.CUDAGraph()
@@ -261,12 +285,13 @@ class StepRunner:
             q_lens=q_lens)
 
     def _context(self, lay: _Layout):
-        tables = []
+        tables, host_tables = [], []
         for lists in lay.tables:
             width = max(1, max(len(l) for l in lists))
             bt = np.full((lay.B, width), -1, np.int32)
             for b, l in enumerate(lists):
                 bt[b, :len(l)] = l
+            host_tables.append(bt)
             tables.append(self._to_device(bt))
         kv = lay.kv_lens.tolist()
         ctx = StepContext(
@@ -283,13 +308,12 @@ class StepRunner:
             req = lay.req[lay.rows]
             ar = np.arange(R + 1, dtype=np.int32)
             kv_r = (lay.pos[lay.rows] + 1).astype(np.int32)
-            long_rows = rows.long()
             ctx.tail = StepContext(
-                num_tokens=R, num_requests=R, token_ids=ctx.token_ids.index_select(0, long_rows),
-                positions=ctx.positions.index_select(0, long_rows), token_req=self._to_device(ar[:R]),
+                num_tokens=R, num_requests=R, token_ids=self._to_device(lay.ids[lay.rows]),
+                positions=self._to_device(lay.pos[lay.rows]), token_req=self._to_device(ar[:R]),
                 cu_q=self._to_device(ar), kv_lens=self._to_device(kv_r),
-                block_tables=[t.index_select(0, self._to_device(req).long()) for t in tables] if R else tables,
-                slots=[s.index_select(0, long_rows) for s in ctx.slots],
+                block_tables=[self._to_device(np.ascontiguousarray(t[req])) for t in host_tables] if R else tables,
+                slots=[self._to_device(s[lay.rows]) for s in lay.slots],
                 state_slots=self._to_device(lay.state_slots[req]),
                 q_lens=[1] * R, kv_lens_host=kv_r.tolist(), max_q_len=1, max_kv_len=int(kv_r.max()) if R else 0)
             ctx.tail_rows = rows
@@ -333,7 +357,7 @@ class StepRunner:
                 if g is None:
                     g = self._graphs[width] = _DecodeGraph(self, width)
                 g.fill(lay, [self.cache.serial(e.request_id) for e in entries])
-                self.h2d_bytes += g.host.numel() * 4
+                self.h2d_bytes += g.nbytes
                 if ids_device is not None:
                     g.d["ids"][:lay.B].copy_(ids_device, non_blocking=True)
                 logits = g.run(self)
@@ -342,7 +366,7 @@ class StepRunner:
                 if ids_device is not None:
                     ctx.token_ids = ids_device
                     if ctx.tail is not None:
-                        ctx.tail.token_ids = ids_device.index_select(0, ctx.tail_rows.long())
+                        ctx.tail.token_ids = ops.gather_rows(ids_device, ctx.tail_rows)
                 logits = self.model.forward(ctx, self.layer_caches, rows)
         except Exception:
             for e in entries:
@@ -355,10 +379,16 @@ class StepRunner:
         self.steps_run += 1
         return logits
 
+    def status_words(self) -> List[torch.Tensor]:
+        """The device words (int32[1]) that kernels of a step may set: bad input seen by the model's
+        kernels, and a bounded wait that a tensor-core kernel gave up (its output is then unfinished)."""
+        return [self.model.status, ops.tc_status(self.device)]
+
     def check_status(self) -> None:
-        """Raise if a kernel flagged bad input (an id outside the table, non-finite logits)."""
-        code = int(self.model.status.item())
-        if code:
-            self.model.status.zero_()
-            raise RuntimeError({1: "a token id was outside the embedding table",
-                                2: "non-finite logits"}.get(code, f"device status {code}"))
+        """Raise if a kernel flagged bad input (an id outside the table, non-finite logits) or gave
+        up a bounded wait.  Waits for the device."""
+        codes = torch.cat(self.status_words()).tolist()
+        if any(codes):
+            for w in self.status_words():
+                w.zero_()
+            raise RuntimeError(ops.describe_status(max(codes)))

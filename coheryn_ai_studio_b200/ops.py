@@ -89,8 +89,9 @@ def _i32(t: torch.Tensor, name: str) -> None:
 
 
 # ------------------------------------------------------------------------------------
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] as float32.  An id outside the table sets status to 1."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+                 scale: Optional[float] = None) -> None:
+    """out[t] = table[ids[t]] (* scale) as float32.  An id outside the table sets status to 1."""
     _dev(table, ids, out, status)
     _i32(ids, "ids")
     V, H = table.shape
@@ -99,7 +100,48 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
     assert table.is_contiguous()
     lib = core()
     _check(lib, lib.coheryn_embed_gather(_ptr(table), _code(table), _ptr(ids), _ptr(out), c_int(T),
-                                         c_int(H), c_int(V), _ptr(status), _stream()))
+                                         c_int(H), c_int(V), _ptr(status), c_float(1.0 if scale is None else scale),
+                                         _stream()))
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """src[rows] for a matrix (or a vector) whose rows are contiguous; ``rows`` int32 on the device."""
+    _dev(src, rows)
+    _i32(rows, "rows")
+    R = rows.numel()
+    if src.dim() == 1:
+        out = torch.empty((R,), dtype=src.dtype, device=src.device)
+        row_bytes, stride = src.element_size(), src.stride(0) * src.element_size()
+    else:
+        assert src.dim() == 2 and src.stride(1) == 1
+        out = torch.empty((R, src.shape[1]), dtype=src.dtype, device=src.device)
+        row_bytes, stride = src.shape[1] * src.element_size(), src.stride(0) * src.element_size()
+    if R:
+        lib = core()
+        _check(lib, lib.coheryn_gather_rows(_ptr(src), c_long(stride), _ptr(rows), _ptr(out), c_int(R), c_int(row_bytes),
+                                            _stream()))
+    return out
+
+
+def scatter_words(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[rows[r]] = src[r] for vectors of 32-bit elements."""
+    _dev(src, rows, out)
+    _i32(rows, "rows")
+    assert src.element_size() == 4 and out.element_size() == 4 and src.is_contiguous() and out.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_scatter_words(_ptr(src), _ptr(rows), _ptr(out), c_int(rows.numel()), _stream()))
+
+
+def scale_add_bias(x: torch.Tensor, scale: Optional[float], bias: Optional[torch.Tensor]) -> None:
+    """In place on float32 rows: x = x * scale + bias (either may be absent)."""
+    _dev(x, bias)
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
+    if bias is not None:
+        assert bias.shape == (x.shape[1],) and bias.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_scale_add_bias(_ptr(x), c_long(x.stride(0)), c_int(x.shape[0]), c_int(x.shape[1]),
+                                           c_float(1.0 if scale is None else scale), _ptr(bias),
+                                           c_int(_code(bias) if bias is not None else F32), _stream()))
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -210,6 +252,17 @@ def qkv_rope_small(x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.T
     return q
 
 
+def seeded_fill(out: torch.Tensor, key: int, first: int, mean: float, deviation: float) -> None:
+    """out.flatten()[i] = the seeded random value of element first + i of the tensor with ``key``
+    (see weights/seeded.py), float32 or bfloat16."""
+    _dev(out)
+    assert out.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_seeded_fill(_ptr(out), c_int(_code(out)), ctypes.c_ulonglong(key), ctypes.c_ulonglong(first),
+                                        ctypes.c_ulonglong(out.numel()), ctypes.c_double(mean), ctypes.c_double(deviation),
+                                        _stream()))
+
+
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out = x @ w.T (+ bias) with float32 FMA accumulation (no tensor cores)."""
     _dev(x, w, bias, out)
@@ -286,7 +339,7 @@ def apply_penalties(logits, rows, ids, counts, rep, freq, pres) -> None:
 
 
 # ------------------------------------------------------------------------------------
-def gemm_bf16_small(x, w, bias, out, gated: bool = False) -> None:
+def gemm_bf16_small(x, w, bias, out, gated: int = 0) -> None:
     """Tensor-core product for at most 64 rows (decode); see csrc/gemm_bf16_small.cu."""
     _dev(x, w, bias, out)
     M, K = x.shape
@@ -297,7 +350,7 @@ def gemm_bf16_small(x, w, bias, out, gated: bool = False) -> None:
     _check(lib, lib.coheryn_gemm_bf16_small(
         _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
         c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)),
-        c_int(1 if gated else 0), _stream()))
+        c_int(int(gated)), _stream()))
 
 
 # Up to this many rows the weight-streaming mma.sync kernel runs; beyond it the TMA/tcgen05
@@ -314,15 +367,35 @@ def tc_status(device) -> torch.Tensor:
     return _tc_status[key]
 
 
+STATUS_MESSAGES = {1: "a token id was outside the embedding table", 2: "non-finite logits"}
+
+
+def describe_status(code: int) -> str:
+    """What a non-zero device status word means."""
+    if code in STATUS_MESSAGES:
+        return STATUS_MESSAGES[code]
+    if 11 <= code <= 39:
+        return (f"a kernel gave up a bounded wait and left its output unfinished (code {code}: 11-13 tensor-core product: "
+                "producer, MMA issuer, epilogue; 19 self-test; 31-39 prompt attention: 31 producer, 32-36 MMA issuer, "
+                "37-39 softmax)")
+    return f"device status {code}"
+
+
 def check_tc_status(device) -> None:
     code = int(tc_status(device).item())
     if code:
         tc_status(device).zero_()
-        raise KernelError(f"a kernel gave up a bounded wait (code {code}: gemm_bf16_tc 11 producer, 12 MMA issuer, "
-                          "13 epilogue; 31-39 attention_tc: 31 producer, 32-36 MMA issuer, 37-39 softmax)")
+        raise KernelError(describe_status(code))
 
 
-def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
+def selftest_bounded_wait(device, tries: int = 300, code: int = 19) -> None:
+    """Launch the self-test kernel: it waits ``tries`` times on a barrier nothing arrives on, gives
+    up, and records ``code`` in the status word of the tensor-core kernels (see csrc/selftest.cu)."""
+    lib = core()
+    _check(lib, lib.coheryn_selftest_bounded_wait(_ptr(tc_status(device)), ctypes.c_uint(tries), c_int(code), _stream()))
+
+
+def gemm_bf16_tc(x, w, bias, out, gated: int = 0) -> None:
     """TMA + tcgen05 product for many rows (prompt portions); see csrc/gemm_tc.cu."""
     _dev(x, w, bias, out)
     M, K = x.shape
@@ -336,7 +409,7 @@ def gemm_bf16_tc(x, w, bias, out, gated: bool = False) -> None:
     _check(lib, lib.coheryn_gemm_bf16_tc(
         _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
         c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)),
-        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _ptr(workspace), c_long(floats), _stream()))
+        c_int(int(gated)), _ptr(tc_status(x.device)), _ptr(workspace), c_long(floats), _stream()))
 
 
 def set_gemm_pairs(on: bool) -> None:
@@ -351,7 +424,7 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
     return max(1, int(lib.coheryn_gemm_tc_workspace_floats(c_int(M), c_int(N), c_int(K))) // (M * N))
 
 
-def gemm_bf16_tc_pair(x, w, bias, out, gated: bool = False) -> None:
+def gemm_bf16_tc_pair(x, w, bias, out, gated: int = 0) -> None:
     """The many-rows product by pairs of CTAs sharing 256 x 256 tiles (tcgen05 cta_group::2);
     see gemm_tc_pair_kernel in csrc/gemm_tc.cu."""
     _dev(x, w, bias, out)
@@ -363,7 +436,7 @@ def gemm_bf16_tc_pair(x, w, bias, out, gated: bool = False) -> None:
     _check(lib, lib.coheryn_gemm_bf16_tc_pair(
         _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
         c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(0)),
-        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _stream()))
+        c_int(int(gated)), _ptr(tc_status(x.device)), _stream()))
 
 
 _few_workspaces = {}
@@ -388,7 +461,7 @@ def few_splits(N: int, K: int) -> int:
     return int(core().coheryn_gemm_tc_few_splits(c_int(N), c_int(K)))
 
 
-def gemm_bf16_tc_few(x, w, bias, out, gated: bool = False, defer: bool = False) -> None:
+def gemm_bf16_tc_few(x, w, bias, out, gated: int = 0, defer: bool = False) -> None:
     """TMA + tcgen05 product for at most 64 rows with the features on the accumulator's
     lanes (decode, short portions); see csrc/gemm_tc_few.cu.  ``defer``: ``out`` is a float32
     stack [splits, M, N] of the K slices' sums, left for the consumer to add."""
@@ -410,7 +483,7 @@ def gemm_bf16_tc_few(x, w, bias, out, gated: bool = False, defer: bool = False) 
     _check(lib, lib.coheryn_gemm_bf16_tc_few(
         _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
         c_int(_code(out)), c_int(M), c_int(N), c_int(K), c_long(x.stride(0)), c_long(out.stride(-2)),
-        c_int(1 if gated else 0), _ptr(tc_status(x.device)), _ptr(workspace),
+        c_int(int(gated)), _ptr(tc_status(x.device)), _ptr(workspace),
         c_long(workspace.numel() if workspace is not None else 0), c_int(1 if defer else 0), _stream()))
 
 
@@ -568,22 +641,37 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
         _stream()))
 
 
-def gated_silu_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(x @ Wg.T) * (x @ Wu.T) for w_gate_up with INTERLEAVED rows (row 2j = gate_j,
+# Activations of the gated epilogue, by the code that the kernels take as their ``gated`` argument
+# (0 means "no gate").  The gate is applied in float32 inside the product's epilogue; an activation
+# that is not built is refused here by name, before anything is launched.
+GATED_ACTIVATIONS = {"silu": 1}
+
+
+def gated_activation_code(activation: str) -> int:
+    try:
+        return GATED_ACTIVATIONS[activation]
+    except KeyError:
+        raise KernelError(f"the gated epilogue of the matrix products is not built for activation {activation!r} "
+                          f"(built: {', '.join(sorted(GATED_ACTIVATIONS))})") from None
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """act(x @ Wg.T) * (x @ Wu.T) for w_gate_up with INTERLEAVED rows (row 2j = gate_j,
     row 2j+1 = up_j), so that a gate/up pair lands in one thread of the epilogue."""
+    code = gated_activation_code(activation)
     M = x.shape[0]
     I = w_gate_up.shape[0] // 2
     out = torch.empty((M, I), dtype=x.dtype, device=x.device)
     if M == 0:
         return out
     if _few_ok(x, w_gate_up):
-        gemm_bf16_tc_few(x, w_gate_up, None, out, gated=True)
+        gemm_bf16_tc_few(x, w_gate_up, None, out, gated=code)
         return out
     if _small_ok(x, w_gate_up):
-        gemm_bf16_small(x, w_gate_up, None, out, gated=True)
+        gemm_bf16_small(x, w_gate_up, None, out, gated=code)
         return out
     if _tc_ok(x, w_gate_up):
-        gemm_bf16_tc(x, w_gate_up, None, out, gated=True)
+        gemm_bf16_tc(x, w_gate_up, None, out, gated=code)
         return out
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     gemm_simt(x, w_gate_up, None, gu)

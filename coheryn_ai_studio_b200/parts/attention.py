@@ -92,12 +92,12 @@ class Attention(Mixer):
         rows, tail = step.tail_rows, step.tail
         if self._fused_rope(x, cache):
             q = self._project_rotate_write(x, step, cache)
-            return self._attend_q(q.index_select(0, rows), tail, cache) if tail.num_tokens else None
+            return self._attend_q(ops.gather_rows(q, rows), tail, cache) if tail.num_tokens else None
         if not cache.writes:   # nothing to write: the wanted rows alone make their queries
             if not tail.num_tokens:
                 return None
             b = self.b_qkv[:self.q_size] if self.b_qkv is not None else None
-            return self._attend(ops.linear(x.index_select(0, rows), self.w_qkv[:self.q_size], b), tail, cache)
+            return self._attend(ops.linear(ops.gather_rows(x, rows), self.w_qkv[:self.q_size], b), tail, cache)
         qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         rot = self.position.rotary_dim if self.position is not None else 0
         cos_sin = self.position.cos_sin() if self.position is not None else None
@@ -105,7 +105,7 @@ class Attention(Mixer):
                           self.num_kv_heads, self.head_dim, rot, cache.page_size)
         if not tail.num_tokens:
             return None
-        return self._attend_q(qkv[:, :self.q_size].index_select(0, rows), tail, cache)
+        return self._attend_q(ops.gather_rows(qkv[:, :self.q_size], rows), tail, cache)
 
     @staticmethod
     def _check(cache) -> None:

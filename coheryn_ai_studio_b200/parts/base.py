@@ -165,17 +165,45 @@ class Position(Part):
 
 
 class Arrangement:
-    """Wires the parts of one layer.  ``forward`` takes and returns the pair
-    (float32 residual stream, pending delta not yet added to it)."""
+    """Wires the parts of one layer.  A subclass names its slots in ``SLOTS`` (slot name -> role:
+    "mixer", "feed_forward" or "norm"; names in ``OPTIONAL`` may stay empty) and receives the
+    built parts by slot name; each also becomes an attribute of that name (None when empty).
+    ``forward`` takes and returns the pair (float32 residual stream, pending delta not yet added
+    to it).  The model asks an arrangement only for what is below; it never names a slot."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm):
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+    SLOTS: Dict[str, str] = {}
+    OPTIONAL: Tuple[str, ...] = ()
+
+    def __init__(self, parts: Dict[str, Part]):
+        unknown = sorted(set(parts) - set(self.SLOTS))
+        missing = sorted(set(self.SLOTS) - set(parts) - set(self.OPTIONAL))
+        if unknown or missing:
+            raise ValueError(f"arrangement {type(self).__name__}: "
+                             + (f"unknown slots {unknown} " if unknown else "")
+                             + (f"missing slots {missing} " if missing else "")
+                             + f"(slots: {sorted(self.SLOTS)})")
+        self.slots = dict(parts)
+        for name in self.SLOTS:
+            setattr(self, name, parts.get(name))
 
     def parts(self) -> Dict[str, Part]:
         """Tensor-name component -> part (names follow the checkpoint)."""
         raise NotImplementedError
+
+    def cache_owner(self) -> Optional[Part]:
+        """The part whose ``cache_requirement`` decides what cache an execution of this layer
+        gets (the first mixer by default), or None."""
+        for name, role in self.SLOTS.items():
+            if role == "mixer" and self.slots.get(name) is not None:
+                return self.slots[name]
+        return None
+
+    def norms(self) -> List[Part]:
+        return [self.slots[n] for n, role in self.SLOTS.items() if role == "norm" and n in self.slots]
+
+    def producers(self) -> List[Part]:
+        """The parts whose outputs go to a norm (mixers and feed-forwards)."""
+        return [self.slots[n] for n, role in self.SLOTS.items() if role != "norm" and n in self.slots]
 
     def forward(self, residual, delta, step: StepContext, cache: Optional[LayerCache]):
         raise NotImplementedError

@@ -9,10 +9,13 @@ from __future__ import annotations
 
 from typing import Dict
 
+from .. import ops
 from .base import Arrangement, Part, register_arrangement
 
 
 class PreNormResidual(Arrangement):
+    SLOTS = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+
     def parts(self) -> Dict[str, Part]:
         return {"input_layernorm": self.mixer_norm, "self_attn": self.mixer,
                 "post_attention_layernorm": self.feed_forward_norm, "mlp": self.feed_forward}
@@ -30,7 +33,7 @@ class PreNormResidual(Arrangement):
         mixed = self.mixer.forward_tail(self.mixer_norm.forward(residual, delta), step, cache)
         if mixed is None:
             return None, None
-        kept = residual.index_select(0, step.tail_rows)
+        kept = ops.gather_rows(residual, step.tail_rows)
         out = self.feed_forward.forward(self.feed_forward_norm.forward(kept, mixed), step.tail)
         return kept, out
 

@@ -1,4 +1,4 @@
-"""Dense gated feed-forward (SwiGLU): y = W_down (silu(W_gate x) * (W_up x)), no biases,
+"""Dense gated feed-forward: y = W_down (act(W_gate x) * (W_up x)), no biases; here act = silu (SwiGLU),
 silu(g) = g / (1 + exp(-g)) in float32
 (crates/coheryn-engine/src/inference.rs:516-540, crates/coheryn-engine/src/cpu.rs:74-78).
 """
@@ -16,8 +16,8 @@ from .base import FeedForward, Runtime, StepContext, register_feed_forward
 class GatedMLP(FeedForward):
     def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, activation: str):
         super().__init__(runtime)
-        if activation != "silu":
-            raise ValueError(f"gated feed-forward: activation {activation!r} is not implemented (silu only)")
+        ops.gated_activation_code(activation)     # refuses, by name, an activation the epilogues lack
+        self.activation = activation
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.w_gate_up = self.w_down = None
 
@@ -34,7 +34,7 @@ class GatedMLP(FeedForward):
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        act = ops.gated_silu_linear(x, self.w_gate_up)
+        act = ops.gated_linear(x, self.w_gate_up, self.activation)
         return ops.linear(act, self.w_down, partial_ok=self.partial_output)
 
 

@@ -1,3 +1,3 @@
-from .sampler import DeviceSampler, HostSampler, RequestSampler, SamplingParams, SplitMix64
+from .sampler import DeviceSampler, RequestSampler, SamplingParams, SplitMix64
 
-__all__ = ["DeviceSampler", "HostSampler", "RequestSampler", "SamplingParams", "SplitMix64"]
+__all__ = ["DeviceSampler", "RequestSampler", "SamplingParams", "SplitMix64"]

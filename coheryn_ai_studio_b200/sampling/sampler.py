@@ -7,8 +7,7 @@ Penalties over the ids seen so far (prompt and generated) come first: for a seen
 ``v = v * rep if v < 0 else v / rep``, then ``v -= presence + count * frequency``.
 
 The draw is made on the host (one 64-bit state per request, advanced only when a token is
-sampled); selection runs on the device.  :class:`HostSampler` is the same algorithm in
-float64 on the host, kept for checking the device path.
+sampled); selection runs on the device.
 """
 from __future__ import annotations
 
@@ -133,7 +132,8 @@ class DeviceSampler:
         if len(hot) < R:
             ops.argmax(logits, out, self.status)
         if hot:
-            sub = logits if len(hot) == R else logits[self._dev(np.asarray(hot, np.int64))]
+            hot_rows = self._dev(np.asarray(hot, np.int32))
+            sub = logits if len(hot) == R else ops.gather_rows(logits, hot_rows)
             temp = np.asarray([samplers[r].params.temperature for r in hot], np.float32)
             topk = np.asarray([samplers[r].params.top_k for r in hot], np.int32)
             topp = np.asarray([samplers[r].params.top_p for r in hot], np.float32)
@@ -143,7 +143,7 @@ class DeviceSampler:
             if len(hot) == R:
                 out = picked
             else:
-                out[self._dev(np.asarray(hot, np.int64))] = picked
+                ops.scatter_words(picked, hot_rows, out)
         words = [self.status] + list(extra_status)
         host = self._pinned(R + len(words))
         host[:R].copy_(out, non_blocking=True)
@@ -179,8 +179,7 @@ class DeviceSampler:
                 w.zero_()
             if status[0]:
                 raise RuntimeError("empty or non-finite logits")
-            raise RuntimeError({1: "a token id was outside the embedding table",
-                                2: "non-finite logits"}.get(max(status[1:]), f"device status {status[1:]}"))
+            raise RuntimeError(ops.describe_status(max(status[1:])))
         for s, tok in zip(pending.samplers, chosen):
             s.observe(tok)
         return chosen
@@ -191,59 +190,3 @@ class PendingSample:
 
     def __init__(self, ids, host, event, samplers, words):
         self.ids, self.host, self.event, self.samplers, self.words = ids, host, event, samplers, words
-
-
-class HostSampler:
-    """sampling.rs:147-222 on the host in float64 (checks the device path; supports a mask)."""
-
-    def __init__(self, params: SamplingParams, history: Sequence[int] = ()):
-        self.state = RequestSampler(params, history)
-
-    def _adjusted(self, i: int, v: float) -> float:
-        p = self.state.params
-        c = self.state.counts.get(i, 0)
-        if c:
-            rep = float(np.float32(p.repetition_penalty))
-            v = v * rep if v < 0 else v / rep
-            v -= float(np.float32(p.presence_penalty)) + c * float(np.float32(p.frequency_penalty))
-        return v
-
-    def sample(self, logits, allowed=None) -> int:
-        logits = np.asarray(logits, dtype=np.float32)
-        if logits.size == 0 or not np.isfinite(logits).all():
-            raise ValueError("empty or non-finite logits")
-        p = self.state.params
-        cand = [i for i in range(logits.size) if allowed is None or allowed[i]]
-        if not cand:
-            raise ValueError("sampling mask permits no token")
-        val = {i: self._adjusted(i, float(logits[i])) for i in cand}
-        if p.greedy:
-            best = cand[0]
-            for i in cand:
-                if val[i] > val[best]:
-                    best = i
-            choice = best
-        else:
-            cand.sort(key=lambda i: (-val[i], i))
-            if 0 < p.top_k < len(cand):
-                cand = cand[:p.top_k]
-            t = float(np.float32(p.temperature))
-            top_p = float(np.float32(p.top_p))
-            probs = [math.exp((val[i] - val[cand[0]]) / t) for i in cand]
-            total = sum(probs)
-            cum, n = 0.0, 0
-            for pr in probs:
-                cum += pr / total
-                n += 1
-                if cum >= top_p:
-                    break
-            probs = probs[:n]
-            threshold = self.state.rng.random() * sum(probs)
-            cum, choice = 0.0, cand[n - 1]
-            for i, pr in zip(cand, probs):
-                cum += pr
-                if threshold < cum:
-                    choice = i
-                    break
-        self.state.observe(choice)
-        return choice

@@ -33,14 +33,14 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
-    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (divides 64)")
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (any size)")
     ap.add_argument("--max-requests", type=int, default=8)
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if args.max_tokens < 1:
         ap.error("--max-tokens must be positive")
-    if args.page_size < 1 or 64 % args.page_size:
-        ap.error("--page-size must divide 64")
+    if args.page_size < 1:
+        ap.error("--page-size must be positive")
 
     import torch
 
@@ -50,7 +50,12 @@ def main(argv=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     _, model = load_model(args.model, args.dtype, args.device)
+    # --max-tokens counts every live request rounded up to 64 tokens.  Pages that divide 64 hold
+    # that exactly; with any other page size a request's last page may stick out of its rounded
+    # count, so each request gets one page of slack.
     num_pages = -(-args.max_tokens // args.page_size)
+    if 64 % args.page_size:
+        num_pages += args.max_requests
     cache = CacheManager(model.cache_requirements(), [e.cache_from for e in model.spec.schedule],
                          parse_dtype(args.dtype), torch.device(args.device), page_size=args.page_size,
                          num_pages=num_pages, max_requests=args.max_requests, prefix_reuse=False)

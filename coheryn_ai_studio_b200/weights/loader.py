@@ -116,34 +116,30 @@ class InitPolicy:
 def random_tensors(expected: Dict[str, TensorSpec], seed: int, policy: InitPolicy,
                    store: torch.dtype = torch.bfloat16, device="cpu",
                    vector_dtype: Optional[torch.dtype] = torch.float32) -> Dict[str, torch.Tensor]:
-    """Seeded random values for every expected tensor, in name order so that the
-    result depends only on (names, shapes, seed, policy).  Values are drawn in float32
-    and rounded to ``store``; norm weights are kept in ``vector_dtype`` when given, so a
+    """Seeded random values for every expected tensor: each element is a function of
+    (seed, tensor name, element index) alone (see :mod:`.seeded`), so the result is the same on
+    the host and on the device, for a whole model or for one tensor of it.  Values are made in
+    float32 and rounded to ``store``; norm weights are kept in ``vector_dtype`` when given, so a
     folder written from them exercises the "stored in 32-bit stays 32-bit" rule."""
-    gen = torch.Generator(device=device)
-    gen.manual_seed(int(seed))
+    from .seeded import seeded_tensor
     out: Dict[str, torch.Tensor] = {}
     for name in sorted(expected):
         spec = expected[name]
         if spec.role == "int_table":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        if spec.init == "zeros":
-            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
-        else:
-            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
-            if spec.init == "normal":
-                t.mul_(policy.matrix_std)
-            elif spec.init == "bias":
-                t.mul_(policy.bias_std)
-            elif spec.init == "norm":
-                t.mul_(policy.norm_jitter).add_(1.0)
-            else:
-                raise ValueError(f"tensor {name}: unknown init {spec.init!r}")
         dt = store
         if spec.init == "norm" and vector_dtype is not None:
             dt = vector_dtype
-        out[name] = t.to(dt)
+        if spec.init == "zeros":
+            out[name] = torch.zeros(spec.shape, dtype=dt, device=device)
+            continue
+        try:
+            mean, deviation = {"normal": (0.0, policy.matrix_std), "bias": (0.0, policy.bias_std),
+                               "norm": (1.0, policy.norm_jitter)}[spec.init]
+        except KeyError:
+            raise ValueError(f"tensor {name}: unknown init {spec.init!r}") from None
+        out[name] = seeded_tensor(seed, name, spec.shape, mean, deviation, dtype=dt, device=device)
     return out
 
 

@@ -171,14 +171,22 @@ def decoder_layer(x: np.ndarray, w: Dict[str, np.ndarray], prefix: str, cfg: dic
     return (x + linear(a, g("mlp.down_proj.weight"))).astype(f32)
 
 
-def forward(cfg: dict, w: Dict[str, np.ndarray], ids, layers: Optional[int] = None) -> np.ndarray:
+def forward(cfg: dict, w: Dict[str, np.ndarray], ids, layers: Optional[int] = None, rows=None,
+            layer_outputs: Optional[list] = None, window: Optional[int] = None) -> np.ndarray:
     """Logits [T, vocab] of a whole sequence (crates/coheryn-engine/src/inference.rs:403-561
-    applied to every position at once)."""
+    applied to every position at once); with ``rows`` only those positions' logits (the final norm
+    and the output product run for the rows whose logits are wanted, inference.rs:545-553).
+    ``layer_outputs``, a list, receives every layer's output [T, hidden] (the "blk.{i}.output" of
+    inference.rs:541-543).  ``window`` (not in the reference's Qwen2) hides keys at p - window and before."""
     T = len(ids)
     positions = np.arange(T)
     x = embedding(w["model.embed_tokens.weight"], ids)
     for i in range(cfg["num_hidden_layers"] if layers is None else layers):
-        x = decoder_layer(x, w, f"model.layers.{i}", cfg, positions)
+        x = decoder_layer(x, w, f"model.layers.{i}", cfg, positions, window)
+        if layer_outputs is not None:
+            layer_outputs.append(x)
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     y = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w.get("lm_head.weight")
     if head is None:

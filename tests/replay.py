@@ -11,31 +11,72 @@ import plain_qwen2 as plain
 from coheryn_ai_studio_b200.cache import CacheManager
 from coheryn_ai_studio_b200.engine import StepEntry, StepRunner, load_model, parse_dtype
 
-# Stated tolerances.  float32: the engine differs from the plain implementation only in
-# the order of float32 sums.  bfloat16: weights are identical (the folders hold bfloat16
-# values); activations and cache are rounded to 8 bits of mantissa at every part, so the
-# bound is relative to the spread of the logits.
+# Stated tolerances.  float32: the engine differs from the plain implementation only in the order of
+# float32 sums.  bfloat16: the weights are identical (the folders hold bfloat16 values); activations
+# and cache are rounded to 8 bits of mantissa at every part, so a logit is off by a few thousandths
+# of the spread of its row.  The bound is relative to that spread (the standard deviation of the plain
+# row) and small enough that ONE wrong key, value or position moves a row out of it:
+# ``assert_bound_sees_a_wrong_token`` measures that on the plain model, so the bound cannot be widened
+# past the point where it would swallow such a fault without a test failing.
 TOL_F32 = 1e-4
+BF16_SIGMAS = 0.04
 
 
-def tol_bf16(ref: np.ndarray) -> float:
-    return 0.04 * max(1.0, float(np.abs(ref).max()))
+def tol_bf16(ref_row: np.ndarray) -> float:
+    return BF16_SIGMAS * float(np.std(ref_row.astype(np.float64)))
+
+
+def assert_bound_sees_a_wrong_token(model_dir: str, tokens: List[int], places=(0, 1, 2, None)) -> float:
+    """Change one token of the sequence (so one key and one value of every layer are wrong for
+    all later rows) and check on the plain model that the LAST row then moves by more than the
+    bfloat16 bound, for a change at the start and in the middle of the sequence.  Returns the
+    smallest move seen, in units of the bound."""
+    cfg, w = plain.read_model(model_dir)
+    ref = plain_logits(model_dir, tokens)[-1]
+    bound = tol_bf16(ref)
+    worst = float("inf")
+    for place in places:
+        j = len(tokens) // 2 if place is None else place
+        if j >= len(tokens) - 1:
+            continue
+        changed = list(tokens)
+        changed[j] = (changed[j] + 1) % cfg["vocab_size"]
+        moved = float(np.abs(plain.forward(cfg, w, changed)[-1] - ref).max())
+        assert moved > 1.25 * bound, (f"a wrong token at place {j} of {len(tokens)} moves the last row by {moved:.4f}, "
+                                      f"which the bfloat16 bound {bound:.4f} would not see")
+        worst = min(worst, moved / bound)
+    return worst
 
 
 class Replay:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16,
-                 max_requests: int = 8, model=None):
+                 max_requests: int = 8, model=None, use_graphs: bool = False, prefix_reuse: bool = False,
+                 layer_outputs: bool = False):
         self.dtype = dtype
         self.model = model if model is not None else load_model(model_dir, dtype)[1]
         self.cache = CacheManager(self.model.cache_requirements(),
                                   [e.cache_from for e in self.model.spec.schedule],
                                   parse_dtype(dtype), torch.device("cuda:0"), page_size=page_size,
                                   num_pages=-(-max_tokens // page_size), max_requests=max_requests,
-                                  prefix_reuse=False)
-        self.runner = StepRunner(self.model, self.cache)
+                                  prefix_reuse=prefix_reuse)
+        self.runner = StepRunner(self.model, self.cache, use_graphs=use_graphs, graph_max_kv_len=max_tokens)
         self.positions: Dict[str, int] = {}
         self.rows: Dict[Tuple[str, int], np.ndarray] = {}
         self.pages_seen: Dict[int, int] = {}
+        self.reused: Dict[str, int] = {}
+        # (request, position) -> [schedule entries, hidden]: every layer's output, when asked for
+        self.layers: Dict[Tuple[str, int], np.ndarray] = {}
+        self.layer_outputs = layer_outputs
+
+    def admit(self, rid: str, prompt: List[int]) -> int:
+        """Admit a request with its whole prompt known, so that leading pages another request
+        filled are mapped instead of computed; returns how many tokens that saves.  The caller
+        then feeds the prompt from that place on."""
+        reused = self.cache.admit(rid, prompt)
+        assert reused is not None
+        self.positions[rid] = reused
+        self.reused[rid] = reused
+        return reused
 
     def step(self, entries: List[Tuple[str, List[int], List[int]]], end=()):
         batch = []
@@ -44,7 +85,20 @@ class Replay:
                 assert self.cache.admit(rid) is not None
                 self.positions[rid] = 0
             batch.append(StepEntry(rid, toks, want))
-        logits = self.runner.step(batch).cpu().numpy()
+        seen = []
+        if self.layer_outputs:
+            self.model.layer_observer = lambda entry, x: seen.append(x.float().cpu().numpy())
+        try:
+            logits = self.runner.step(batch).cpu().numpy()
+        finally:
+            self.model.layer_observer = None
+        if seen:
+            stack = np.stack(seen)                       # [entries, T, H]
+            o = 0
+            for rid, toks, _ in entries:
+                for t in range(len(toks)):
+                    self.layers[(rid, self.positions[rid] + t)] = stack[:, o + t]
+                o += len(toks)
         self.runner.check_status()
         self.cache.check()
         for rid, _, _ in entries:
@@ -89,5 +143,23 @@ def compare(replay: Replay, model_dir: str, sequences: Dict[str, List[int]], lab
                 f"{label} {rid}@{pos}: argmax differs"
         else:
             t = tol_bf16(ref)
-            assert diff <= t, f"{label} {rid}@{pos}: |d|={diff:.3e} > {t:.3e}"
+            assert diff <= t, f"{label} {rid}@{pos}: |d|={diff:.3e} > {t:.3e} ({BF16_SIGMAS} sigma of the row)"
     return worst
+
+
+def assert_greedy_follows_plain(model_dir: str, prompt: List[int], tokens: List[int], dtype: str, label: str = ""):
+    """Every generated token, given the tokens before it, is the plain implementation's choice: the
+    first maximum of the plain logits, or, in bfloat16, a token whose plain logit lies within twice
+    the bound of that maximum (a near-tie that rounding may decide either way).  The walk follows
+    the ENGINE's tokens, so every one of them is checked, also after a near-tie."""
+    cfg, w = plain.read_model(model_dir)
+    ids = list(prompt)
+    for k, tok in enumerate(tokens):
+        ref = plain.forward(cfg, w, ids, rows=[len(ids) - 1])[0]
+        best = int(np.argmax(ref))
+        if tok != best:
+            gap = float(ref[best] - ref[tok])
+            assert dtype != "float32" or gap < 2 * TOL_F32, f"{label} token {k}: {tok} is not the plain choice {best}"
+            assert gap <= 2 * tol_bf16(ref), (f"{label} token {k}: {tok} lies {gap:.4f} below the plain choice {best}, "
+                                              f"more than rounding explains ({2 * tol_bf16(ref):.4f})")
+        ids.append(tok)

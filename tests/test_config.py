@@ -25,8 +25,8 @@ def test_sizes_come_from_config_json(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(d))
     cfg, spec = load_config(str(tmp_path))
     assert (cfg.hidden_size, cfg.head_dim, cfg.vocab_size) == (80, 16, 77)
-    assert len(spec.layers) == 1 and spec.layers[0].mixer.params["num_heads"] == 5
-    assert spec.layers[0].feed_forward.params["intermediate_size"] == 100
+    assert len(spec.layers) == 1 and spec.layers[0].parts["mixer"].params["num_heads"] == 5
+    assert spec.layers[0].parts["feed_forward"].params["intermediate_size"] == 100
     assert spec.head_name == "lm_head" and spec.vocab_size == 77
 
 
@@ -93,8 +93,8 @@ def test_registry_semantics():
 
 def test_schedule_is_validated():
     norm = PartSpec("rmsnorm", {"size": 8, "eps": 1e-6})
-    from coheryn_ai_studio_b200.config import LayerSpec
-    layer = LayerSpec("model.layers.0", "prenorm_residual", PartSpec("attention"), PartSpec("gated_mlp"), norm, norm)
+    from coheryn_ai_studio_b200.config import prenorm_layer
+    layer = prenorm_layer("model.layers.0", PartSpec("attention"), PartSpec("gated_mlp"), norm, norm)
     def spec(schedule):
         return ModelSpec("T", 8, 10, 16, "model.embed_tokens", [layer], schedule, norm, "model.norm", None)
     spec([ScheduleEntry(0), ScheduleEntry(0), ScheduleEntry(0, cache_from=1)]).validate()
@@ -104,3 +104,38 @@ def test_schedule_is_validated():
         spec([ScheduleEntry(0, cache_from=0)]).validate()
     with pytest.raises(ValueError, match="owns no cache"):
         spec([ScheduleEntry(0), ScheduleEntry(0, cache_from=0), ScheduleEntry(0, cache_from=1)]).validate()
+
+
+def test_describe_is_metadata_only():
+    """Capabilities and cache cost from the configuration alone
+    (crates/coheryn-engine/src/adapters.rs:11-21, 39-58)."""
+    import tiny
+    arch = architecture_for(tiny.TINY_B.to_dict())
+    d = arch.describe(tiny.TINY_B)
+    caps = d["capabilities"]
+    assert caps["adapter"] == "qwen2-b200-v1" and caps["architecture"] == "Qwen2ForCausalLM"
+    assert caps["formats"] == ("safetensors", "gguf") and caps["dtypes"] == ("bfloat16", "float32")
+    assert caps["paged_kv"] and caps["fixed_state_bytes_per_request"] == 0 and caps["continuous_batching"]
+    # 3 layers x (keys + values) x 1 kv head x 32
+    assert caps["kv_bytes_per_token"] == {"bfloat16": 3 * 2 * 32 * 2, "float32": 3 * 2 * 32 * 4}
+    assert d["layers"] == 3 and d["context"] == 512 and d["vocabulary"] == 1000
+    c = tiny.TINY_B
+    per_layer = ((c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim * (c.hidden_size + 1)
+                 + c.hidden_size * c.num_attention_heads * c.head_dim + 3 * c.hidden_size * c.intermediate_size + 2 * c.hidden_size)
+    assert d["parameters"] == 3 * per_layer + 2 * c.vocab_size * c.hidden_size + c.hidden_size
+    assert d["config"]["rms_norm_eps"] == 1e-5
+
+
+def test_unknown_slot_of_an_arrangement_is_refused():
+    import torch
+    from coheryn_ai_studio_b200.config import LayerSpec
+    from coheryn_ai_studio_b200.parts import DecoderModel, Runtime
+    norm = PartSpec("rmsnorm", {"size": 8, "eps": 1e-6})
+    layer = LayerSpec("model.layers.0", "prenorm_residual", {"mixer_norm": norm, "third_norm": norm})
+    spec = ModelSpec("T", 8, 10, 16, "model.embed_tokens", [layer], [ScheduleEntry(0)], norm, "model.norm", None)
+    with pytest.raises(ValueError, match="third_norm"):
+        DecoderModel(spec, Runtime(torch.float32, torch.device("cpu")))
+    layer = LayerSpec("model.layers.0", "prenorm_residual", {"mixer_norm": norm})
+    spec = ModelSpec("T", 8, 10, 16, "model.embed_tokens", [layer], [ScheduleEntry(0)], norm, "model.norm", None)
+    with pytest.raises(ValueError, match="missing slots"):
+        DecoderModel(spec, Runtime(torch.float32, torch.device("cpu")))

@@ -1,0 +1,198 @@
+"""Weights made so that ONE key decides a row: random weights spread attention almost evenly over
+hundreds of keys, and then a key read from the wrong slot, a page's edge off by one or a window that
+ends one position early or late moves the logits by less than rounding does.  Here the first
+layer's queries of a marker token Y and the key of a marker token X carry one large component in
+the slowest-turning pair of the head, so that a row of Y puts nearly all of its weight on the one X
+far behind it; losing, misplacing or wrongly seeing that key changes the row many times the
+tolerance.  The engine is replayed whole, in portions cut at and around the key's place, token by
+token, and with pages used again, in float32 and bfloat16, against the plain implementation."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import tiny
+from replay import TOL_F32, Replay, tol_bf16
+
+pytestmark = pytest.mark.gpu
+X, Y = 7, 11           # marker tokens
+BOOST = 0.95
+
+
+def craft(folder: str) -> None:
+    """Rewrite the folder's weights in place: columns 0 and 1 of the embedding are the markers'
+    alone, every query head of layer 0 reads column 1 and the keys read column 0, both into the
+    first element of the head's slowest-turning pair."""
+    from coheryn_ai_studio_b200.weights import write_file
+    from coheryn_ai_studio_b200.weights.safetensors_io import TensorReader, read_header
+    path = os.path.join(folder, "model.safetensors")
+    entries = read_header(path)
+    reader = TensorReader(entries)
+    t = {n: reader.read(n).clone() for n in entries}
+    reader.close()
+    cfg = plain.read_model(folder)[0]
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+    slow = hd // 2 - 1
+    emb = t["model.embed_tokens.weight"].float()
+    emb[:, 0] = 0
+    emb[:, 1] = 0
+    for tok, col in ((X, 0), (Y, 1)):
+        emb[tok] *= 0.2
+        emb[tok, col] = 6.0
+    t["model.embed_tokens.weight"] = emb.to(t["model.embed_tokens.weight"].dtype)
+    p = "model.layers.0.self_attn."
+    for name, heads, col in ((p + "q_proj", cfg["num_attention_heads"], 1), (p + "k_proj", cfg["num_key_value_heads"], 0)):
+        wq, bq = t[name + ".weight"].float(), t[name + ".bias"].float()
+        for h in range(heads):
+            wq[h * hd + slow] = 0
+            wq[h * hd + slow, col] = BOOST
+            bq[h * hd + slow] = 0
+        t[name + ".weight"], t[name + ".bias"] = wq.to(t[name + ".weight"].dtype), bq.to(t[name + ".bias"].dtype)
+    write_file(path, sorted(t.items()), metadata={"format": "pt"})
+
+
+def sequence(seed: int, n: int, place: int, vocab: int, tail: int = 3):
+    """n ordinary tokens with X at ``place``, then ``tail`` times Y."""
+    rng = np.random.default_rng(seed)
+    ids = [int(v) for v in rng.integers(12, vocab, n)]
+    ids[place] = X
+    return ids + [Y] * tail
+
+
+def check(replay, folder, seqs, window=None, bound_scale=1.0):
+    cfg, w = plain.read_model(folder)
+    worst = 0.0
+    for (rid, pos), row in sorted(replay.rows.items()):
+        ref = plain.forward(cfg, w, seqs[rid], rows=[pos], window=window)[0]
+        diff = float(np.abs(row - ref).max())
+        bound = TOL_F32 if replay.dtype == "float32" else bound_scale * tol_bf16(ref)
+        assert diff <= bound, f"{rid}@{pos}: |d| = {diff:.4e} > {bound:.4e}"
+        worst = max(worst, diff / bound)
+    return worst
+
+
+@pytest.fixture(scope="module")
+def crafted(tmp_path_factory):
+    base = tmp_path_factory.mktemp("far")
+    out = {}
+    for name in ("A_loud", "B_loud"):
+        out[name] = tiny.make_folder(base, name)
+        craft(out[name])
+    return out
+
+
+def test_the_key_really_decides_the_row(crafted):
+    """On the plain model: taking the far X away moves the rows of Y by tens of bounds; changing an
+    ordinary token beside it does not.  (Without this the tests below could pass on luck.)"""
+    for name, folder in crafted.items():
+        cfg, w = plain.read_model(folder)
+        V = cfg["vocab_size"]
+        seq = sequence(1, 200, 37, V)
+        ref = plain.forward(cfg, w, seq, rows=[200, 201, 202])
+        gone = list(seq); gone[37] = 20
+        beside = list(seq); beside[38] = (beside[38] + 1 - 12) % (V - 12) + 12
+        d_gone = np.abs(plain.forward(cfg, w, gone, rows=[200, 201, 202]) - ref).max(axis=1)
+        d_beside = np.abs(plain.forward(cfg, w, beside, rows=[200, 201, 202]) - ref).max(axis=1)
+        bounds = np.array([tol_bf16(r) for r in ref])
+        assert (d_gone > 20 * bounds).all(), (name, d_gone / bounds)
+        assert (d_beside < d_gone / 8).all(), (name, d_beside / bounds)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A_loud", "B_loud"])
+def test_a_far_key_at_every_kind_of_place(name, dtype, crafted):
+    """The deciding key sits at the first position, at both sides of a page's edge, of a tile's and of
+    a split's edge (pages of 16; the kernels' tiles of 64 and 128 positions), and 230 positions back.
+    Each sequence runs whole with its last tokens decoded one by one, and again in portions cut just
+    before, at and after the key."""
+    folder = crafted[name]
+    cfg = plain.read_model(folder)[0]
+    V, n = cfg["vocab_size"], 236
+    places = [0, 1, 15, 16, 17, 63, 64, 65, 127, 128, 129, 5, 200]
+    seqs = {f"k{j}": sequence(100 + j, n, j, V) for j in places}
+    r = Replay(folder, dtype, max_tokens=4 * 256)
+    live = []
+    for rid, seq in seqs.items():                        # up to four live: pages go round
+        r.step([(rid, seq[:n], [n - 1])])
+        live.append(rid)
+        for t in range(n, n + 3):
+            r.step([(rid, [seq[t]], [0])])
+        if len(live) == 4:
+            r.step([(live[0], [Y], [0])], end=live[:3])   # one more Y row for the oldest, then three go
+            seqs[live[0]] = seqs[live[0]] + [Y]
+            live = live[3:]
+    check(r, folder, seqs)
+    cut = Replay(folder, dtype, max_tokens=2 * 256)
+    for j in places:
+        rid, seq = f"k{j}", sequence(100 + j, n, j, V)
+        edges = sorted({0, max(j - 1, 0), j, j + 1, j + 2, n // 2, n - 2, n + 3} - {0})
+        o = 0
+        for e in edges:
+            if e > o:
+                cut.step([(rid, seq[o:e], [e - o - 1])])
+                o = e
+        cut.step([(rid, [Y], [0])], end=[rid])
+        seqs[rid] = seq + [Y]
+    check(cut, folder, seqs)
+
+
+def window_spec(c):
+    from coheryn_ai_studio_b200.config import ModelSpec, PartSpec, ScheduleEntry, prenorm_layer
+    H = c["hidden_size"]
+    hd = c["head_dim"]
+    norm = PartSpec("rmsnorm", {"size": H, "eps": c["rms_norm_eps"]})
+    rope = PartSpec("rope_rotate_half", {"head_dim": hd, "rotary_dim": hd, "theta": c["rope_theta"],
+                                         "max_positions": c["max_position_embeddings"]})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": c["num_attention_heads"],
+                                  "num_kv_heads": c["num_key_value_heads"], "head_dim": hd, "qkv_bias": True,
+                                  "o_bias": False, "window": c["window"], "scale": hd ** -0.5})
+    ff = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": c["intermediate_size"], "activation": "silu"})
+    layers = [prenorm_layer(f"model.layers.{i}", attn, ff, norm, norm, rope) for i in range(c["num_hidden_layers"])]
+    return ModelSpec("ToyWindowForCausalLM", H, c["vocab_size"], c["max_position_embeddings"], "model.embed_tokens",
+                     layers, [ScheduleEntry(i) for i in range(len(layers))], norm, "model.norm", None)
+
+
+class WindowConfig(dict):
+    def to_dict(self):
+        return dict(self)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [21, 64])
+def test_a_windows_edge(window, dtype, tmp_path):
+    """Attention with a window, the deciding key exactly at its edge: the row that still sees the key
+    and the next one, which must not, both equal the plain implementation; whole, decoded one by one
+    (pages behind the window go back to the pool meanwhile) and cut at the edge."""
+    from coheryn_ai_studio_b200.config import register_architecture, unregister_architecture
+    from coheryn_ai_studio_b200.engine import write_random_model
+    cfg = WindowConfig(architectures=["ToyWindowForCausalLM"], hidden_size=96, num_attention_heads=3, num_key_value_heads=1,
+                       head_dim=32, intermediate_size=128, vocab_size=300, rms_norm_eps=1e-5, rope_theta=1e6,
+                       max_position_embeddings=512, window=window, num_hidden_layers=2)
+    register_architecture("ToyWindowForCausalLM", lambda obj: WindowConfig(obj), window_spec)
+    try:
+        folder = str(tmp_path / "win")
+        write_random_model(folder, cfg, 4, tiny.POLICY_LOUD)
+        craft(folder)
+        V, j = 300, 70
+        # Y rows at the last position that sees X (j + window - 1) and at the first that does not
+        n = j + window - 1
+        seq = sequence(9, n, j, V, tail=0) + [Y, Y, Y]
+        seqs = {"w": seq, "d": seq, "c": seq}
+        r = Replay(folder, dtype, max_tokens=3 * 192, page_size=8)
+        r.step([("w", seq, [n - 1, n, n + 1, n + 2])])
+        r.step([("d", seq[:n - 4], [n - 5])])
+        for t in range(n - 4, n + 3):
+            r.step([("d", [seq[t]], [0])])
+        assert r.cache.block_table("d", 0)[:(n + 3 - window) // 8 - 1] == [-1] * ((n + 3 - window) // 8 - 1)
+        r.step([("c", seq[:n], [n - 1])])
+        r.step([("c", seq[n:n + 1], [0])])
+        r.step([("c", seq[n + 1:], [0, 1])])
+        check(r, folder, seqs, window=window)
+        # sanity on the plain side: the two rows around the edge differ by far more than the bound
+        pcfg, w = plain.read_model(folder)
+        sees, blind = plain.forward(pcfg, w, seq, rows=[n, n + 1], window=window)
+        assert np.abs(sees - blind).max() > 20 * tol_bf16(sees)
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")

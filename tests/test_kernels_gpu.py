@@ -617,3 +617,140 @@ def test_sample_follows_reference_order(V):
     assert status.item() == 0
 
 
+
+
+# ------------------------------------------------------------------ seeded weights, row moves, status
+def test_seeded_fill_on_the_device_equals_numpy_bit_for_bit():
+    """The CUDA generator, the host runtime's and the numpy restatement of the plain implementation
+    give the same bits: float32 and bfloat16, a start in the middle of a tensor, an index beyond 2^32."""
+    import plain_random as pr
+    from coheryn_ai_studio_b200.weights.seeded import seeded_tensor
+    name = "model.layers.1.mlp.down_proj.weight"
+    for seed, first, n, mean, dev in [(11, 0, 300_001, 0.0, 0.02), (1, 2 ** 32 + 7, 8191, 1.0, 0.01), (2 ** 64 - 1, 5, 2048, 0.0, 0.1)]:
+        ref = pr.values(pr.tensor_key(seed, name), np.arange(first, first + n, dtype=np.uint64), mean, dev)
+        got = seeded_tensor(seed, name, (n,), mean, dev, device=DEV, first=first)
+        host = seeded_tensor(seed, name, (n,), mean, dev, device="cpu", first=first)
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+        assert torch.equal(got.cpu(), host)
+        got16 = seeded_tensor(seed, name, (n,), mean, dev, dtype=torch.bfloat16, device=DEV, first=first)
+        assert np.array_equal(got16.float().cpu().numpy().view(np.uint32), pr.round_bf16(ref).view(np.uint32))
+
+
+def test_random_model_on_the_device_equals_the_folder(tmp_path):
+    """One seed, one model: the folder written on the host and the model made on the device hold
+    the same values (so what a benchmark times can be checked against the plain implementation)."""
+    import tiny
+    from coheryn_ai_studio_b200.engine import load_model, random_model_on_device, write_random_model
+    from coheryn_ai_studio_b200.weights import InitPolicy
+    pol = InitPolicy(0.05, 0.1, 0.02)
+    folder = str(tmp_path / "m")
+    write_random_model(folder, tiny.TINY_B, 9, pol)
+    a = load_model(folder, "bfloat16")[1]
+    b = random_model_on_device(tiny.TINY_B, 9, "bfloat16", policy=pol)
+    assert torch.equal(a.embedding, b.embedding) and torch.equal(a.head, b.head)
+    for la, lb in zip(a.layers, b.layers):
+        assert torch.equal(la.mixer.w_qkv, lb.mixer.w_qkv) and torch.equal(la.mixer.b_qkv.float(), lb.mixer.b_qkv.float())
+        assert torch.equal(la.feed_forward.w_gate_up, lb.feed_forward.w_gate_up)
+        assert torch.equal(la.mixer_norm.weight.float(), lb.mixer_norm.weight.float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+def test_gather_scatter_rows(dtype):
+    rng = np.random.default_rng(2)
+    for T, H in [(37, 72), (9, 5), (64, 1)]:
+        src = torch.from_numpy(rng.integers(-1000, 1000, (T, H)).astype(np.float32)).to(dtype).to(DEV)
+        rows = torch.from_numpy(rng.integers(0, T, 21).astype(np.int32)).to(DEV)
+        assert torch.equal(ops().gather_rows(src, rows), src[rows.long()])
+        wide = torch.zeros((T, H + 8), dtype=dtype, device=DEV)
+        wide[:, :H] = src
+        assert torch.equal(ops().gather_rows(wide[:, :H], rows), src[rows.long()])      # a column slice: strided rows
+    vec = torch.arange(50, dtype=torch.int32, device=DEV)
+    rows = torch.tensor([49, 0, 7], dtype=torch.int32, device=DEV)
+    assert ops().gather_rows(vec, rows).tolist() == [49, 0, 7]
+    out = torch.full((50,), -1, dtype=torch.int32, device=DEV)
+    ops().scatter_words(torch.tensor([5, 6, 7], dtype=torch.int32, device=DEV), rows, out)
+    assert out[49].item() == 5 and out[0].item() == 6 and out[7].item() == 7 and int((out == -1).sum()) == 47
+
+
+def test_scale_add_bias_and_embedding_scale():
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((5, 1003)).astype(np.float32)
+    b = rng.standard_normal(1003).astype(np.float32)
+    for scale, bias in [(0.5, b), (None, b), (3.0, None)]:
+        t = t32(x)
+        ops().scale_add_bias(t, scale, t32(bias) if bias is not None else None)
+        want = x * np.float32(1.0 if scale is None else scale) + (bias if bias is not None else 0)
+        assert np.abs(t.cpu().numpy() - want).max() <= 1e-6
+    table = t32(rng.standard_normal((30, 24)).astype(np.float32))
+    ids = torch.tensor([3, 29, 0], dtype=torch.int32, device=DEV)
+    out = torch.empty((3, 24), dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().embed_gather(table, ids, out, status, scale=1.75)
+    assert torch.equal(out, table[ids.long()] * 1.75) and status.item() == 0
+
+
+def test_unbuilt_gated_activation_is_refused_by_name():
+    with pytest.raises(ops().KernelError, match="gelu"):
+        ops().gated_activation_code("gelu")
+    x = torch.zeros((4, 64), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((32, 64), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops().KernelError, match="relu2"):
+        ops().gated_linear(x, w, "relu2")
+    assert ops().gated_linear(x, w, "silu").shape == (4, 16)
+
+
+def test_a_wait_that_runs_out_becomes_an_error_on_the_host(tmp_path):
+    """A bounded wait that gives up leaves a code in the status word of the tensor-core kernels; the
+    step function, the replay program's check and the engine's sampling path all read that word and
+    raise.  The wait here is the self-test kernel's: a barrier that nothing arrives on, a few hundred
+    tries, nothing in flight when it gives up."""
+    import tiny
+    from coheryn_ai_studio_b200.cache import CacheManager
+    from coheryn_ai_studio_b200.engine import Engine, StepEntry, StepRunner, load_model
+    dev = torch.device(DEV)
+    ops().check_tc_status(dev)                                   # clean before
+    ops().selftest_bounded_wait(dev, tries=300)
+    with pytest.raises(ops().KernelError, match="bounded wait"):
+        ops().check_tc_status(dev)
+    ops().check_tc_status(dev)                                   # reading it cleared it
+    folder = tiny.make_folder(tmp_path, "A")
+    model = load_model(folder, "bfloat16")[1]
+    cache = CacheManager(model.cache_requirements(), [None] * len(model.spec.schedule), torch.bfloat16, dev,
+                         page_size=16, num_pages=8, max_requests=2, prefix_reuse=False)
+    runner = StepRunner(model, cache)
+    cache.admit("r")
+    runner.step([StepEntry("r", [1, 2, 3], [2])])
+    runner.check_status()
+    ops().selftest_bounded_wait(dev, tries=200)
+    runner.step([StepEntry("r", [4], [0])])
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        runner.check_status()
+    runner.check_status()
+    eng = Engine(model, dtype="bfloat16", context=64, max_num_seqs=2)
+    eng.add_request([5, 6, 7], max_tokens=4)
+    eng.step()
+    ops().selftest_bounded_wait(dev, tries=200)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        while eng.has_work():
+            eng.step()
+    assert int(ops().tc_status(dev).item()) == 0
+
+
+def test_device_sampler_on_the_reference_fixture():
+    """The reference's sampling fixture (fixtures/constraints/sampling-v2.json: a greedy tie, a seeded
+    masked top-k/top-p case, negative penalties, the largest seed) through the DEVICE sampler.  The
+    engine has no mask option; a masked entry is presented as a logit far below every other, which
+    the kernels rank last and give no mass."""
+    import json
+    import os
+    from coheryn_ai_studio_b200.sampling import DeviceSampler, RequestSampler, SamplingParams
+    fx = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_sampling_v2.json")))
+    sampler = DeviceSampler(torch.device(DEV))
+    for case in fx["cases"]:
+        params = SamplingParams(**case["settings"], **case["penalties"])
+        rs = RequestSampler(params, case["history"])
+        base = np.asarray(case["logits"], np.float32)
+        base[~np.asarray(case["allowed"], bool)] = np.float32(-3.0e38)
+        for expected in case["expected_ids"]:
+            logits = torch.from_numpy(base.copy()).to(DEV)[None, :]
+            assert sampler.sample(logits, [rs]) == [expected], case["id"]

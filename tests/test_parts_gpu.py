@@ -197,6 +197,25 @@ def toy_routed_ff_class():
     return HashRoutedFF
 
 
+def toy_arrangement_class():
+    from coheryn_ai_studio_b200.parts import Arrangement
+
+    class SandwichMixer(Arrangement):
+        """x += norm_after(mixer(norm_before(x))) and nothing else: three slots, no feed-forward."""
+        SLOTS = {"mixer": "mixer", "before": "norm", "after": "norm"}
+
+        def parts(self):
+            return {"before": self.before, "self_attn": self.mixer, "after": self.after}
+
+        def forward(self, residual, delta, step, cache):
+            mixed = self.mixer.forward(self.before.forward(residual, delta), step, cache)
+            if mixed.dim() == 3:
+                mixed = mixed.sum(0)
+            scratch = mixed.float().contiguous()              # the second norm normalises the mixer's output alone
+            return residual, self.after.forward(scratch, None)
+    return SandwichMixer
+
+
 def toy_position_class():
     from coheryn_ai_studio_b200.parts import Position
 
@@ -236,7 +255,7 @@ def plain_linear_rope(x, positions, head_dim, rotary_dim, rate):
 
 
 def toy_spec(c):
-    from coheryn_ai_studio_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from coheryn_ai_studio_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, prenorm_layer
     H = c["hidden_size"]
     norm = PartSpec("rmsnorm", {"size": H, "eps": c["rms_norm_eps"]})
     rope = PartSpec("rope_rotate_half", {"head_dim": c["head_dim"], "rotary_dim": c["head_dim"],
@@ -251,15 +270,19 @@ def toy_spec(c):
     linear = PartSpec("test_linear_angles", {"head_dim": c["head_dim"], "rotary_dim": c["toy_rotary_dim"],
                                              "rate": c["toy_rate"], "max_positions": c["max_position_embeddings"]})
     layers = [
-        LayerSpec("model.layers.0", "prenorm_residual", attn(None), ff, norm, norm, rope),
-        LayerSpec("model.layers.1", "prenorm_residual", PartSpec("test_decay", {"hidden_size": H, "decay": 0.5}), routed, norm, norm),
-        LayerSpec("model.layers.2", "prenorm_residual", attn(c["window"]), ff, norm, norm, linear),
+        prenorm_layer("model.layers.0", attn(None), ff, norm, norm, rope),
+        prenorm_layer("model.layers.1", PartSpec("test_decay", {"hidden_size": H, "decay": 0.5}), routed, norm, norm),
+        prenorm_layer("model.layers.2", attn(c["window"]), ff, norm, norm, linear),
+        # another arrangement, defined in this file: a mixer between two norms and no feed-forward
+        LayerSpec("model.layers.3", "test_sandwich_mixer", {"mixer": attn(None), "before": norm, "after": norm}, rope),
     ]
     # layer 0 twice (two caches), the toy layer, the windowed layer, then layer 0 a third
     # time reading the cache its FIRST run wrote
-    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2), ScheduleEntry(0, cache_from=0)]
+    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2), ScheduleEntry(3),
+                ScheduleEntry(0, cache_from=0)]
     return ModelSpec("ToyStateForCausalLM", H, c["vocab_size"], c["max_position_embeddings"], "model.embed_tokens",
-                     layers, schedule, norm, "model.norm", "lm_head")
+                     layers, schedule, norm, "model.norm", "lm_head", embedding_scale=c["embedding_scale"],
+                     logit_scale=c["logit_scale"], head_bias_name="lm_head.bias")
 
 
 class ToyConfig(dict):
@@ -269,7 +292,8 @@ class ToyConfig(dict):
 
 TOY = ToyConfig(architectures=["ToyStateForCausalLM"], hidden_size=48, num_attention_heads=3, num_key_value_heads=1,
                 head_dim=16, intermediate_size=80, vocab_size=130, rms_norm_eps=1e-5, rope_theta=1e4,
-                max_position_embeddings=128, window=11, experts=3, expert_size=40, toy_rotary_dim=8, toy_rate=0.01)
+                max_position_embeddings=128, window=11, experts=3, expert_size=40, toy_rotary_dim=8, toy_rate=0.01,
+                embedding_scale=1.75, logit_scale=0.5)
 
 
 def toy_plain_forward(cfg, w, ids):
@@ -277,7 +301,7 @@ def toy_plain_forward(cfg, w, ids):
     T = len(ids)
     positions = np.arange(T)
     hd, nh, nkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
-    x = plain.embedding(w["model.embed_tokens.weight"], ids)
+    x = (plain.embedding(w["model.embed_tokens.weight"], ids) * np.float32(cfg["embedding_scale"])).astype(np.float32)
     kept = {}
 
     def turn(x, i):
@@ -327,20 +351,32 @@ def toy_plain_forward(cfg, w, ids):
     x = routed(decay_layer(x, 1), 1)
     x = mlp(attention_layer(x, 0, None, 2), 0)
     x = mlp(attention_layer(x, 2, cfg["window"], 3), 2)
-    x = mlp(attention_layer(x, 0, None, 4, cache_from=0), 0)
-    return plain.linear(plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), w["lm_head.weight"])
+    def sandwich(x, i, entry):
+        p = f"model.layers.{i}."
+        y = plain.rms_norm(x, w[p + "before.weight"], cfg["rms_norm_eps"])
+        q = turn(plain.linear(y, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]), i)
+        k = turn(plain.linear(y, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]), i)
+        v = plain.linear(y, w[p + "self_attn.v_proj.weight"], w[p + "self_attn.v_proj.bias"])
+        o = plain.linear(plain.attention(q, k, v, nh, nkv, hd, None), w[p + "self_attn.o_proj.weight"])
+        return (x + plain.rms_norm(o, w[p + "after.weight"], cfg["rms_norm_eps"])).astype(np.float32)
+
+    x = sandwich(x, 3, 4)
+    x = mlp(attention_layer(x, 0, None, 5, cache_from=0), 0)
+    logits = plain.linear(plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), w["lm_head.weight"])
+    return (logits * np.float32(cfg["logit_scale"]) + w["lm_head.bias"].astype(np.float32)).astype(np.float32)
 
 
 @pytest.fixture(scope="module")
 def toy_folder(tmp_path_factory):
     from coheryn_ai_studio_b200.config import register_architecture, unregister_architecture
     from coheryn_ai_studio_b200.engine import write_random_model
-    from coheryn_ai_studio_b200.parts import (FEED_FORWARDS, MIXERS, POSITIONS, register_feed_forward, register_mixer,
-                                              register_position)
+    from coheryn_ai_studio_b200.parts import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, POSITIONS, register_arrangement,
+                                              register_feed_forward, register_mixer, register_position)
     from coheryn_ai_studio_b200.weights import InitPolicy
     register_mixer("test_decay", toy_decay_mixer_class())
     register_feed_forward("test_hash_routed", toy_routed_ff_class())
     register_position("test_linear_angles", toy_position_class())
+    register_arrangement("test_sandwich_mixer", toy_arrangement_class())
     register_architecture("ToyStateForCausalLM", lambda obj: ToyConfig(obj), toy_spec)
     d = str(tmp_path_factory.mktemp("toy") / "model")
     write_random_model(d, TOY, 7, InitPolicy(0.08, 0.2, 0.05))
@@ -349,6 +385,7 @@ def toy_folder(tmp_path_factory):
     MIXERS.pop("test_decay", None)
     FEED_FORWARDS.pop("test_hash_routed", None)
     POSITIONS.pop("test_linear_angles", None)
+    ARRANGEMENTS.pop("test_sandwich_mixer", None)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -362,8 +399,8 @@ def test_toy_architecture_steps_through_the_engine(toy_folder, dtype):
     rng = np.random.default_rng(3)
     seqs = {"a": rng.integers(0, 130, 45).tolist(), "b": rng.integers(0, 130, 30).tolist()}
     r = Replay(toy_folder, dtype, max_tokens=128, page_size=8)
-    assert len(r.cache.groups) == 2                       # full attention (2 entries) and the window
-    assert [len(g.entries) for g in r.cache.groups] == [2, 1]
+    assert len(r.cache.groups) == 2                       # full attention (3 entries) and the window
+    assert [len(g.entries) for g in r.cache.groups] == [3, 1]
     r.step([("a", seqs["a"][:20], list(range(20)))])
     r.step([("a", seqs["a"][20:23], [0, 1, 2]), ("b", seqs["b"][:17], list(range(17)))])
     r.step([("a", seqs["a"][23:], list(range(22))), ("b", seqs["b"][17:19], [0, 1])])
@@ -393,3 +430,149 @@ def test_toy_architecture_generates_through_the_entry_point(toy_folder):
     for _ in range(6):
         seq.append(int(np.argmax(toy_plain_forward(cfg, w, seq)[-1])))
     assert list(out[0]["token_ids"]) == seq[len(prompt):]
+
+
+# ------------------------------------------------------------------ fixed state and a window under CUDA graphs
+def device_decay_mixer_class():
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.parts import FixedState, Mixer
+    from coheryn_ai_studio_b200.weights import TensorSpec
+
+    class DeviceDecayMixer(Mixer):
+        """state = decay * state + x per request, kept in a fixed-state slot; never reads a result on
+        the host, so a decode step with it can be captured in a CUDA graph (capturable stays True)."""
+
+        def __init__(self, runtime, hidden_size, decay):
+            super().__init__(runtime)
+            self.hidden_size, self.decay = hidden_size, float(decay)
+
+        def cache_requirement(self):
+            return FixedState((self.hidden_size,), torch.float32)
+
+        def tensor_specs(self):
+            return {"mix.weight": TensorSpec((self.hidden_size, self.hidden_size))}
+
+        def bind(self, tensors):
+            self.w = tensors["mix.weight"]
+
+        def forward(self, x, step, cache):
+            xs = x.float()
+            if step.max_q_len == 1:
+                slots = step.state_slots.long()
+                out = cache.state.index_select(0, slots) * self.decay + xs
+                cache.state.index_copy_(0, slots, out)
+            else:
+                out, o = torch.empty_like(xs), 0
+                for b, n in enumerate(step.q_lens):
+                    slot = step.state_slots[b:b + 1].long()
+                    s = cache.state.index_select(0, slot)[0]
+                    for t in range(o, o + n):
+                        s = self.decay * s + xs[t]
+                        out[t] = s
+                    cache.state.index_copy_(0, slot, s[None])
+                    o += n
+            return ops.linear(out.to(x.dtype), self.w)
+    return DeviceDecayMixer
+
+
+GRAPH_TOY = ToyConfig(architectures=["ToyGraphForCausalLM"], hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+                      head_dim=16, intermediate_size=96, vocab_size=200, rms_norm_eps=1e-6, rope_theta=1e4,
+                      max_position_embeddings=128, window=7)
+
+
+def graph_toy_spec(c):
+    from coheryn_ai_studio_b200.config import ModelSpec, PartSpec, ScheduleEntry, prenorm_layer
+    H = c["hidden_size"]
+    norm = PartSpec("rmsnorm", {"size": H, "eps": c["rms_norm_eps"]})
+    rope = PartSpec("rope_rotate_half", {"head_dim": c["head_dim"], "rotary_dim": c["head_dim"], "theta": c["rope_theta"],
+                                         "max_positions": c["max_position_embeddings"]})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": c["num_attention_heads"], "num_kv_heads": c["num_key_value_heads"],
+                                  "head_dim": c["head_dim"], "qkv_bias": True, "o_bias": False, "window": c["window"],
+                                  "scale": c["head_dim"] ** -0.5})
+    ff = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": c["intermediate_size"], "activation": "silu"})
+    layers = [prenorm_layer("model.layers.0", attn, ff, norm, norm, rope),
+              prenorm_layer("model.layers.1", PartSpec("test_device_decay", {"hidden_size": H, "decay": 0.5}), ff, norm, norm)]
+    return ModelSpec("ToyGraphForCausalLM", H, c["vocab_size"], c["max_position_embeddings"], "model.embed_tokens", layers,
+                     [ScheduleEntry(0), ScheduleEntry(1)], norm, "model.norm", None)
+
+
+def graph_toy_plain(cfg, w, ids):
+    T, positions = len(ids), np.arange(len(ids))
+    hd, nh, nkv, eps = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["rms_norm_eps"]
+    x = plain.embedding(w["model.embed_tokens.weight"], ids)
+
+    def mlp(x, p):
+        y = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+        a = plain.swiglu(plain.linear(y, w[p + "mlp.gate_proj.weight"]), plain.linear(y, w[p + "mlp.up_proj.weight"]))
+        return (x + plain.linear(a, w[p + "mlp.down_proj.weight"])).astype(np.float32)
+    p = "model.layers.0."
+    y = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+    q = plain.rope(plain.linear(y, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]), positions, hd, cfg["rope_theta"])
+    k = plain.rope(plain.linear(y, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]), positions, hd, cfg["rope_theta"])
+    v = plain.linear(y, w[p + "self_attn.v_proj.weight"], w[p + "self_attn.v_proj.bias"])
+    x = (x + plain.linear(plain.attention(q, k, v, nh, nkv, hd, cfg["window"]), w[p + "self_attn.o_proj.weight"])).astype(np.float32)
+    x = mlp(x, p)
+    p = "model.layers.1."
+    y = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+    s, rows = np.zeros(y.shape[1], np.float32), []
+    for t in range(T):
+        s = (np.float32(0.5) * s + y[t]).astype(np.float32)
+        rows.append(s)
+    x = (x + plain.linear(np.stack(rows), w[p + "self_attn.mix.weight"])).astype(np.float32)
+    x = mlp(x, p)
+    return plain.linear(plain.rms_norm(x, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_fixed_state_and_a_window_under_cuda_graphs(tmp_path, dtype):
+    """A model whose parts can all be captured, one of them a mixer with state of its own, the other
+    attention with a window (pages go back while decoding): decode steps replayed from CUDA graphs
+    give the logits of the plain implementation, for every batch width met, although the capture's
+    warm-up runs the step several times (the state is put back) and a window rewrites block-table
+    rows in place."""
+    from coheryn_ai_studio_b200.config import register_architecture, unregister_architecture
+    from coheryn_ai_studio_b200.engine import write_random_model
+    from coheryn_ai_studio_b200.parts import MIXERS, register_mixer
+    from coheryn_ai_studio_b200.weights import InitPolicy
+    from replay import Replay, tol_bf16
+    register_mixer("test_device_decay", device_decay_mixer_class())
+    register_architecture("ToyGraphForCausalLM", lambda obj: ToyConfig(obj), graph_toy_spec)
+    try:
+        folder = str(tmp_path / "graph_toy")
+        write_random_model(folder, GRAPH_TOY, 13, InitPolicy(0.08, 0.2, 0.05))
+        cfg, w = plain.read_model(folder)
+        rng = np.random.default_rng(8)
+        seqs = {k: rng.integers(0, 200, n).tolist() for k, n in (("a", 40), ("b", 31), ("c", 26))}
+        r = Replay(folder, dtype, max_tokens=128, page_size=4, use_graphs=True)
+        assert r.runner.use_graphs and r.cache.has_fixed_state
+        r.step([("a", seqs["a"][:9], [8]), ("b", seqs["b"][:5], [4])])
+        for t in range(20):                                   # widths 2, then 3, then 2 again
+            entries = [("a", [seqs["a"][9 + t]], [0]), ("b", [seqs["b"][5 + t]], [0])]
+            if 4 <= t < 14:
+                entries.append(("c", [seqs["c"][t - 4]], [0]))
+            r.step(entries, end=["c"] if t == 13 else ())
+        assert sorted(r.runner._graphs) == [2, 3] and all(g.graph is not None for g in r.runner._graphs.values())
+        assert r.cache.block_table("a", 0)[:4] == [-1] * 4      # the window of 7 has passed the first pages of 4
+        for rid, seq in seqs.items():
+            ref = graph_toy_plain(cfg, w, seq)
+            rows = [(pos, row) for (k, pos), row in r.rows.items() if k == rid]
+            assert len(rows) >= 10
+            for pos, row in rows:
+                tol = 2e-4 if dtype == "float32" else tol_bf16(ref[pos])
+                assert np.abs(row - ref[pos]).max() <= tol, (rid, pos)
+    finally:
+        unregister_architecture("ToyGraphForCausalLM")
+        MIXERS.pop("test_device_decay", None)
+
+
+def test_describe_reports_capabilities_and_cache_cost(toy_folder):
+    """The registry's metadata face (crates/coheryn-engine/src/adapters.rs:11-21, 39-58): the toy
+    architecture keeps fixed state, so its bytes per request are not zero."""
+    from coheryn_ai_studio_b200.config import describe_model
+    d = describe_model(toy_folder)
+    caps = d["capabilities"]
+    assert caps["architecture"] == "ToyStateForCausalLM" and caps["adapter"] == "toystateforcausallm-b200-v1"
+    assert caps["fixed_state_bytes_per_request"] == 48 * 4 and caps["paged_kv"]
+    # four cache entries hold keys and values (three full, one windowed): 2 * kv heads * head size each
+    assert caps["kv_bytes_per_token"] == {"bfloat16": 2 * 4 * 2 * 16, "float32": 4 * 4 * 2 * 16}
+    assert d["attention_windows"] == [11] and d["schedule_entries"] == 6 and d["layers"] == 4

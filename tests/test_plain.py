@@ -105,3 +105,18 @@ def test_prefix_logits_do_not_depend_on_the_future(tmp_path):
     full = plain.forward(cfg, w, ids)
     part = plain.forward(cfg, w, ids[:11])
     assert np.allclose(full[:11], part, atol=1e-6)
+
+
+def test_the_bfloat16_bound_sees_one_wrong_token(tmp_path):
+    """The bound that the bfloat16 model tests allow (a share of the spread of the plain row) is
+    smaller than what ONE wrong token among the keys does to the last row, at the start and in the
+    middle of sequences as long as those tests replay: widening the bound until it swallows such a
+    fault fails here."""
+    import tiny
+    from replay import assert_bound_sees_a_wrong_token
+    for name in tiny.CONFIGS:
+        folder = tiny.make_folder(tmp_path, name)
+        V = tiny.CONFIGS[name][0].vocab_size
+        assert assert_bound_sees_a_wrong_token(folder, tiny.prompt(20, 90, V)) > 1.25
+        if name.endswith("loud"):
+            assert assert_bound_sees_a_wrong_token(folder, tiny.prompt(20, 150, V)) > 1.25

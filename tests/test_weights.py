@@ -144,3 +144,61 @@ def test_sharded_folder(tmp_path):
     json.dump({"weight_map": wm}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
     with pytest.raises(SafetensorsError, match="plain file name"):
         index_model_dir(d)
+
+
+# ------------------------------------------------------------------ seeded values
+def test_splitmix64_known_answers():
+    """The first outputs of SplitMix64 from state 0, as published with the generator, and the
+    sampler's stream of the reference's fixture use the same constants
+    (crates/coheryn-engine/src/sampling.rs:123-130)."""
+    import plain_random as pr
+    got = [int(v) for v in pr._draw(0, np.array([1, 2, 3], dtype=np.uint64))]
+    assert got == [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F]
+    assert plain.PlainSampler(seed=0).random() == (0xE220A8397B1DCDAF >> 11) / 2.0 ** 53
+
+
+def test_seeded_values_host_equals_numpy_bit_for_bit():
+    """The host runtime's generator (C++) and the numpy restatement of the plain implementation
+    give the same float32 and bfloat16 bits, for any stretch of a tensor."""
+    import plain_random as pr
+    from coheryn_ai_studio_b200.weights.seeded import seeded_tensor, tensor_key
+    name = "model.layers.3.self_attn.q_proj.weight"
+    assert tensor_key(7, name) == pr.tensor_key(7, name)
+    assert tensor_key(2 ** 64 - 1, "") == (2 ** 64 - 1) ^ 0xCBF29CE484222325
+    for seed, first, n, mean, dev in [(7, 0, 70001, 0.0, 0.02), (0, 2 ** 33 + 5, 4099, 1.0, 0.01), (2 ** 63 + 11, 3, 1000, 0.0, 0.1)]:
+        ref = pr.values(pr.tensor_key(seed, name), np.arange(first, first + n, dtype=np.uint64), mean, dev)
+        got = seeded_tensor(seed, name, (n,), mean, dev, first=first).numpy()
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+        got16 = seeded_tensor(seed, name, (n,), mean, dev, dtype=torch.bfloat16, first=first)
+        assert np.array_equal(got16.float().numpy().view(np.uint32), pr.round_bf16(ref).view(np.uint32))
+    # whole-tensor helper of the plain side: rows picked out equal the rows of the whole
+    whole = pr.tensor(5, "model.embed_tokens.weight", (40, 24), 0.0, 0.02)
+    some = pr.tensor(5, "model.embed_tokens.weight", (40, 24), 0.0, 0.02, rows=[39, 0, 7])
+    assert np.array_equal(whole[[39, 0, 7]], some)
+    assert np.array_equal(seeded_tensor(5, "model.embed_tokens.weight", (40, 24), 0.0, 0.02).numpy(), whole)
+
+
+def test_seeded_values_are_standard_normal():
+    import plain_random as pr
+    from coheryn_ai_studio_b200.weights.seeded import seeded_tensor
+    z = seeded_tensor(3, "t", (2_000_000,), 0.0, 1.0).double().numpy()
+    assert abs(z.mean()) < 4e-3 and abs(z.std() - 1) < 4e-3
+    assert abs((z ** 3).mean()) < 2e-2 and abs((z ** 4).mean() - 3) < 5e-2
+    assert np.isfinite(z).all() and np.abs(z).max() < 8.6            # sqrt(-2 ln 2^-53) = 8.57
+    # the spelled-out logarithm and cosine agree with the maths library to 1e-14
+    k = np.random.default_rng(0).integers(1, 2 ** 53, size=50000, dtype=np.uint64)
+    assert np.abs(pr._ln_unit(k) - np.log(k.astype(np.float64) / 2.0 ** 53)).max() < 1e-14
+    assert np.abs(pr._cos_turn(k) - np.cos(2 * np.pi * (k.astype(np.float64) / 2.0 ** 53))).max() < 1e-14
+    edge = np.array([1, 2 ** 53, 2 ** 52, 2 ** 52 + 1, 3], dtype=np.uint64)
+    assert np.abs(pr._ln_unit(edge) - np.log(edge.astype(np.float64) / 2.0 ** 53)).max() < 1e-13
+    assert pr._ln_unit(np.array([2 ** 53], dtype=np.uint64))[0] == 0.0
+
+
+def test_a_tensor_does_not_depend_on_the_others(tmp_path):
+    """value(seed, name, index): the same tensor comes out whatever else the model holds."""
+    from coheryn_ai_studio_b200.weights import InitPolicy, random_tensors
+    from coheryn_ai_studio_b200.weights.spec import TensorSpec
+    a = random_tensors({"w": TensorSpec((8, 16)), "n": TensorSpec((16,), role="vector", init="norm")}, 4, InitPolicy())
+    b = random_tensors({"w": TensorSpec((8, 16)), "aa": TensorSpec((3, 3))}, 4, InitPolicy())
+    assert torch.equal(a["w"], b["w"]) and a["n"].dtype == torch.float32 and a["w"].dtype == torch.bfloat16
+    assert not torch.equal(a["w"], random_tensors({"w": TensorSpec((8, 16))}, 5, InitPolicy())["w"])

@@ -68,3 +68,7 @@ def test_static_argmax_refuses_what_does_not_fit():
     rc = lib.coheryn_argmax_static(logits.data_ptr(), 151936, 2000, 151936, out.data_ptr(), status.data_ptr(), stream)
     assert rc != 0 and b"static scratch holds 65536" in lib.coheryn_last_error()
     torch.cuda.synchronize()
+    # 65,536 rows of a small vocabulary fit the slots but not the launch grid: refused as well
+    rc = lib.coheryn_argmax_static(logits.data_ptr(), 8, 65536, 8, out.data_ptr(), status.data_ptr(), stream)
+    assert rc != 0 and b"at most 65535 rows" in lib.coheryn_last_error()
+    torch.cuda.synchronize()

@@ -25,7 +25,8 @@ POLICY_B = InitPolicy(matrix_std=0.02, bias_std=0.1, norm_jitter=0.01)
 # changes them visibly.
 POLICY_LOUD = InitPolicy(matrix_std=0.08, bias_std=0.2, norm_jitter=0.05)
 
-CONFIGS = {"A": (TINY_A, POLICY_A, 0), "B": (TINY_B, POLICY_B, 1)}
+CONFIGS = {"A": (TINY_A, POLICY_A, 0), "B": (TINY_B, POLICY_B, 1),
+           "A_loud": (TINY_A, POLICY_LOUD, 0), "B_loud": (TINY_B, POLICY_LOUD, 1)}
 
 
 def make_folder(tmp_path, name: str, policy=None, store=torch.bfloat16) -> str:
