@@ -502,7 +502,7 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
                    const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                    const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                    const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window, float scale_log2,
-                   int split) {
+                   int split, int settled) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long long rowoff[SSTAGES][STILE];   // element offset of a tile's rows in a cache tensor, -1: not read
   __shared__ int pages_s[SPLIT_MAX / 2 + 2];     // block-table entries of the split's pages (pages of one position: splits of at most 256)
@@ -562,8 +562,11 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
 #pragma unroll
   for (int s = 0; s < SSTAGES; ++s) plan(t_first + s);
   __syncthreads();
+  // `settled` = 0: the positions before the request's new tokens may have been written by this very
+  // step (the wanted rows of a portion, run as one-token requests after the portion's keys and values
+  // went to the cache): nothing of the cache is read before the wait then.
   int issued = 0;
-  while (issued < SSTAGES && (t_first + issued >= t_end || c0 + (t_first + issued + 1) * STILE <= base_pos)) {
+  while (settled && issued < SSTAGES && (t_first + issued >= t_end || c0 + (t_first + issued + 1) * STILE <= base_pos)) {
     issue(t_first + issued);
     ++issued;
   }
@@ -760,7 +763,7 @@ template <int SSTAGES>
 int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_stride, float* scratch, int max_splits,
                          const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks,
                          const int* cu_q, const int* kv_lens, int nh, int nkv, int page_size, int window,
-                         float scale_log2, int split) {
+                         float scale_log2, int split, int settled) {
   constexpr size_t SMEM = stream_smem(SSTAGES);
   static bool configured = false;
   if (!configured) {
@@ -770,7 +773,7 @@ int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_s
   }
   co_launch(attn_stream_kernel<SSTAGES>, grid, dim3(128), SMEM, stream, (const bf16*)q, q_stride, scratch, max_splits,
             (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
-            window, scale_log2, split);
+            window, scale_log2, split, settled);
   CO_CHECK_LAUNCH("attn_stream");
   return 0;
 }
@@ -778,7 +781,7 @@ int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_s
 int launch_stream(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
                   const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
                   int page_size, int window, float scale_log2, int max_kv_len, int max_rows, float* scratch,
-                  long scratch_floats, cudaStream_t stream) {
+                  long scratch_floats, int settled, cudaStream_t stream) {
   const int split = split_keys(B, nkv, max_kv_len, page_size);
   const int max_splits = (max_kv_len + split - 1) / split + 1;
   if (!scratch || scratch_floats < (long)B * nkv * max_splits * SPLIT_FLOATS)
@@ -793,10 +796,10 @@ int launch_stream(const void* q, long q_stride, void* out, long out_stride, cons
   const bool shallow = forced_stages ? forced_stages == 2 : (long)B * nkv * ((max_kv_len + split - 1) / split) > 3 * 148L;
   const int rc = shallow ? launch_stream_kernel<2>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache,
                                                    block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, window,
-                                                   scale_log2, split)
+                                                   scale_log2, split, settled)
                          : launch_stream_kernel<3>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache,
                                                    block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, window,
-                                                   scale_log2, split);
+                                                   scale_log2, split, settled);
   if (rc) return rc;
   const int threads = 32 * (max_rows < 16 ? max_rows : 16);
   co_launch(attn_combine_kernel, dim3(nkv, B), dim3(threads), 0, stream, (const float*)scratch, max_splits,
@@ -822,13 +825,14 @@ CO_EXPORT long coheryn_attn_scratch_floats(int B, int nkv, int max_kv_len) {
 // q: [T, nh*HD] rows of stride q_stride; out likewise.  Caches: [page][kv head][slot][HD].
 // cu_q [B+1], kv_lens [B] on the device.  Host hints: max_rows = the largest q_len*G of the
 // batch, any_small / any_large = whether some request has <= 16 / > 16 rows, max_kv_len,
-// total_tokens = T, num_pages = pages per cache tensor.
+// total_tokens = T, num_pages = pages per cache tensor; settled = whether the positions before each
+// request's new tokens were written by EARLIER steps (the decode kernel then reads them ahead of time).
 CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                                      const void* v_cache, const int* block_tables, int max_blocks, const int* cu_q,
                                      const int* kv_lens, int B, int nh, int nkv, int page_size, int window,
                                      float scale, int max_rows, int any_small, int any_large, int max_kv_len,
                                      float* scratch, long scratch_floats, int* status, int total_tokens,
-                                     int num_pages, cudaStream_t stream) {
+                                     int num_pages, int settled, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nkv <= 0 || nh % nkv) CO_FAIL("attention_bf16: %d heads do not group over %d kv heads", nh, nkv);
   if ((q_stride & 7) || (out_stride & 3) || ((uintptr_t)out & 7))
@@ -864,6 +868,6 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
   }
   if (split_path)
     return launch_stream(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B, nh,
-                         nkv, page_size, window, scale_log2, max_kv_len, max_rows, scratch, scratch_floats, stream);
+                         nkv, page_size, window, scale_log2, max_kv_len, max_rows, scratch, scratch_floats, settled, stream);
   return 0;
 }

@@ -315,7 +315,8 @@ class StepRunner:
                 block_tables=[self._to_device(np.ascontiguousarray(t[req])) for t in host_tables] if R else tables,
                 slots=[self._to_device(s[lay.rows]) for s in lay.slots],
                 state_slots=self._to_device(lay.state_slots[req]),
-                q_lens=[1] * R, kv_lens_host=kv_r.tolist(), max_q_len=1, max_kv_len=int(kv_r.max()) if R else 0)
+                q_lens=[1] * R, kv_lens_host=kv_r.tolist(), max_q_len=1, max_kv_len=int(kv_r.max()) if R else 0,
+                prior_positions_settled=False)
             ctx.tail_rows = rows
         return ctx, rows
 

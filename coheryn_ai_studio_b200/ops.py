@@ -576,7 +576,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     (``step`` is a StepContext).  Chooses the kernel by dtype and shape."""
     attention_rows(q, out, k_cache, v_cache, step.block_tables[group], step.token_req,
                    step.positions, num_heads, num_kv_heads, head_dim, page_size, window, scale,
-                   cu_q=step.cu_q, kv_lens=step.kv_lens, q_lens=step.q_lens, max_kv_len=step.max_kv_len)
+                   cu_q=step.cu_q, kv_lens=step.kv_lens, q_lens=step.q_lens, max_kv_len=step.max_kv_len,
+                   settled=step.prior_positions_settled)
 
 
 def attention_lib(head_dim: int):
@@ -606,12 +607,15 @@ def set_attention_tc_cluster(head_dim: int, cluster: int) -> None:
 
 def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads, num_kv_heads,
                    head_dim, page_size, window, scale, cu_q=None, kv_lens=None, q_lens=None,
-                   max_kv_len=None, force_simple=False) -> None:
+                   max_kv_len=None, force_simple=False, settled=True) -> None:
     """Attention of rows (request token_req[i] at position positions[i]) over cache pages.
     bfloat16 rows that are whole runs of consecutive positions per request, ending at the
     request's last position (``cu_q``, ``kv_lens`` on the device, ``q_lens`` and
     ``max_kv_len`` on the host) go to the tensor-core kernels when the head size is a
-    multiple of 16 up to 256; everything else goes to the float32-arithmetic kernel."""
+    multiple of 16 up to 256; everything else goes to the float32-arithmetic kernel.
+    ``settled``: the keys and values at positions before each request's first row were written by
+    earlier steps, so the decode kernel may fetch them before it waits for the step's earlier
+    kernels; False when this step itself wrote them (the wanted rows of a portion)."""
     fast = (not force_simple and q.dtype == torch.bfloat16 and cu_q is not None and kv_lens is not None
             and q_lens is not None and max_kv_len is not None and head_dim % 16 == 0 and 16 <= head_dim <= 256
             and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0)
@@ -638,7 +642,7 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
         c_int(num_heads), c_int(num_kv_heads), c_int(page_size), c_int(window or 0), c_float(scale),
         c_int(max(rows)), c_int(1 if any_small else 0), c_int(1 if any_large else 0), c_int(max_kv_len),
         _ptr(scratch), c_long(floats), _ptr(tc_status(q.device)), c_int(q.shape[0]), c_int(k_cache.shape[0]),
-        _stream()))
+        c_int(1 if settled else 0), _stream()))
 
 
 # Activations of the gated epilogue, by the code that the kernels take as their ``gated`` argument

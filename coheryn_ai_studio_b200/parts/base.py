@@ -99,6 +99,11 @@ class StepContext:
     # that needs no logits stops after the append in the last layer).  tail.num_tokens may be 0.
     tail: Optional["StepContext"] = None
     tail_rows: Optional[torch.Tensor] = None   # [R] int32
+    # True (every ordinary step): what the cache holds at positions BEFORE a request's first token
+    # of this step was written by earlier steps, so a kernel may read it ahead of the step's own
+    # kernels.  False for the context of the wanted rows (``tail``): its one-token "requests" look
+    # back on keys and values that this same step has just written.
+    prior_positions_settled: bool = True
 
 
 # ------------------------------------------------------------------------------- parts

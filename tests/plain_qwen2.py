@@ -152,42 +152,61 @@ def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     return ((g / (f32(1.0) + np.exp(-g, dtype=f32))).astype(f32) * up.astype(f32)).astype(f32)
 
 
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    """float32 values rounded to the nearest bfloat16 (ties to even), kept as float32."""
+    u = np.ascontiguousarray(x, dtype=f32).view(np.uint32)
+    u = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    return u.view(f32)
+
+
 def decoder_layer(x: np.ndarray, w: Dict[str, np.ndarray], prefix: str, cfg: dict, positions,
-                  window: Optional[int] = None) -> np.ndarray:
-    """Pre-norm residual block (crates/coheryn-engine/src/inference.rs:440-540)."""
+                  window: Optional[int] = None, rnd=None) -> np.ndarray:
+    """Pre-norm residual block (crates/coheryn-engine/src/inference.rs:440-540).  ``rnd`` (None: the
+    identity) is applied to what a part hands to the next: see ``forward``."""
+    rnd = rnd or (lambda a: a)
     heads, kv_heads = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     hd = cfg.get("head_dim") or cfg["hidden_size"] // heads
     eps, theta = cfg["rms_norm_eps"], cfg.get("rope_theta", 10000.0)
     g = lambda n: w.get(f"{prefix}.{n}")
-    y = rms_norm(x, g("input_layernorm.weight"), eps)
-    q = linear(y, g("self_attn.q_proj.weight"), g("self_attn.q_proj.bias"))
-    k = linear(y, g("self_attn.k_proj.weight"), g("self_attn.k_proj.bias"))
-    v = linear(y, g("self_attn.v_proj.weight"), g("self_attn.v_proj.bias"))
-    q, k = rope(q, positions, hd, theta), rope(k, positions, hd, theta)
-    o = attention(q, k, v, heads, kv_heads, hd, window)
-    x = (x + linear(o, g("self_attn.o_proj.weight"))).astype(f32)
-    y = rms_norm(x, g("post_attention_layernorm.weight"), eps)
-    a = swiglu(linear(y, g("mlp.gate_proj.weight")), linear(y, g("mlp.up_proj.weight")))
-    return (x + linear(a, g("mlp.down_proj.weight"))).astype(f32)
+    y = rnd(rms_norm(x, g("input_layernorm.weight"), eps))
+    q = rnd(linear(y, g("self_attn.q_proj.weight"), g("self_attn.q_proj.bias")))
+    k = rnd(linear(y, g("self_attn.k_proj.weight"), g("self_attn.k_proj.bias")))
+    v = rnd(linear(y, g("self_attn.v_proj.weight"), g("self_attn.v_proj.bias")))
+    q, k = rnd(rope(q, positions, hd, theta)), rnd(rope(k, positions, hd, theta))
+    o = rnd(attention(q, k, v, heads, kv_heads, hd, window))
+    x = (x + rnd(linear(o, g("self_attn.o_proj.weight")))).astype(f32)
+    y = rnd(rms_norm(x, g("post_attention_layernorm.weight"), eps))
+    a = rnd(swiglu(linear(y, g("mlp.gate_proj.weight")), linear(y, g("mlp.up_proj.weight"))))
+    return (x + rnd(linear(a, g("mlp.down_proj.weight")))).astype(f32)
 
 
 def forward(cfg: dict, w: Dict[str, np.ndarray], ids, layers: Optional[int] = None, rows=None,
-            layer_outputs: Optional[list] = None, window: Optional[int] = None) -> np.ndarray:
+            layer_outputs: Optional[list] = None, window: Optional[int] = None, rounded: bool = False) -> np.ndarray:
     """Logits [T, vocab] of a whole sequence (crates/coheryn-engine/src/inference.rs:403-561
     applied to every position at once); with ``rows`` only those positions' logits (the final norm
     and the output product run for the rows whose logits are wanted, inference.rs:545-553).
     ``layer_outputs``, a list, receives every layer's output [T, hidden] (the "blk.{i}.output" of
-    inference.rs:541-543).  ``window`` (not in the reference's Qwen2) hides keys at p - window and before."""
+    inference.rs:541-543).  ``window`` (not in the reference's Qwen2) hides keys at p - window and before.
+
+    ``rounded``: the same arithmetic, but everything a part hands to the next (normalised rows,
+    q/k/v, rotated q and k, the attention output, the two projections' outputs, the gated
+    activation) is rounded to bfloat16 first; residual stream, reductions and logits stay as they
+    are.  The distance between this model and the unrounded one is what keeping activations and
+    cache in bfloat16 costs by itself, whoever does the arithmetic: the yardstick for a bfloat16
+    engine's distance from the unrounded model."""
+    rnd = round_bf16 if rounded else None
     T = len(ids)
     positions = np.arange(T)
     x = embedding(w["model.embed_tokens.weight"], ids)
     for i in range(cfg["num_hidden_layers"] if layers is None else layers):
-        x = decoder_layer(x, w, f"model.layers.{i}", cfg, positions, window)
+        x = decoder_layer(x, w, f"model.layers.{i}", cfg, positions, window, rnd)
         if layer_outputs is not None:
             layer_outputs.append(x)
     if rows is not None:
         x = x[np.asarray(rows, dtype=np.int64)]
     y = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    if rounded:
+        y = round_bf16(y)
     head = w.get("lm_head.weight")
     if head is None:
         head = w["model.embed_tokens.weight"]   # tied (inference.rs:548-552)

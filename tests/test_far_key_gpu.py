@@ -14,7 +14,7 @@ import torch
 
 import plain_qwen2 as plain
 import tiny
-from replay import TOL_F32, Replay, tol_bf16
+from replay import TOL_F32, Replay, bf16_excess, tol_bf16
 
 pytestmark = pytest.mark.gpu
 X, Y = 7, 11           # marker tokens
@@ -61,15 +61,21 @@ def sequence(seed: int, n: int, place: int, vocab: int, tail: int = 3):
     return ids + [Y] * tail
 
 
-def check(replay, folder, seqs, window=None, bound_scale=1.0):
+def check(replay, folder, seqs, window=None):
     cfg, w = plain.read_model(folder)
     worst = 0.0
     for (rid, pos), row in sorted(replay.rows.items()):
         ref = plain.forward(cfg, w, seqs[rid], rows=[pos], window=window)[0]
         diff = float(np.abs(row - ref).max())
-        bound = TOL_F32 if replay.dtype == "float32" else bound_scale * tol_bf16(ref)
-        assert diff <= bound, f"{rid}@{pos}: |d| = {diff:.4e} > {bound:.4e}"
-        worst = max(worst, diff / bound)
+        if replay.dtype == "float32":
+            excess = diff / TOL_F32
+        else:
+            excess = bf16_excess(row, ref, plain.forward(cfg, w, seqs[rid], rows=[pos], window=window, rounded=True)[0])
+        # The rounding noise of these models hangs on a few large terms (the markers' components),
+        # so two draws of it differ more than on random weights: twice the usual bound is allowed,
+        # against faults that cost tens of bounds (test_the_key_really_decides_the_row).
+        assert excess <= (1.0 if replay.dtype == "float32" else 2.0), f"{rid}@{pos}: {excess:.2f} of the bound (largest |d| = {diff:.4e})"
+        worst = max(worst, excess)
     return worst
 
 
@@ -91,13 +97,15 @@ def test_the_key_really_decides_the_row(crafted):
         V = cfg["vocab_size"]
         seq = sequence(1, 200, 37, V)
         ref = plain.forward(cfg, w, seq, rows=[200, 201, 202])
+        twin = plain.forward(cfg, w, seq, rows=[200, 201, 202], rounded=True)
         gone = list(seq); gone[37] = 20
         beside = list(seq); beside[38] = (beside[38] + 1 - 12) % (V - 12) + 12
-        d_gone = np.abs(plain.forward(cfg, w, gone, rows=[200, 201, 202]) - ref).max(axis=1)
-        d_beside = np.abs(plain.forward(cfg, w, beside, rows=[200, 201, 202]) - ref).max(axis=1)
-        bounds = np.array([tol_bf16(r) for r in ref])
-        assert (d_gone > 20 * bounds).all(), (name, d_gone / bounds)
-        assert (d_beside < d_gone / 8).all(), (name, d_beside / bounds)
+        l_gone = plain.forward(cfg, w, gone, rows=[200, 201, 202])
+        l_beside = plain.forward(cfg, w, beside, rows=[200, 201, 202])
+        e_gone = np.array([bf16_excess(g, r, t) for g, r, t in zip(l_gone, ref, twin)])
+        e_beside = np.array([bf16_excess(g, r, t) for g, r, t in zip(l_beside, ref, twin)])
+        assert (e_gone > 15).all(), (name, e_gone)
+        assert (e_beside < e_gone / 8).all(), (name, e_beside)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -193,6 +201,7 @@ def test_a_windows_edge(window, dtype, tmp_path):
         # sanity on the plain side: the two rows around the edge differ by far more than the bound
         pcfg, w = plain.read_model(folder)
         sees, blind = plain.forward(pcfg, w, seq, rows=[n, n + 1], window=window)
-        assert np.abs(sees - blind).max() > 20 * tol_bf16(sees)
+        twin = plain.forward(pcfg, w, seq, rows=[n], window=window, rounded=True)[0]
+        assert bf16_excess(blind, sees, twin) > 15
     finally:
         unregister_architecture("ToyWindowForCausalLM")

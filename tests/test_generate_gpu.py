@@ -272,3 +272,21 @@ def test_decode_steps_queued_behind_a_busy_device_keep_their_own_inputs(folders)
         runner.check_status()
         return torch.stack(out).cpu()
     assert torch.equal(run(True), run(False))
+
+
+def test_trace_command_prints_layer_outputs_and_logits(folders):
+    """``coheryn trace``: per position one line for every layer's output and one for the logits
+    (crates/coheryn-engine/src/inference.rs:541-556, crates/coheryn-cli/src/main.rs:487-506), equal
+    to the plain implementation's."""
+    p = tiny.prompt(97, 6, 512)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "coheryn"), "trace", folders["A"], "--tokens",
+                        ",".join(map(str, p)), "--context", "64", "--dtype", "float32"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert [(l["position"], l["name"]) for l in lines] == [(t, n) for t in range(6) for n in ("blk.0.output", "blk.1.output", "logits")]
+    cfg, w = plain.read_model(folders["A"])
+    layers = []
+    ref = plain.forward(cfg, w, p, layer_outputs=layers)
+    for l in lines:
+        want = ref[l["position"]] if l["name"] == "logits" else layers[int(l["name"].split(".")[1])][l["position"]]
+        assert np.abs(np.asarray(l["values"], np.float32) - want).max() <= 1e-4 * max(1.0, float(np.abs(want).max()))

@@ -117,7 +117,7 @@ def test_gated_mlp_part(dtype):
     out = ff.forward(xd, None)
     tol = 1e-4 if dtype == torch.float32 else 0.03 * np.abs(ref).max()
     assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
-    with pytest.raises(ValueError, match="gelu"):
+    with pytest.raises(RuntimeError, match="gelu"):
         GatedMLP(rt(dtype), 8, 8, "gelu")
 
 
@@ -392,7 +392,7 @@ def toy_folder(tmp_path_factory):
 def test_toy_architecture_steps_through_the_engine(toy_folder, dtype):
     """Registered, built from config.json, loaded by tensor name and stepped in portions
     beside another request, with no change to the framework."""
-    from replay import Replay
+    from replay import Replay, tol_bf16_spread
     cfg, w = plain.read_model(toy_folder)
     assert "model.layers.1.self_attn.mix.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
     assert "model.layers.1.mlp.experts.2.up.weight" in w and "model.layers.1.mlp.gate_proj.weight" not in w
@@ -412,7 +412,7 @@ def test_toy_architecture_steps_through_the_engine(toy_folder, dtype):
         ref = toy_plain_forward(cfg, w, seq)
         for (k, pos), row in r.rows.items():
             if k == rid:
-                tol = 2e-4 if dtype == "float32" else 0.04 * max(1.0, np.abs(ref[pos]).max())
+                tol = 2e-4 if dtype == "float32" else tol_bf16_spread(ref[pos], 0.1)
                 assert np.abs(row - ref[pos]).max() <= tol, (rid, pos)
     r.cache.free("a"); r.cache.free("b"); r.cache.check()
     assert r.cache.available_pages() == [16, 16]
@@ -534,7 +534,7 @@ def test_fixed_state_and_a_window_under_cuda_graphs(tmp_path, dtype):
     from coheryn_ai_studio_b200.engine import write_random_model
     from coheryn_ai_studio_b200.parts import MIXERS, register_mixer
     from coheryn_ai_studio_b200.weights import InitPolicy
-    from replay import Replay, tol_bf16
+    from replay import Replay, tol_bf16_spread
     register_mixer("test_device_decay", device_decay_mixer_class())
     register_architecture("ToyGraphForCausalLM", lambda obj: ToyConfig(obj), graph_toy_spec)
     try:
@@ -558,7 +558,7 @@ def test_fixed_state_and_a_window_under_cuda_graphs(tmp_path, dtype):
             rows = [(pos, row) for (k, pos), row in r.rows.items() if k == rid]
             assert len(rows) >= 10
             for pos, row in rows:
-                tol = 2e-4 if dtype == "float32" else tol_bf16(ref[pos])
+                tol = 2e-4 if dtype == "float32" else tol_bf16_spread(ref[pos], 0.1)
                 assert np.abs(row - ref[pos]).max() <= tol, (rid, pos)
     finally:
         unregister_architecture("ToyGraphForCausalLM")
