@@ -71,10 +71,11 @@ def check(replay, folder, seqs, window=None):
             excess = diff / TOL_F32
         else:
             excess = bf16_excess(row, ref, plain.forward(cfg, w, seqs[rid], rows=[pos], window=window, rounded=True)[0])
-        # The rounding noise of these models hangs on a few large terms (the markers' components),
-        # so two draws of it differ more than on random weights: twice the usual bound is allowed,
-        # against faults that cost tens of bounds (test_the_key_really_decides_the_row).
-        assert excess <= (1.0 if replay.dtype == "float32" else 2.0), f"{rid}@{pos}: {excess:.2f} of the bound (largest |d| = {diff:.4e})"
+        # The rounding noise of these models hangs on a few large terms (the markers' components and,
+        # with tied embeddings, their two logit columns), so two draws of it differ far more than on
+        # random weights: four times the usual bound is allowed, against faults that cost fifteen
+        # bounds and more (test_the_key_really_decides_the_row).
+        assert excess <= (1.0 if replay.dtype == "float32" else 4.0), f"{rid}@{pos}: {excess:.2f} of the bound (largest |d| = {diff:.4e})"
         worst = max(worst, excess)
     return worst
 
