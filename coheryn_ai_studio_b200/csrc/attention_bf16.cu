@@ -778,10 +778,172 @@ int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_s
   return 0;
 }
 
-int launch_stream(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
-                  const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
-                  int page_size, int window, float scale_log2, int max_kv_len, int max_rows, float* scratch,
-                  long scratch_floats, int settled, cudaStream_t stream) {
+// ------------------------------------------------------------------------------------
+// attn_merge_oproj: decoding with one token per request.  Instead of attn_combine writing the merged
+// rows and a separate product reading them back, a CTA per (query head h, tile of 128 output
+// features) merges the splits of head h for every request (as attn_combine does, in ascending order),
+// rounds the rows to bfloat16 as the combine would, and multiplies them with its tile of the output
+// matrix: out_h[b, n] = sum_k o_h[b, k] W[n, h HD + k].  The heads' contributions are left as a
+// float32 stack parts[h][b][n] for the norm that follows, which adds them in order anyway.  The W
+// tile (a constant) is fetched before the kernel waits for the splits.
+// ------------------------------------------------------------------------------------
+constexpr int MO_TILE = 128;
+constexpr int MO_THREADS = 256;
+constexpr size_t MO_SMEM_TILES = (size_t)(MO_TILE + 16) * LDS * sizeof(bf16);
+// plus, per request and split, the split's maximum (then its factor) and its sum
+inline size_t mo_smem(int max_splits) { return MO_SMEM_TILES + (size_t)2 * 16 * max_splits * sizeof(float); }
+
+__global__ void __launch_bounds__(MO_THREADS)
+attn_merge_oproj_kernel(const float* __restrict__ scratch, int max_splits, const int* __restrict__ kv_lens, int B,
+                        int nh, int nkv, int window, int split, const bf16* __restrict__ w, long ldw, int H,
+                        const void* __restrict__ bias, int bias_dtype, float* __restrict__ parts) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Ws = reinterpret_cast<bf16*>(smem_raw);      // [MO_TILE][LDS]: W[n0 + i, h HD ..]
+  bf16* As = Ws + MO_TILE * LDS;                     // [16][LDS]: the merged rows of head h
+  float* fs = reinterpret_cast<float*>(As + 16 * LDS);   // [16][max_splits]: maximum, then factor, of a split
+  float* ls = fs + 16 * max_splits;                      // [16][max_splits]: sum of a split
+  __shared__ int nsp[16];
+  __shared__ float inv_den[16];
+  co_pdl_launch_dependents();
+  const int n0 = blockIdx.x * MO_TILE, h = blockIdx.y;
+  const int G = nh / nkv, kvh = h / G, r = h % G;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  for (int c = tid; c < MO_TILE * CHUNKS; c += MO_THREADS) {
+    const int row = c / CHUNKS, piece = c % CHUNKS;
+    const bool valid = n0 + row < H;
+    cp_async16(Ws + row * LDS + piece * 8, w + (valid ? (size_t)(n0 + row) * ldw + (size_t)h * HD + piece * 8 : 0), valid);
+  }
+  cp_async_commit();
+  for (int c = tid; c < 16 * CHUNKS; c += MO_THREADS)    // rows without a request stay zero
+    *reinterpret_cast<uint4*>(As + (c / CHUNKS) * LDS + (c % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
+  if (tid < 16) {                                        // the lengths are inputs of the step
+    int n = 0;
+    if (tid < B) {
+      const int kv_len = kv_lens[tid];
+      const int key_first = window > 0 ? max(0, kv_len - window) : 0;
+      n = (kv_len - 1) / split - key_first / split + 1;
+    }
+    nsp[tid] = n;
+  }
+  __syncthreads();
+  co_pdl_wait();
+  // One round trip for everything: a thread owns (request, four columns) and asks for the first
+  // sixteen splits' accumulators at once; the (maximum, sum) pairs of all splits go to shared memory
+  // beside them, and the factors are worked out while the accumulators are still on their way.
+  constexpr int PRE = 16;
+  const int item = tid;                                   // items beyond B * HD / 4 own nothing
+  const int ib = item / (HD / 4), ic = (item - ib * (HD / 4)) * 4;
+  const bool owns = item < B * (HD / 4);
+  const int in = owns ? nsp[ib] : 0;
+  const float* ibase = scratch + ((size_t)(owns ? ib : 0) * nkv + kvh) * max_splits * SPLIT_FLOATS + r * HD + ic;
+  float4 pre[PRE];
+#pragma unroll
+  for (int u = 0; u < PRE; ++u)
+    pre[u] = u < in ? *reinterpret_cast<const float4*>(ibase + (size_t)u * SPLIT_FLOATS) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = tid; i < B * max_splits; i += MO_THREADS) {
+    const int b = i / max_splits, sp = i - b * max_splits;
+    if (sp < nsp[b]) {
+      const float2 ml = *reinterpret_cast<const float2*>(scratch + (((size_t)b * nkv + kvh) * max_splits + sp) * SPLIT_FLOATS +
+                                                         16 * HD + 2 * r);
+      fs[i] = ml.x;
+      ls[i] = ml.y;
+    }
+  }
+  __syncthreads();
+  for (int b = warp; b < B; b += MO_THREADS / 32) {      // a warp per request: the factors and the denominator
+    const int n = nsp[b];
+    float* f = fs + b * max_splits;
+    const float* l = ls + b * max_splits;
+    float M = -INFINITY;
+    for (int sp = lane; sp < n; sp += 32) M = fmaxf(M, f[sp]);
+    M = co_warp_max(M);
+    float den = 0.f;
+    for (int sp = lane; sp < n; sp += 32) {
+      const float fac = f[sp] == -INFINITY ? 0.f : exp2f(f[sp] - M);
+      f[sp] = fac;
+      den += fac * l[sp];
+    }
+    den = co_warp_sum(den);
+    if (lane == 0) inv_den[b] = 1.0f / den;
+  }
+  __syncthreads();
+  // The splits' accumulators added in ascending order: the first sixteen from registers, the rest
+  // (long contexts) eight loads at a time; then further items of a head size above 128 or B * HD / 4 > 256.
+  for (int i = tid; i < B * (HD / 4); i += MO_THREADS) {
+    const int b = i / (HD / 4), c = (i - b * (HD / 4)) * 4;
+    const int n = nsp[b];
+    const float* f = fs + b * max_splits;
+    const float* base = scratch + ((size_t)b * nkv + kvh) * max_splits * SPLIT_FLOATS + r * HD + c;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int s0 = 0;
+    if (i == tid) {
+#pragma unroll
+      for (int u = 0; u < PRE; ++u) {
+        const float fu = u < n ? f[u] : 0.f;
+        acc.x += fu * pre[u].x; acc.y += fu * pre[u].y; acc.z += fu * pre[u].z; acc.w += fu * pre[u].w;
+      }
+      s0 = PRE;
+    }
+    for (; s0 < n; s0 += 8) {
+      float4 tv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        tv[u] = s0 + u < n ? *reinterpret_cast<const float4*>(base + (size_t)(s0 + u) * SPLIT_FLOATS) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float fu = s0 + u < n ? f[s0 + u] : 0.f;
+        acc.x += fu * tv[u].x; acc.y += fu * tv[u].y; acc.z += fu * tv[u].z; acc.w += fu * tv[u].w;
+      }
+    }
+    const float inv = inv_den[b];
+    uint2 raw;
+    raw.x = pack_bf16(acc.x * inv, acc.y * inv);
+    raw.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(As + b * LDS + c) = raw;
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // out[16 requests, 128 features]: warp w owns features 16 w .. 16 w + 15
+  float o[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+#pragma unroll
+  for (int kd = 0; kd < HD / 16; ++kd) {
+    unsigned a[4];
+    ldmatrix_x4(a, As + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + kd * 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const bf16* wr = Ws + (warp * 16 + nt * 8 + g) * LDS + kd * 16 + 2 * t;
+      mma_bf16(o[nt], a, *reinterpret_cast<const unsigned*>(wr), *reinterpret_cast<const unsigned*>(wr + 8));
+    }
+  }
+  float* dst = parts + (size_t)h * B * H;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    const int n = n0 + warp * 16 + nt * 8 + 2 * t;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int b = g + half * 8;
+      if (b >= B) continue;
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        if (n + e < H) {
+          float v = o[nt][half * 2 + e];
+          if (bias && h == 0) v += co_load_any(bias, bias_dtype, n + e);
+          dst[(size_t)b * H + n + e] = v;
+        }
+    }
+  }
+}
+
+// The stream kernel over every request with at most 16 rows; the splits' partial results stay in
+// scratch.  Returns the positions per split through *split_out (and the slots per request and kv head).
+int launch_stream_splits(const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_tables,
+                         int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv, int page_size,
+                         int window, float scale_log2, int max_kv_len, float* scratch, long scratch_floats, int settled,
+                         cudaStream_t stream, int* split_out, int* max_splits_out) {
   const int split = split_keys(B, nkv, max_kv_len, page_size);
   const int max_splits = (max_kv_len + split - 1) / split + 1;
   if (!scratch || scratch_floats < (long)B * nkv * max_splits * SPLIT_FLOATS)
@@ -794,12 +956,22 @@ int launch_stream(const void* q, long q_stride, void* out, long out_stride, cons
     forced_stages = e ? atoi(e) : 0;
   }
   const bool shallow = forced_stages ? forced_stages == 2 : (long)B * nkv * ((max_kv_len + split - 1) / split) > 3 * 148L;
-  const int rc = shallow ? launch_stream_kernel<2>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache,
-                                                   block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, window,
-                                                   scale_log2, split, settled)
-                         : launch_stream_kernel<3>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache,
-                                                   block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, window,
-                                                   scale_log2, split, settled);
+  *split_out = split;
+  *max_splits_out = max_splits;
+  return shallow ? launch_stream_kernel<2>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache, block_tables,
+                                           max_blocks, cu_q, kv_lens, nh, nkv, page_size, window, scale_log2, split, settled)
+                 : launch_stream_kernel<3>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache, block_tables,
+                                           max_blocks, cu_q, kv_lens, nh, nkv, page_size, window, scale_log2, split, settled);
+}
+
+int launch_stream(const void* q, long q_stride, void* out, long out_stride, const void* k_cache, const void* v_cache,
+                  const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B, int nh, int nkv,
+                  int page_size, int window, float scale_log2, int max_kv_len, int max_rows, float* scratch,
+                  long scratch_floats, int settled, cudaStream_t stream) {
+  int split = 0, max_splits = 0;
+  const int rc = launch_stream_splits(q, q_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B, nh, nkv,
+                                      page_size, window, scale_log2, max_kv_len, scratch, scratch_floats, settled, stream,
+                                      &split, &max_splits);
   if (rc) return rc;
   const int threads = 32 * (max_rows < 16 ? max_rows : 16);
   co_launch(attn_combine_kernel, dim3(nkv, B), dim3(threads), 0, stream, (const float*)scratch, max_splits,
@@ -869,5 +1041,40 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
   if (split_path)
     return launch_stream(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B, nh,
                          nkv, page_size, window, scale_log2, max_kv_len, max_rows, scratch, scratch_floats, settled, stream);
+  return 0;
+}
+
+// Decoding, one token per request (B <= 16 requests, at most 16 heads per kv head): attention over the
+// cache pages and the output projection in two kernels.  q: [B, nh*HD]; w: [H, nh*HD] bfloat16 rows of
+// stride ldw; parts: float32 [nh][B][H], the heads' contributions to q_attended @ w.T (+ bias in part
+// 0), whose sum over the heads is the projection's output.  cu_q must be 0, 1, .., B.
+CO_EXPORT int coheryn_attention_oproj_bf16(const void* q, long q_stride, const void* k_cache, const void* v_cache,
+                                           const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens,
+                                           int B, int nh, int nkv, int page_size, int window, float scale, int max_kv_len,
+                                           float* scratch, long scratch_floats, const void* w, long ldw, int H,
+                                           const void* bias, int bias_dtype, float* parts, int settled, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (B > 16) CO_FAIL("attention_oproj: at most 16 requests, not %d", B);
+  if (nkv <= 0 || nh % nkv || nh / nkv > 16) CO_FAIL("attention_oproj: %d heads over %d kv heads", nh, nkv);
+  if ((q_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)w & 15) ||
+      (ldw & 7))
+    CO_FAIL("attention_oproj: operands must be 16-byte aligned");
+  if ((max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1 > 512) CO_FAIL("attention_oproj: %d positions are too many splits", max_kv_len);
+  int split = 0, max_splits = 0;
+  const int rc = launch_stream_splits(q, q_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B, nh, nkv,
+                                      page_size, window, scale * 1.4426950408889634f, max_kv_len, scratch, scratch_floats,
+                                      settled, stream, &split, &max_splits);
+  if (rc) return rc;
+  static size_t configured = 0;
+  const size_t smem = mo_smem(max_splits);
+  if (smem > configured) {
+    if (smem > 200 * 1024) CO_FAIL("attention_oproj: %d splits need %zu bytes of shared memory", max_splits, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_merge_oproj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) CO_FAIL("attention_oproj: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  co_launch(attn_merge_oproj_kernel, dim3((H + MO_TILE - 1) / MO_TILE, nh), dim3(MO_THREADS), smem, stream, (const float*)scratch,
+            max_splits, kv_lens, B, nh, nkv, window, split, (const bf16*)w, ldw, H, bias, bias_dtype, parts);
+  CO_CHECK_LAUNCH("attn_merge_oproj");
   return 0;
 }

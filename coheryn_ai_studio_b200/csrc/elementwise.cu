@@ -310,9 +310,10 @@ add_parts_rmsnorm_vec_kernel(float* __restrict__ resid, const float* __restrict_
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float* x = resid + src * H;
   const float* d = parts + src * H;
-  // Eight parts of every step are fetched before the first is added: the row's latency is a
-  // couple of round trips whatever the number of parts; the additions keep the order 0, 1, ...
-  constexpr int ZB = 8;
+  // Up to sixteen parts of every step are fetched before the first is added (the twelve heads of an
+  // output projection, the twelve K slices of a down projection: one round trip); the additions
+  // keep the order 0, 1, ...
+  constexpr int ZB = STEPS == 1 ? 16 : 8;
   float4 v[STEPS], sum[STEPS];
 #pragma unroll
   for (int i = 0; i < STEPS; ++i) {

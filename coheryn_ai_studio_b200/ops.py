@@ -505,8 +505,13 @@ DEFER_MIN_K = 4096
 DEFER_MIN_K_WIDE = int(os.environ.get("COHERYN_DEFER_MIN_K_WIDE", "1024"))
 
 
+# A weight matrix of at least this many elements (the output head over a large vocabulary) goes
+# through the few-rows product up to FEW_DEFER_M rows: its stream is all that matters there.
+FEW_LARGE_WEIGHT = 128 << 20
+
+
 def _few_ok(x, w, partial_ok: bool = False) -> bool:
-    if not _few_shape_ok(x, w):
+    if not _few_shape_ok(x, w, FEW_DEFER_M if w.numel() >= FEW_LARGE_WEIGHT else None):
         return False
     return partial_ok or few_splits(w.shape[0], w.shape[1]) == 1
 
@@ -643,6 +648,45 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
         c_int(max(rows)), c_int(1 if any_small else 0), c_int(1 if any_large else 0), c_int(max_kv_len),
         _ptr(scratch), c_long(floats), _ptr(tc_status(q.device)), c_int(q.shape[0]), c_int(k_cache.shape[0]),
         c_int(1 if settled else 0), _stream()))
+
+
+# Decode steps of at most this many requests merge the attention splits inside the output
+# projection's kernel (0 switches that off: the splits are merged by a kernel of their own and the
+# projection is an ordinary product).
+ATTN_OPROJ_M = int(os.environ.get("COHERYN_ATTN_OPROJ_M", "16"))
+
+
+def attention_oproj_ok(q: torch.Tensor, w_o: torch.Tensor, step, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return (q.dtype == torch.bfloat16 and w_o.dtype == torch.bfloat16 and step.max_q_len == 1
+            and 0 < step.num_requests <= min(ATTN_OPROJ_M, 16) and q.shape[0] == step.num_requests
+            and num_heads // num_kv_heads <= 16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and step.max_kv_len is not None and (step.max_kv_len + 127) // 128 + 1 <= 512
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and w_o.stride(1) == 1 and w_o.stride(0) % 8 == 0
+            and w_o.data_ptr() % 16 == 0 and w_o.shape[0] % 4 == 0)
+
+
+def attention_oproj(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int, num_heads: int,
+                    num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int], scale: float,
+                    w_o: torch.Tensor, b_o: Optional[torch.Tensor]) -> torch.Tensor:
+    """Decode attention of one token per request and the output projection: returns a float32 stack
+    [num_heads, B, H] whose sum over the heads is attention(q) @ w_o.T (+ b_o); the consumer (a norm
+    that takes partial sums) adds the heads in order.  See attn_merge_oproj in csrc/attention_bf16.cu."""
+    block_tables, cu_q, kv_lens = step.block_tables[group], step.cu_q, step.kv_lens
+    _dev(q, k_cache, v_cache, block_tables, cu_q, kv_lens, w_o, b_o)
+    _i32(block_tables, "block_tables"); _i32(cu_q, "cu_q"); _i32(kv_lens, "kv_lens")
+    B, H = step.num_requests, w_o.shape[0]
+    assert w_o.shape[1] == num_heads * head_dim and k_cache.dtype == q.dtype
+    lib = attention_lib(head_dim)
+    floats = int(lib.coheryn_attn_scratch_floats(c_int(B), c_int(num_kv_heads), c_int(step.max_kv_len)))
+    scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
+    parts = torch.empty((num_heads, B, H), dtype=torch.float32, device=q.device)
+    _check(lib, lib.coheryn_attention_oproj_bf16(
+        _ptr(q), c_long(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), c_int(block_tables.shape[1]),
+        _ptr(cu_q), _ptr(kv_lens), c_int(B), c_int(num_heads), c_int(num_kv_heads), c_int(page_size), c_int(window or 0),
+        c_float(scale), c_int(step.max_kv_len), _ptr(scratch), c_long(floats), _ptr(w_o), c_long(w_o.stride(0)), c_int(H),
+        _ptr(b_o), c_int(_code(b_o) if b_o is not None else F32), _ptr(parts), c_int(1 if step.prior_positions_settled else 0),
+        _stream()))
+    return parts
 
 
 # Activations of the gated epilogue, by the code that the kernels take as their ``gated`` argument

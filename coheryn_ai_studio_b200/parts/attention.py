@@ -128,6 +128,11 @@ class Attention(Mixer):
 
     def _attend_q(self, q: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
         """Attention of rotated queries over the cache, then the output projection."""
+        if self.partial_output and ops.attention_oproj_ok(q, self.w_o, step, self.num_heads, self.num_kv_heads, self.head_dim):
+            # a small decode batch: the splits of the attention are merged inside the projection's kernel,
+            # and the heads' contributions go to the next norm as partial sums
+            return ops.attention_oproj(q, cache.k, cache.v, step, cache.group, self.num_heads, self.num_kv_heads,
+                                       self.head_dim, cache.page_size, self.window, self.scale, self.w_o, self.b_o)
         o = torch.empty((q.shape[0], self.q_size), dtype=q.dtype, device=q.device)
         ops.attention(q, o, cache.k, cache.v, step, cache.group, self.num_heads, self.num_kv_heads, self.head_dim,
                       cache.page_size, self.window, self.scale)

@@ -754,3 +754,40 @@ def test_device_sampler_on_the_reference_fixture():
         for expected in case["expected_ids"]:
             logits = torch.from_numpy(base.copy()).to(DEV)[None, :]
             assert sampler.sample(logits, [rs]) == [expected], case["id"]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,H", [(12, 2, 128, 16, 1536), (4, 2, 16, 16, 64), (3, 1, 32, 8, 100), (16, 1, 64, 16, 200),
+                                              (6, 3, 112, 32, 264)])
+@pytest.mark.parametrize("window", [None, 150])
+def test_decode_attention_with_the_projection_merged(nh, nkv, hd, page, H, window):
+    """attn_merge_oproj: decode attention of one token per request with the splits merged inside the
+    output projection's kernel.  The sum of the heads' parts equals plain attention times the output
+    matrix; requests of one key, of a split's edge (128, 129) and of many splits; widths that are no
+    multiple of the 128-feature tile; a bias."""
+    from types import SimpleNamespace
+    rng = np.random.default_rng(nh * 7 + hd)
+    lens = [1, 128, 129, 700, 64, 333, 2, 513, 40]
+    B = len(lens)
+    kc, vc, bt, ks, vs = paged_setup(rng, lens, nkv, hd, page, torch.bfloat16, shuffle=True)
+    q = torch.from_numpy(rng.standard_normal((B, nh * hd)).astype(np.float32)).to(torch.bfloat16).to(DEV)
+    w = torch.from_numpy((rng.standard_normal((H, nh * hd)) * 0.05).astype(np.float32)).to(torch.bfloat16).to(DEV)
+    bias = torch.from_numpy(rng.standard_normal(H).astype(np.float32)).to(DEV)
+    scale = 1.0 / np.sqrt(hd)
+    step = SimpleNamespace(block_tables=[bt], cu_q=t32(np.arange(B + 1, dtype=np.int32)), kv_lens=t32(np.asarray(lens, np.int32)),
+                           num_requests=B, max_q_len=1, max_kv_len=max(lens), prior_positions_settled=True)
+    assert ops().attention_oproj_ok(q, w, step, nh, nkv, hd)
+    for b_o in (None, bias):
+        parts = ops().attention_oproj(q, kc, vc, step, 0, nh, nkv, hd, page, window, scale, w, b_o)
+        assert parts.shape == (nh, B, H)
+        attended = attention_reference(q.float().cpu().numpy(), ks, vs, list(range(B)), [n - 1 for n in lens], nh, nkv, hd,
+                                       window, scale)
+        rounded = torch.from_numpy(attended).to(torch.bfloat16).float().numpy()       # the kernel rounds the merged rows
+        ref = plain.linear(rounded, w.float().cpu().numpy(), None if b_o is None else bias.cpu().numpy())
+        got = parts.sum(0).cpu().numpy()
+        # merged rows rounded to 8 bits of mantissa before the product: relative 2^-8 of each row's terms
+        tol = 2 ** -7 * np.sqrt((rounded.astype(np.float64) ** 2).sum(axis=1, keepdims=True)) * 0.05 + 1e-3
+        assert np.all(np.abs(got - ref) <= tol)
+        # a head's part alone: its slice of the rows times its slice of the matrix
+        h = nh - 1
+        ref_h = plain.linear(rounded[:, h * hd:(h + 1) * hd], w.float().cpu().numpy()[:, h * hd:(h + 1) * hd])
+        assert np.all(np.abs(parts[h].cpu().numpy() - ref_h) <= tol)
