@@ -560,6 +560,99 @@ rope_kv_write_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
   }
 }
 
+// The same for a q/k/v product whose K slices have not been added yet: value(t, col) = sum over
+// the slices of parts[s][t][col] (in order, from zero) + bias[col], rounded to bfloat16 as the
+// product's own output would be, then rotated; q goes to q_out [T, nh * hd], k and v to the cache.
+__global__ void __launch_bounds__(32)
+rope_kv_write_parts_kernel(const float* __restrict__ parts, int splits, size_t split_stride, const void* __restrict__ bias,
+                           int bias_dtype, __nv_bfloat16* __restrict__ q_out, const int* __restrict__ positions,
+                           const float2* __restrict__ cos_sin, const int* __restrict__ slots,
+                           __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int nh, int nkv, int hd,
+                           int page_size) {
+  typedef __nv_bfloat16 T;
+  constexpr int VEC = 8;
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int t = blockIdx.x;
+  const int half = hd >> 1, per_half = half / VEC, per_head = hd / VEC;
+  const size_t width = (size_t)(nh + 2 * nkv) * hd;
+  const float* row = parts + (size_t)t * width;
+  const int pos = positions[t];
+  const float2* cs = cos_sin + (size_t)pos * half;
+  const int slot = slots[t];
+  const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  auto gather = [&](size_t col, float (&v)[VEC]) {      // eight columns from col, slices added in order, bias, rounding
+    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+    for (int z = 0; z < splits; ++z) {
+      const float4 a = *reinterpret_cast<const float4*>(row + (size_t)z * split_stride + col);
+      const float4 b = *reinterpret_cast<const float4*>(row + (size_t)z * split_stride + col + 4);
+      lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+      hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+    }
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      if (bias) v[i] += co_load_any(bias, bias_dtype, col + i);
+      v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+    }
+  };
+  // One block per (token, head): heads 0 .. nh - 1 are queries, then the keys, then the values.
+  const int head = blockIdx.y;
+  if (head < nh + nkv) {
+    for (int it = threadIdx.x; it < per_half; it += blockDim.x) {
+      const int c = it * VEC;
+      float fa[VEC], fb[VEC];
+      gather((size_t)head * hd + c, fa);
+      gather((size_t)head * hd + half + c, fb);
+      T a[VEC], b[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float2 k = cs[c + i];
+        a[i] = __float2bfloat16_rn(fmaf(fa[i], k.x, -(fb[i] * k.y)));
+        b[i] = __float2bfloat16_rn(fmaf(fa[i], k.y, fb[i] * k.x));
+      }
+      T* dst;
+      if (head < nh) dst = q_out + ((size_t)t * nh + head) * hd;
+      else {
+        if (slot < 0) continue;
+        dst = k_cache + (((size_t)page * nkv + (head - nh)) * page_size + off) * hd;
+      }
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(a);
+      *reinterpret_cast<uint4*>(dst + half + c) = *reinterpret_cast<const uint4*>(b);
+    }
+  } else if (slot >= 0) {
+    const int kvh = head - nh - nkv;
+    for (int it = threadIdx.x; it < per_head; it += blockDim.x) {
+      const int c = it * VEC;
+      float fv[VEC];
+      gather((size_t)head * hd + c, fv);
+      T v[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = __float2bfloat16_rn(fv[i]);
+      T* dst = v_cache + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(v);
+    }
+  }
+}
+
+// parts: float32 [splits][T][(nh + 2 nkv) * hd]; the whole head is rotated (rotary size = hd, hd / 2 a
+// multiple of 8); q_out: bfloat16 [T, nh * hd].
+CO_EXPORT int coheryn_rope_kv_write_parts(const float* parts, int splits, long split_stride, const void* bias, int bias_dtype,
+                                          void* q_out, const int* positions, const float* cos_sin, const int* slots,
+                                          void* k_cache, void* v_cache, int T, int nh, int nkv, int hd, int page_size,
+                                          cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (splits < 1 || (hd / 2) % 8 || (hd & 1)) CO_FAIL("rope_kv_write_parts: %d parts, head size %d", splits, hd);
+  if (((uintptr_t)parts & 15) || (split_stride & 3) || ((uintptr_t)q_out & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
+    CO_FAIL("rope_kv_write_parts: operands must be 16-byte aligned");
+  if (nh + 2 * nkv > 65535) CO_FAIL("rope_kv_write_parts: %d heads", nh + 2 * nkv);
+  co_launch(rope_kv_write_parts_kernel, dim3(T, nh + 2 * nkv), dim3(32), 0, stream, parts, splits, (size_t)split_stride, bias, bias_dtype,
+            (__nv_bfloat16*)q_out, positions, (const float2*)cos_sin, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh,
+            nkv, hd, page_size);
+  CO_CHECK_LAUNCH("rope_kv_write_parts");
+  return 0;
+}
+
 CO_EXPORT int coheryn_rope_kv_write(void* qkv, int dtype, const int* positions, const float* cos_sin,
                                     const int* slots, void* k_cache, void* v_cache, int T, int nh, int nkv,
                                     int hd, int rot, int page_size, int write_kv, cudaStream_t stream) {

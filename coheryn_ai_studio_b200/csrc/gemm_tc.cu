@@ -739,7 +739,7 @@ bool make_out_map(CUtensorMap* map, const void* out, int out_dtype, int M, int n
 template <int BN, int STAGES>
 int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, int bias_dtype, void* out,
               int out_dtype, int M, int N, int K, long ldo, int epilogue, int* status, cudaStream_t stream,
-              float* partial = nullptr, int splits = 1) {
+              float* partial = nullptr, int splits = 1, bool leave_parts = false) {
   // bfloat16 output leaves through shared memory and TMA stores where whole chunks of 64 output
   // columns divide the tile.
   CUtensorMap mo = mx;
@@ -761,7 +761,7 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
                              K, ldo, epilogue, status, used > 1 ? partial : (float*)nullptr, k_per_split);
   if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("gemm_tc");
-  if (used > 1) {
+  if (used > 1 && !leave_parts) {
     const long pairs = (long)M * ((N + 1) / 2);
     const int blocks = (int)((pairs + 255) / 256 < 148 * 8 ? (pairs + 255) / 256 : 148 * 8);
     le = co_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)partial, used, M, N, bias,
@@ -936,6 +936,39 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (bn == 256 && g_stages == 2) GO(256, 2);
   if (bn == 256 && g_stages == 3) GO(256, 3);
   if (bn == 128 && g_stages == 3) GO(128, 3);
+  if (bn == 256) GO(256, 4);
+  if (bn == 192) GO(192, 4);
+  if (bn == 128) GO(128, 6);
+  if (bn == 64) GO(64, 8);
+  GO(32, 8);
+#undef GO
+}
+
+// How many K slices coheryn_gemm_bf16_tc_parts leaves for this shape (0 or 1: the shape is not split,
+// use the ordinary entry).
+CO_EXPORT int coheryn_gemm_tc_parts_count(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0 || pair_suits(M, N)) return 0;
+  const int bn = tile_width(M, N);
+  if (bn == 256 && (long)((M + BM - 1) / BM) * ((N + 255) / 256) > 148) return 0;
+  const int s = splits_for(M, N, K, bn);
+  if (s < 2) return 0;
+  const int k_tiles = (K + BK - 1) / BK, per = (k_tiles + s - 1) / s;
+  return (k_tiles + per - 1) / per;
+}
+
+// The product of a shape whose K is split, with the addition of the slices left to the consumer:
+// parts receives float32 [count][M][N] (count = coheryn_gemm_tc_parts_count), no bias, no epilogue.
+CO_EXPORT int coheryn_gemm_bf16_tc_parts(const void* x, const void* w, float* parts, int M, int N, int K, long ldx,
+                                         int* status, cudaStream_t stream) {
+  const int count = coheryn_gemm_tc_parts_count(M, N, K);
+  if (count < 2) CO_FAIL("gemm_bf16_tc_parts: the shape M=%d N=%d K=%d is not split over K", M, N, K);
+  if ((K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc_parts: misaligned operands");
+  const int bn = tile_width(M, N);
+  const int splits = splits_for(M, N, K, bn);
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, K, bn))
+    CO_FAIL("gemm_bf16_tc_parts: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%ld)", M, N, K, ldx);
+#define GO(BN_, ST_) return launch_tc<BN_, ST_>(mx, mw, nullptr, CO_F32, parts, CO_F32, M, N, K, (long)N, 0, status, stream, parts, splits, true)
   if (bn == 256) GO(256, 4);
   if (bn == 192) GO(192, 4);
   if (bn == 128) GO(128, 6);

@@ -263,6 +263,47 @@ def seeded_fill(out: torch.Tensor, key: int, first: int, mean: float, deviation:
                                         _stream()))
 
 
+# Up to this many rows a q/k/v product whose K the many-rows kernel splits leaves the addition of
+# its slices to the rotation kernel (one kernel less between the product and the attention).
+QKV_PARTS_M = int(os.environ.get("COHERYN_QKV_PARTS_M", "256"))
+
+
+def qkv_parts_count(x, w_qkv, k_cache, rotary_dim: int, head_dim: int) -> int:
+    """The K slices that ``qkv_rope_parts`` would leave for this step's q/k/v product (0: not that path)."""
+    M, K = x.shape
+    if not (QKV_ROPE_M < M <= QKV_PARTS_M and x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+            and k_cache is not None and k_cache.dtype == torch.bfloat16 and rotary_dim == head_dim and head_dim % 16 == 0
+            and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w_qkv.is_contiguous()
+            and w_qkv.data_ptr() % 16 == 0):
+        return 0
+    return int(core().coheryn_gemm_tc_parts_count(c_int(M), c_int(w_qkv.shape[0]), c_int(K)))
+
+
+def qkv_rope_parts(x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], positions: torch.Tensor,
+                   cos_sin: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, count: int) -> torch.Tensor:
+    """q, k, v = x @ w_qkv.T (+ b) by the many-rows product with K cut into ``count`` slices, whose
+    addition, the bias, the rotation of q and k and the cache write of k and v happen in ONE following
+    kernel (see ``rope_kv_write``).  Returns the rotated q ``[T, num_heads * head_dim]``."""
+    _dev(x, w_qkv, b_qkv, positions, cos_sin, slots, k_cache, v_cache)
+    _i32(positions, "positions"); _i32(slots, "slots")
+    T, K = x.shape
+    N = w_qkv.shape[0]
+    assert N == (num_heads + 2 * num_kv_heads) * head_dim
+    assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1:] == (head_dim // 2, 2)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+    lib = core()
+    parts = torch.empty((count, T, N), dtype=torch.float32, device=x.device)
+    _check(lib, lib.coheryn_gemm_bf16_tc_parts(_ptr(x), _ptr(w_qkv), _ptr(parts), c_int(T), c_int(N), c_int(K),
+                                               c_long(x.stride(0)), _ptr(tc_status(x.device)), _stream()))
+    q = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    _check(lib, lib.coheryn_rope_kv_write_parts(
+        _ptr(parts), c_int(count), c_long(T * N), _ptr(b_qkv), c_int(_code(b_qkv) if b_qkv is not None else F32), _ptr(q),
+        _ptr(positions), _ptr(cos_sin), _ptr(slots), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(num_heads),
+        c_int(num_kv_heads), c_int(head_dim), c_int(page_size), _stream()))
+    return q
+
+
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out = x @ w.T (+ bias) with float32 FMA accumulation (no tensor cores)."""
     _dev(x, w, bias, out)

@@ -64,25 +64,40 @@ class Attention(Mixer):
         self.w_o = tensors["o_proj.weight"]
         self.b_o = tensors.get("o_proj.bias")
 
-    def _fused_rope(self, x: torch.Tensor, cache: LayerCache) -> bool:
-        """Few rows (decoding): the q/k/v product rotates and writes the cache itself."""
-        return (cache.writes and self.position is not None
-                and ops.qkv_rope_ok(x, self.w_qkv, cache.k, self.position.rotary_dim, self.head_dim))
+    def _rotated_queries(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        """q, k, v of every row; k and v (rotated k) written to the cache; returns the rotated q
+        [T, heads * head size] (possibly a column slice of a wider buffer).  Three ways to the same
+        values: few rows (decoding) rotate and write in the product's own epilogue; a product whose K
+        the many-rows kernel splits leaves the addition of its slices to the rotation kernel; otherwise
+        the product, then the rotation kernel."""
+        rot = self.position.rotary_dim if self.position is not None else 0
+        cos_sin = self.position.cos_sin() if self.position is not None else None
+        slots = step.slots[cache.group]
+        if self.position is not None and ops.qkv_rope_ok(x, self.w_qkv, cache.k, rot, self.head_dim):
+            return ops.qkv_rope_small(x, self.w_qkv, self.b_qkv, step.positions, cos_sin, slots, cache.k, cache.v,
+                                      self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size)
+        count = ops.qkv_parts_count(x, self.w_qkv, cache.k, rot, self.head_dim) if self.position is not None else 0
+        if count > 1:
+            return ops.qkv_rope_parts(x, self.w_qkv, self.b_qkv, step.positions, cos_sin, slots, cache.k, cache.v,
+                                      self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, count)
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        ops.rope_kv_write(qkv, step.positions, cos_sin, slots, cache.k, cache.v, self.num_heads, self.num_kv_heads,
+                          self.head_dim, rot, cache.page_size)
+        return qkv[:, :self.q_size]
 
-    def _project_rotate_write(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
-        return ops.qkv_rope_small(x, self.w_qkv, self.b_qkv, step.positions, self.position.cos_sin(),
-                                  step.slots[cache.group], cache.k, cache.v, self.num_heads, self.num_kv_heads,
-                                  self.head_dim, cache.page_size)
+    def _queries_only(self, x: torch.Tensor, positions: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+        """For an execution that reads keys and values another one wrote: only q is made and rotated."""
+        b = self.b_qkv[:self.q_size] if self.b_qkv is not None else None
+        q = ops.linear(x, self.w_qkv[:self.q_size], b)
+        rot = self.position.rotary_dim if self.position is not None else 0
+        cos_sin = self.position.cos_sin() if self.position is not None else None
+        ops.rope_kv_write(q, positions, cos_sin, None, None, None, self.num_heads, 0, self.head_dim, rot, cache.page_size)
+        return q
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
         self._check(cache)
-        if self._fused_rope(x, cache):
-            return self._attend_q(self._project_rotate_write(x, step, cache), step, cache)
-        if cache.writes:
-            qkv = ops.linear(x, self.w_qkv, self.b_qkv)
-        else:   # this execution reads keys and values another one wrote: only q is made
-            qkv = ops.linear(x, self.w_qkv[:self.q_size], self.b_qkv[:self.q_size] if self.b_qkv is not None else None)
-        return self._attend(qkv, step, cache)
+        q = self._rotated_queries(x, step, cache) if cache.writes else self._queries_only(x, step.positions, cache)
+        return self._attend_q(q, step, cache)
 
     supports_tail = True
 
@@ -90,41 +105,19 @@ class Attention(Mixer):
         """Keys and values of every row go to the cache; only the wanted rows attend."""
         self._check(cache)
         rows, tail = step.tail_rows, step.tail
-        if self._fused_rope(x, cache):
-            q = self._project_rotate_write(x, step, cache)
-            return self._attend_q(ops.gather_rows(q, rows), tail, cache) if tail.num_tokens else None
         if not cache.writes:   # nothing to write: the wanted rows alone make their queries
             if not tail.num_tokens:
                 return None
-            b = self.b_qkv[:self.q_size] if self.b_qkv is not None else None
-            return self._attend(ops.linear(ops.gather_rows(x, rows), self.w_qkv[:self.q_size], b), tail, cache)
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
-        rot = self.position.rotary_dim if self.position is not None else 0
-        cos_sin = self.position.cos_sin() if self.position is not None else None
-        ops.rope_kv_write(qkv, step.positions, cos_sin, step.slots[cache.group], cache.k, cache.v, self.num_heads,
-                          self.num_kv_heads, self.head_dim, rot, cache.page_size)
+            return self._attend_q(self._queries_only(ops.gather_rows(x, rows), tail.positions, cache), tail, cache)
+        q = self._rotated_queries(x, step, cache)
         if not tail.num_tokens:
             return None
-        return self._attend_q(ops.gather_rows(qkv[:, :self.q_size], rows), tail, cache)
+        return self._attend_q(ops.gather_rows(q, rows), tail, cache)
 
     @staticmethod
     def _check(cache) -> None:
         if cache is None or cache.kind != "paged":
             raise ValueError("attention needs a paged key/value cache")
-
-    def _attend(self, qkv: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
-        T = qkv.shape[0]
-        nh, hd = self.num_heads, self.head_dim
-        rot = self.position.rotary_dim if self.position is not None else 0
-        cos_sin = self.position.cos_sin() if self.position is not None else None
-        if cache.writes:
-            ops.rope_kv_write(qkv, step.positions, cos_sin, step.slots[cache.group], cache.k, cache.v,
-                              nh, self.num_kv_heads, hd, rot, cache.page_size)
-            q = qkv[:, :self.q_size]
-        else:
-            q = qkv
-            ops.rope_kv_write(q, step.positions, cos_sin, None, None, None, nh, 0, hd, rot, cache.page_size)
-        return self._attend_q(q, step, cache)
 
     def _attend_q(self, q: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
         """Attention of rotated queries over the cache, then the output projection."""

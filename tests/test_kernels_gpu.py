@@ -791,3 +791,38 @@ def test_decode_attention_with_the_projection_merged(nh, nkv, hd, page, H, windo
         h = nh - 1
         ref_h = plain.linear(rounded[:, h * hd:(h + 1) * hd], w.float().cpu().numpy()[:, h * hd:(h + 1) * hd])
         assert np.all(np.abs(parts[h].cpu().numpy() - ref_h) <= tol)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,K,page,T", [(12, 2, 128, 1536, 16, 64), (4, 2, 64, 1024, 16, 40), (28, 4, 128, 3584, 16, 150),
+                                                (6, 2, 32, 768, 8, 130)])
+def test_qkv_product_whose_slices_the_rotation_adds(nh, nkv, hd, K, page, T):
+    """A q/k/v product whose K the many-rows kernel splits, with the addition of the slices, the bias,
+    the rotation and the cache write in one following kernel: the bits of the product with its own
+    reduction followed by the rotation kernel."""
+    rng = np.random.default_rng(nh + hd + T)
+    N = (nh + 2 * nkv) * hd
+    x = t32(rng.standard_normal((T, K)).astype(np.float32)).to(torch.bfloat16)
+    w = t32((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
+    b = t32(rng.standard_normal(N).astype(np.float32))
+    max_pos = 300
+    ang = rng.uniform(0, 6.28, size=(max_pos, hd // 2)).astype(np.float32)
+    cos_sin = t32(np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32))
+    positions = t32(rng.integers(0, max_pos, size=T).astype(np.int32))
+    pages = 40
+    slots_np = rng.permutation(pages * page)[:T].astype(np.int32)
+    slots_np[1] = -1                                   # a row that writes nothing
+    slots = t32(slots_np)
+    kc = torch.zeros(pages, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    count = ops().qkv_parts_count(x, w, kc, hd, hd)
+    assert count > 1, "the shape was meant to be one whose K is split"
+    for bias in (b, None):
+        kc.zero_(); vc.zero_()
+        q = ops().qkv_rope_parts(x, w, bias, positions, cos_sin, slots, kc, vc, nh, nkv, hd, page, count)
+        qkv = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_bf16_tc(x, w, bias, qkv)            # the same kernel, its own ordered reduction
+        kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+        ops().rope_kv_write(qkv, positions, cos_sin, slots, kc2, vc2, nh, nkv, hd, hd, page)
+        assert torch.equal(q, qkv[:, :nh * hd])
+        assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    ops().check_tc_status(torch.device(DEV))
