@@ -276,8 +276,7 @@ def main() -> int:
             assert eng.cache.admit(req.request_id) is not None
             assert eng.cache.reserve(req.request_id, prompt[:-1])
             eng.cache.commit(req.request_id)
-            req.num_computed = n - 1
-            eng.scheduler.running.append(req)
+            eng.scheduler.adopt_running(req, n - 1)
             eng._requests[req.request_id] = req
             from coheryn_ai_studio_b200.engine.engine import _Timing
             eng._timing[req.request_id] = _Timing(time.perf_counter())

@@ -12,39 +12,54 @@ prompt_len - 1 so the last prompt token is always recomputed:
 crates/coheryn-engine/src/inference/generation.rs:189-202; here the unit is a page).
 Prefix reuse is switched off when any group has a window or any mixer keeps fixed
 state, because those cannot be rebuilt from pages alone.
+
+The books (which request holds which page in which group, what is reserved and what
+committed, the hash chain of full pages, the pages a window has passed, the state slots) are
+kept by the native host runtime (``csrc/host_engine.cpp``: ``CacheBook``, over the pools of
+``csrc/host_pools.h``).  This class owns the device tensors and is the book's Python face; the
+scheduler's native planner works on the same book.
 """
 from __future__ import annotations
 
-import hashlib
-import struct
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..parts.base import FixedState, LayerCache, PagedKV
-from .pages import CacheError, PagePool, SlotPool
+from .pages import CacheError, PagePool, SlotPool, host
+
+_ALREADY, _NO_SLOT, _UNKNOWN, _UNCOMMITTED, _NOT_ENOUGH = 6, 7, 8, 9, 4
 
 
 @dataclass
 class _Group:
     need: PagedKV
     entries: List[int]                   # schedule entries that own a slice
-    pool: PagePool
+    pool: Optional[PagePool] = None      # a face on the book's pool of this group
     tensor: Optional[torch.Tensor] = None
 
 
-@dataclass
-class _Request:
-    slot: int
-    serial: int = 0                      # unique per admission: tells a re-admitted id from the old one
-    length: int = 0                      # tokens whose keys/values are committed
-    tokens: List[int] = field(default_factory=list)    # committed + reserved token ids
-    tables: List[List[int]] = field(default_factory=list)   # per group: page per block, -1 once given back
-    unknown_at: Optional[int] = None     # index of a token whose id is not known yet (a step launched ahead)
-    hashed_blocks: int = 0
-    last_hash: bytes = b""
-    reused: int = 0
+class _Requests:
+    """The live requests as the book knows them: ``id in requests``, ``len(requests)``, truth."""
+
+    def __init__(self, manager: "CacheManager"):
+        self._m = manager
+
+    def __contains__(self, req_id) -> bool:
+        return bool(self._m._lib.coheryn_book_has(self._m._book, str(req_id).encode()))
+
+    def __len__(self) -> int:
+        return int(self._m._lib.coheryn_book_count(self._m._book))
+
+    def __bool__(self) -> bool:
+        return len(self) > 0
+
+
+def _ints(values: Sequence[int]):
+    n = len(values)
+    return (ctypes.c_int * max(n, 1))(*[int(v) for v in values]), n
 
 
 class CacheManager:
@@ -69,7 +84,7 @@ class CacheManager:
                         g.entries.append(e)
                         break
                 else:
-                    self.groups.append(_Group(need, [e], PagePool(num_pages)))
+                    self.groups.append(_Group(need, [e]))
                     self._entry_group[e] = (len(self.groups) - 1, 0)
             elif isinstance(need, FixedState):
                 self._state[e] = torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype,
@@ -82,11 +97,30 @@ class CacheManager:
             n = g.need
             g.tensor = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
                                    dtype=dtype, device=device)
-        self.slots = SlotPool(max_requests)
-        self.requests: Dict[str, _Request] = {}
-        self._admissions = 0
-        self.prefix_reuse = bool(prefix_reuse) and not self._state and all(
-            g.need.window is None for g in self.groups)
+        reuse = bool(prefix_reuse) and not self._state and all(g.need.window is None for g in self.groups)
+        self._lib = host()
+        windows, n_groups = _ints([g.need.window or 0 for g in self.groups])
+        self._book = self._lib.coheryn_book_new(page_size, num_pages, max_requests, 1 if reuse else 0, n_groups, windows)
+        if not self._book:
+            raise CacheError("the native cache book could not be made")
+        for gi, g in enumerate(self.groups):
+            g.pool = PagePool.borrowed(self._lib.coheryn_book_pool(self._book, gi), num_pages, keep_alive=self)
+        self.slots = SlotPool.borrowed(self._lib.coheryn_book_slots(self._book), max_requests, keep_alive=self)
+        self.requests = _Requests(self)
+
+    def __del__(self):
+        book, self._book = getattr(self, "_book", None), None
+        if book:
+            self._lib.coheryn_book_delete(book)
+
+    @property
+    def book_handle(self):
+        """The native book, for the planner that schedules over it."""
+        return self._book
+
+    @property
+    def prefix_reuse(self) -> bool:
+        return bool(self._lib.coheryn_book_prefix_reuse(self._book))
 
     # ------------------------------------------------------------------ views for the model
     def layer_caches(self) -> List[Optional[LayerCache]]:
@@ -124,158 +158,142 @@ class CacheManager:
         return sum(2 * len(g.entries) * g.need.num_kv_heads * g.need.head_dim * item for g in self.groups)
 
     # ------------------------------------------------------------------ requests
-    def _block_hash(self, prev: bytes, block_tokens: Sequence[int]) -> bytes:
-        return hashlib.sha256(prev + struct.pack(f"<{len(block_tokens)}i", *block_tokens)).digest()
+    def _key(self, req_id) -> bytes:
+        return str(req_id).encode()
+
+    def _number(self, req_id, what: int) -> int:
+        v = int(self._lib.coheryn_book_number(self._book, self._key(req_id), what))
+        if v < 0:
+            raise KeyError(req_id)
+        return v
+
+    def zero_state(self, req_id) -> None:
+        """A request starts from zero state: called for every admission (also those the native
+        planner makes)."""
+        if self._state:
+            slot = self.state_slot(req_id)
+            for st in self._state.values():
+                st[slot].zero_()
 
     def admit(self, req_id: str, prompt: Optional[Sequence[int]] = None) -> Optional[int]:
         """Give the request a state slot (zeroed) and, when a prompt is given and prefix
         reuse is on, map the leading full pages that are already cached.  Returns the
         number of prompt tokens reused, or None when no slot is free."""
-        if req_id in self.requests:
+        reused, slot, serial = ctypes.c_int(0), ctypes.c_int(-1), ctypes.c_longlong(0)
+        if prompt is None:
+            arr, n = None, -1
+        else:
+            arr, n = _ints(prompt)
+        rc = self._lib.coheryn_book_admit(self._book, self._key(req_id), arr, n, ctypes.byref(reused),
+                                          ctypes.byref(slot), ctypes.byref(serial))
+        if rc == _ALREADY:
             raise CacheError(f"request {req_id!r} is already admitted")
-        slot = self.slots.allocate()
-        if slot is None:
+        if rc == _NO_SLOT:
             return None
-        for st in self._state.values():
-            st[slot].zero_()
-        self._admissions += 1
-        r = _Request(slot=slot, serial=self._admissions, tables=[[] for _ in self.groups])
-        self.requests[req_id] = r
-        if prompt is not None and self.prefix_reuse and self.groups and len(prompt) > 1:
-            limit = (len(prompt) - 1) // self.page_size
-            h = b""
-            found: List[List[int]] = []
-            for b in range(limit):
-                h = self._block_hash(h, prompt[b * self.page_size:(b + 1) * self.page_size])
-                pages = [g.pool.lookup(h) for g in self.groups]
-                if any(p is None for p in pages):
-                    break
-                found.append(pages)
-                r.last_hash = h
-            for pages in found:
-                for gi, p in enumerate(pages):
-                    self.groups[gi].pool.retain(p)
-                    r.tables[gi].append(p)
-            n = len(found) * self.page_size
-            r.length = r.reused = n
-            r.tokens = list(prompt[:n])
-            r.hashed_blocks = len(found)
-        return r.reused
+        if rc:
+            raise CacheError(f"cache book: status {rc} while request {req_id!r} is admitted")
+        self.zero_state(req_id)
+        return reused.value
 
     def length(self, req_id: str) -> int:
-        return self.requests[req_id].length
-
-    def _first_needed_block(self, g: _Group, next_position: int) -> int:
-        if g.need.window is None:
-            return 0
-        return max(0, next_position - g.need.window + 1) // self.page_size
+        return self._number(req_id, 0)
 
     def pages_needed(self, req_id: str, n: int) -> List[int]:
-        r = self.requests[req_id]
-        blocks = -(-(r.length + n) // self.page_size)
-        return [max(0, blocks - len(t)) for t in r.tables]
+        out = (ctypes.c_int * max(len(self.groups), 1))()
+        if self._lib.coheryn_book_pages_needed(self._book, self._key(req_id), int(n), out):
+            raise KeyError(req_id)
+        return list(out[:len(self.groups)])
 
     def can_reserve(self, req_id: str, n: int) -> bool:
-        return all(need <= g.pool.available for need, g in zip(self.pages_needed(req_id, n), self.groups))
+        return all(need <= avail for need, avail in zip(self.pages_needed(req_id, n), self.available_pages()))
 
     def reserve(self, req_id: str, tokens: Sequence[int]) -> bool:
         """Pages for ``tokens`` after what the request already holds.  All groups or none:
         returns False and changes nothing when any pool is short."""
-        r = self.requests[req_id]
-        if len(r.tokens) != r.length:
-            raise CacheError(f"request {req_id!r} has a reservation that was not committed")
-        need = self.pages_needed(req_id, len(tokens))
-        if any(n > g.pool.available for n, g in zip(need, self.groups)):
+        arr, n = _ints(tokens)
+        rc = self._lib.coheryn_book_reserve(self._book, self._key(req_id), arr, n)
+        if rc == _NOT_ENOUGH:
             return False
-        for n, g, t in zip(need, self.groups, r.tables):
-            t.extend(g.pool.allocate(n))
-        r.tokens.extend(int(x) for x in tokens)
+        if rc == _UNCOMMITTED:
+            raise CacheError(f"request {req_id!r} has a reservation that was not committed")
+        if rc == _UNKNOWN:
+            raise KeyError(req_id)
+        if rc:
+            raise CacheError(f"cache book: status {rc} while pages are reserved for {req_id!r}")
         return True
 
     def slot_ids(self, req_id: str, group: int) -> List[int]:
         """Cache slot (page * page_size + offset) of every reserved, uncommitted token."""
-        r = self.requests[req_id]
-        ps, table = self.page_size, r.tables[group]
-        return [table[p // ps] * ps + p % ps for p in range(r.length, len(r.tokens))]
+        n = self._number(req_id, 1) - self._number(req_id, 0)
+        out = (ctypes.c_int * max(n, 1))()
+        if self._lib.coheryn_book_slot_ids(self._book, self._key(req_id), group, out, n) < 0:
+            raise KeyError(req_id)
+        return list(out[:n])
 
     def block_table(self, req_id: str, group: int) -> List[int]:
-        return self.requests[req_id].tables[group]
+        cap = -(-max(self._number(req_id, 1), 1) // self.page_size) + 1
+        out = (ctypes.c_int * cap)()
+        n = self._lib.coheryn_book_table(self._book, self._key(req_id), group, out, cap)
+        if n < 0:
+            raise KeyError(req_id)
+        if n > cap:
+            out = (ctypes.c_int * n)()
+            self._lib.coheryn_book_table(self._book, self._key(req_id), group, out, n)
+        return list(out[:n])
 
     def state_slot(self, req_id: str) -> int:
-        return self.requests[req_id].slot
+        return self._number(req_id, 2)
 
     def serial(self, req_id: str) -> int:
         """A number unique to this admission of the request."""
-        return self.requests[req_id].serial
+        return self._number(req_id, 5)
 
     def commit(self, req_id: str) -> None:
         """The reserved tokens' keys and values are written: advance the length, hash the
         pages that became full, give back the pages a window has passed."""
-        r = self.requests[req_id]
-        r.length = len(r.tokens)
-        ps = self.page_size
-        if self.prefix_reuse:
-            known = r.length if r.unknown_at is None else min(r.length, r.unknown_at)   # hashing waits for the id
-            while (r.hashed_blocks + 1) * ps <= known:
-                b = r.hashed_blocks
-                r.last_hash = self._block_hash(r.last_hash, r.tokens[b * ps:(b + 1) * ps])
-                for g, t in zip(self.groups, r.tables):
-                    g.pool.set_hash(t[b], r.last_hash)
-                r.hashed_blocks += 1
-        for g, t in zip(self.groups, r.tables):
-            if g.need.window is None:
-                continue
-            for b in range(min(self._first_needed_block(g, r.length), len(t))):
-                if t[b] >= 0:
-                    g.pool.release(t[b])
-                    t[b] = -1
+        if self._lib.coheryn_book_commit(self._book, self._key(req_id)):
+            raise KeyError(req_id)
 
     def mark_unknown(self, req_id: str, index: int) -> None:
         """Token ``index`` of the request was reserved with a placeholder id: the step that runs
         it was launched before the id was read back.  Pages holding it are not hashed until
         ``patch_token`` supplies the id."""
-        self.requests[req_id].unknown_at = index
+        if self._lib.coheryn_book_mark_unknown(self._book, self._key(req_id), int(index)):
+            raise KeyError(req_id)
 
     def patch_token(self, req_id: str, index: int, token: int) -> None:
-        r = self.requests[req_id]
-        r.tokens[index] = int(token)
-        if r.unknown_at == index:
-            r.unknown_at = None
+        rc = self._lib.coheryn_book_patch_token(self._book, self._key(req_id), int(index), int(token))
+        if rc == _UNKNOWN:
+            raise KeyError(req_id)
+        if rc:
+            raise IndexError(f"request {req_id!r} holds no token {index}")
 
     def rollback(self, req_id: str) -> None:
         """Drop a reservation that was not committed (pages beyond the committed length
         go back)."""
-        r = self.requests[req_id]
-        del r.tokens[r.length:]
-        keep = -(-r.length // self.page_size)
-        for g, t in zip(self.groups, r.tables):
-            for p in t[keep:]:
-                if p >= 0:
-                    g.pool.release(p)
-            del t[keep:]
+        if self._lib.coheryn_book_rollback(self._book, self._key(req_id)):
+            raise KeyError(req_id)
 
     def free(self, req_id: str) -> None:
-        r = self.requests.pop(req_id, None)
-        if r is None:
+        if self._lib.coheryn_book_free(self._book, self._key(req_id)):
             raise CacheError(f"request {req_id!r} is not admitted")
-        for g, t in zip(self.groups, r.tables):
-            for p in t:
-                if p >= 0:
-                    g.pool.release(p)
-        self.slots.release(r.slot)
 
     def available_pages(self) -> List[int]:
-        return [g.pool.available for g in self.groups]
+        out = (ctypes.c_int * max(len(self.groups), 1))()
+        self._lib.coheryn_book_available(self._book, out)
+        return list(out[:len(self.groups)])
 
     def check(self) -> None:
         """No page lost, held twice or freed twice; no slot lost."""
-        for gi, g in enumerate(self.groups):
-            held: Dict[int, int] = {}
-            for r in self.requests.values():
-                for p in r.tables[gi]:
-                    if p >= 0:
-                        held[p] = held.get(p, 0) + 1
-            g.pool.check(held)
-        self.slots.check()
-        if len({r.slot for r in self.requests.values()}) != len(self.requests):
-            raise CacheError("two requests share a state slot")
+        group, page, info = ctypes.c_int(-1), ctypes.c_int(-1), ctypes.c_int(0)
+        rc = self._lib.coheryn_book_check(self._book, ctypes.byref(group), ctypes.byref(page), ctypes.byref(info))
+        if rc == 0:
+            return
+        g, p = group.value, page.value
+        raise CacheError({
+            1: f"group {g}: page {p} has a negative reference count",
+            2: f"group {g}: page {p} is in {info.value} places (free / idle / held)",
+            3: f"group {g}: idle page {p} has no hash",
+            4: f"group {g}: page {p}: the pool counts {info.value} holders, the requests hold it otherwise",
+            5: "slot pool lost or duplicated a slot",
+            6: "two requests share a state slot"}.get(rc, f"cache book: check returned {rc}"))

@@ -47,8 +47,41 @@ def _host():
         lib.coheryn_pool_lookup.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
         lib.coheryn_pool_check.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int),
                                            ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+        P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        IP, S = ctypes.POINTER(ctypes.c_int), ctypes.c_char_p
+        sig = {
+            "coheryn_book_new": (P, [I, I, I, I, I, IP]), "coheryn_book_delete": (None, [P]),
+            "coheryn_book_prefix_reuse": (I, [P]), "coheryn_book_set_prefix_reuse": (None, [P, I]),
+            "coheryn_book_pool": (P, [P, I]), "coheryn_book_slots": (P, [P]), "coheryn_book_count": (I, [P]),
+            "coheryn_book_has": (I, [P, S]), "coheryn_book_admit": (I, [P, S, IP, I, IP, IP, ctypes.POINTER(L)]),
+            "coheryn_book_number": (L, [P, S, I]), "coheryn_book_pages_needed": (I, [P, S, I, IP]),
+            "coheryn_book_reserve": (I, [P, S, IP, I]), "coheryn_book_commit": (I, [P, S]),
+            "coheryn_book_rollback": (I, [P, S]), "coheryn_book_free": (I, [P, S]),
+            "coheryn_book_mark_unknown": (I, [P, S, I]), "coheryn_book_patch_token": (I, [P, S, I, I]),
+            "coheryn_book_table": (I, [P, S, I, IP, I]), "coheryn_book_slot_ids": (I, [P, S, I, IP, I]),
+            "coheryn_book_available": (None, [P, IP]), "coheryn_book_check": (I, [P, IP, IP, IP]),
+            "coheryn_book_layout": (I, [P, I, ctypes.POINTER(S), IP, IP, IP, I, IP, IP, IP, ctypes.POINTER(L)]),
+            "coheryn_planner_new": (P, [P, I, I, I]), "coheryn_planner_delete": (None, [P]),
+            "coheryn_planner_max_seqs": (I, [P]),
+            "coheryn_planner_add": (I, [P, S, IP, I, I, IP, I, I, IP]),
+            "coheryn_planner_adopt": (I, [P, S, IP, I, I, I, IP]), "coheryn_planner_has_work": (I, [P]),
+            "coheryn_planner_schedule": (I, [P]), "coheryn_planner_lookahead": (I, [P, I, IP, IP, IP]),
+            "coheryn_planner_plan": (I, [P, IP, IP, IP, IP, I]), "coheryn_planner_list": (I, [P, I, IP, I]),
+            "coheryn_planner_tokens": (I, [P, I, I, I, IP]), "coheryn_planner_job": (L, [P, I, I]),
+            "coheryn_planner_set_computed": (None, [P, I, I]), "coheryn_planner_advance": (None, [P, I, IP, IP]),
+            "coheryn_planner_append_token": (I, [P, I, I]), "coheryn_planner_finish": (I, [P, I, I]),
+            "coheryn_planner_stats": (None, [P, ctypes.POINTER(L)]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
         _lib = lib
     return _lib
+
+
+def host():
+    """The native host runtime with every entry point declared."""
+    return _host()
 
 
 UNKNOWN_PAGE, NOT_HELD, FREE_PAGE, NOT_ENOUGH, BAD_ARGUMENT = 1, 2, 3, 4, 5
@@ -60,13 +93,21 @@ class PagePool:
             raise ValueError("a pool cannot have a negative number of pages")
         self.num_pages = num_pages
         self._lib = _host()
+        self._owned = True
         self._h = self._lib.coheryn_pool_new(num_pages)
         if not self._h:
             raise CacheError("the native page pool could not be made")
 
+    @classmethod
+    def borrowed(cls, handle, num_pages: int, keep_alive=None) -> "PagePool":
+        """A face on a pool that someone else owns (a group's pool inside the cache book)."""
+        self = cls.__new__(cls)
+        self.num_pages, self._lib, self._h, self._owned, self._keep = num_pages, _host(), handle, False, keep_alive
+        return self
+
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
+        if h and getattr(self, "_owned", False):
             self._lib.coheryn_pool_delete(h)
 
     def _fail(self, code: int, page: int, doing: str):
@@ -167,13 +208,20 @@ class SlotPool:
             raise ValueError("a pool cannot have a negative number of slots")
         self.num_slots = num_slots
         self._lib = _host()
+        self._owned = True
         self._h = self._lib.coheryn_slots_new(num_slots)
         if not self._h:
             raise CacheError("the native slot pool could not be made")
 
+    @classmethod
+    def borrowed(cls, handle, num_slots: int, keep_alive=None) -> "SlotPool":
+        self = cls.__new__(cls)
+        self.num_slots, self._lib, self._h, self._owned, self._keep = num_slots, _host(), handle, False, keep_alive
+        return self
+
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
+        if h and getattr(self, "_owned", False):
             self._lib.coheryn_slots_delete(h)
 
     @property

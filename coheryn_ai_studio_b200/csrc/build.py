@@ -179,7 +179,7 @@ def host_compiler() -> str:
                      "of this engine cannot be built")
 
 
-HOST_SOURCES = ["host_pages.cpp", "host_seeded.cpp"]
+HOST_SOURCES = ["host_pages.cpp", "host_engine.cpp", "host_seeded.cpp"]
 # -ffp-contract=off: the seeded weights must round after every operation, as the CUDA kernel does.
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-ffp-contract=off", "-pthread"]
 
@@ -187,7 +187,7 @@ HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-
 def build_host_library() -> str:
     """The host runtime (page and slot bookkeeping): plain C++, no CUDA, compiled in a second."""
     h = hashlib.sha256()
-    for f in HOST_SOURCES + ["seeded_values.h"]:
+    for f in HOST_SOURCES + ["seeded_values.h", "host_pools.h", "host_sha256.h"]:
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(f.encode())
             h.update(fh.read())

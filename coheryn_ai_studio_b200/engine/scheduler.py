@@ -19,14 +19,19 @@ allocated on demand:
   admitted running request is preempted: its pages are freed and it goes back to the head
   of the waiting queue with its prompt and the tokens generated so far, to be computed
   again later.  Sampling state is kept, so its output is the same as without preemption.
+
+The decisions are taken by the native planner (``csrc/host_engine.cpp``: ``Planner``), which
+works on the cache manager's native book; :class:`Scheduler` is its Python face and keeps the
+user-facing :class:`Request` records (token lists, sampler state, results) in step with it.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Deque, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 from ..cache.manager import CacheManager
+from ..cache.pages import host
 from ..sampling.sampler import RequestSampler, SamplingParams
 
 FINISH_STOP, FINISH_LENGTH, FINISH_CANCELLED = "stop", "length", "cancelled"
@@ -51,6 +56,7 @@ class Request:
     preemptions: int = 0
     sampler: Optional[RequestSampler] = None
     arrival: int = 0
+    handle: int = -1                 # the native planner's number for this request
 
     @property
     def tokens(self) -> List[int]:
@@ -81,130 +87,133 @@ class Scheduled:
     samples: bool        # the step's last token of this request yields a sampled token
 
 
+_REASONS = {1: FINISH_STOP, 2: FINISH_LENGTH, 3: FINISH_CANCELLED}
+_REASON_CODES = {v: k for k, v in _REASONS.items()}
+
+
+def _ints(values):
+    n = len(values)
+    return (ctypes.c_int * max(n, 1))(*[int(v) for v in values]), n
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, context: int, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 2048):
         if max_num_seqs < 1 or max_num_batched_tokens < 1:
             raise ValueError("max_num_seqs and max_num_batched_tokens must be positive")
         self.cache, self.context = cache, context
-        self.max_num_seqs = min(max_num_seqs, cache.max_requests)
         self.max_num_batched_tokens = max_num_batched_tokens
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []
-        self._arrivals = 0
-        self.stats = {"steps": 0, "preemptions": 0, "admitted": 0, "finished": 0,
-                      "scheduled_tokens": 0, "max_batch_width": 0}
+        self._lib = host()
+        self._h = self._lib.coheryn_planner_new(cache.book_handle, int(context), int(max_num_seqs),
+                                                int(max_num_batched_tokens))
+        if not self._h:
+            raise RuntimeError("the native planner could not be made")
+        self.max_num_seqs = int(self._lib.coheryn_planner_max_seqs(self._h))
+        self._jobs: List[Request] = []          # by handle
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.coheryn_planner_delete(h)
+
+    # ------------------------------------------------------------------ views
+    def _list(self, which: int) -> List[Request]:
+        cap = max(len(self._jobs), 1)
+        out = (ctypes.c_int * cap)()
+        n = self._lib.coheryn_planner_list(self._h, which, out, cap)
+        return [self._jobs[out[i]] for i in range(n)]
+
+    @property
+    def running(self) -> List[Request]:
+        """The running requests in order of admission (a copy)."""
+        return self._list(2)
+
+    @property
+    def waiting(self) -> List[Request]:
+        """The waiting requests in queue order (a copy)."""
+        return self._list(3)
+
+    @property
+    def stats(self) -> dict:
+        out = (ctypes.c_longlong * 6)()
+        self._lib.coheryn_planner_stats(self._h, out)
+        return {"steps": out[0], "preemptions": out[1], "admitted": out[2], "finished": out[3],
+                "scheduled_tokens": out[4], "max_batch_width": out[5]}
 
     # ------------------------------------------------------------------ submission
+    def _refuse(self, code: int, req: Request) -> None:
+        ps = self.cache.page_size
+        need = -(-(len(req.prompt) + max(req.max_tokens - 1, 0)) // ps)
+        raise RequestRefused({
+            20: "the prompt holds no token",
+            21: "max_tokens must not be negative",
+            22: f"prompt ({len(req.prompt)}) + max_tokens ({req.max_tokens}) exceeds the context of {self.context}",
+            23: f"the request needs {need} cache pages; the pool has {self.cache.num_pages}",
+            25: f"request id {req.request_id!r} is in use",
+        }.get(code, f"the planner refused the request (status {code})"))
+
     def add(self, req: Request) -> None:
-        if not req.prompt:
-            raise RequestRefused("the prompt holds no token")
-        if req.max_tokens < 0:
-            raise RequestRefused("max_tokens must not be negative")
-        if len(req.prompt) + req.max_tokens > self.context:
-            raise RequestRefused(f"prompt ({len(req.prompt)}) + max_tokens ({req.max_tokens}) "
-                                 f"exceeds the context of {self.context}")
-        need = -(-(len(req.prompt) + max(req.max_tokens - 1, 0)) // self.cache.page_size)
-        if self.cache.groups and need > self.cache.num_pages:
-            raise RequestRefused(f"the request needs {need} cache pages; the pool has "
-                                 f"{self.cache.num_pages}")
-        req.arrival = self._arrivals
-        self._arrivals += 1
+        prompt, n = _ints(req.prompt)
+        stops, n_stops = _ints(req.stop_token_ids)
+        handle = ctypes.c_int(-1)
+        code = self._lib.coheryn_planner_add(self._h, str(req.request_id).encode(), prompt, n, int(req.max_tokens), stops,
+                                             n_stops, 1 if req.params.penalised else 0, ctypes.byref(handle))
+        if code:
+            self._refuse(code, req)
+        self._register(req, handle.value)
         if req.sampler is None:
             req.sampler = RequestSampler(req.params, req.prompt)
-        self.waiting.append(req)
+
+    def _register(self, req: Request, handle: int) -> None:
+        req.handle = handle
+        req.arrival = handle
+        assert handle == len(self._jobs)
+        self._jobs.append(req)
+
+    def adopt_running(self, req: Request, computed: int) -> None:
+        """Take in a request whose pages are already in the cache (``computed`` tokens of its prompt
+        committed under its id): it counts as running from now on.  For callers that fill the cache
+        by other means than running the prompt."""
+        prompt, n = _ints(req.prompt)
+        handle = ctypes.c_int(-1)
+        code = self._lib.coheryn_planner_adopt(self._h, str(req.request_id).encode(), prompt, n, int(req.max_tokens),
+                                               int(computed), ctypes.byref(handle))
+        if code:
+            self._refuse(code, req)
+        self._register(req, handle.value)
+        req.num_computed = computed
+        if req.sampler is None:
+            req.sampler = RequestSampler(req.params, req.prompt)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.coheryn_planner_has_work(self._h))
 
     # ------------------------------------------------------------------ one step's plan
-    def _preempt(self, victim: Request) -> None:
-        """Free a running request's pages and put it back at the head of the queue."""
-        self.running.remove(victim)
-        self.cache.free(victim.request_id)
-        victim.num_computed = 0
-        victim.preemptions += 1
-        self.stats["preemptions"] += 1
-        self.waiting.appendleft(victim)
-
-    def _largest_fit(self, req: Request, n: int, reserved: List[int]) -> int:
-        """The most tokens (at most n) of ``req`` that the free pages can take."""
-        ps = self.cache.page_size
-        for gi, avail in enumerate(self.cache.available_pages()):
-            blocks = len(self.cache.block_table(req.request_id, gi)) + avail - reserved[gi]
-            n = min(n, blocks * ps - self.cache.length(req.request_id))
-        return max(n, 0)
+    def _plan(self, n: int, placeholder: bool = False) -> List[Scheduled]:
+        cap = max(n, 1)
+        jobs, starts, counts, samples = ((ctypes.c_int * cap)() for _ in range(4))
+        self._lib.coheryn_planner_plan(self._h, jobs, starts, counts, samples, cap)
+        out = []
+        for i in range(n):
+            req = self._jobs[jobs[i]]
+            toks = [PLACEHOLDER_TOKEN] * counts[i] if placeholder else req.token_slice(starts[i], starts[i] + counts[i])
+            out.append(Scheduled(req, toks, bool(samples[i])))
+        return out
 
     def schedule(self) -> List[Scheduled]:
-        budget = self.max_num_batched_tokens
-        plan: List[Scheduled] = []
-        reserved = [0] * len(self.cache.groups)      # pages promised to earlier entries of this step
-        preemptions_before = self.stats["preemptions"]
-
-        def fits(req: Request, n: int) -> bool:
-            need = self.cache.pages_needed(req.request_id, n)
-            if not any(need):
-                return True
-            avail = self.cache.available_pages()
-            return all(r + x <= a for r, x, a in zip(reserved, need, avail))
-
-        def take(req: Request, n: int) -> None:
-            for i, x in enumerate(self.cache.pages_needed(req.request_id, n)):
-                reserved[i] += x
-            toks = req.token_slice(req.num_computed, req.num_computed + n)
-            plan.append(Scheduled(req, toks, req.num_computed + n == req.num_tokens))
-
-        # running requests, oldest first
-        preempted_ids = set()
-        for req in sorted(self.running, key=lambda r: r.arrival):
-            if budget == 0 or req.request_id in preempted_ids:      # nothing left, or preempted below
-                continue
-            n = min(req.num_tokens - req.num_computed, budget)
-            while not fits(req, n):
-                planned = {s.request.request_id for s in plan}
-                victims = [r for r in self.running if r is not req and r.request_id not in planned]
-                if not victims:
-                    # Nobody left to preempt: run the part of the portion that fits.
-                    n = self._largest_fit(req, n, reserved)
-                    break
-                victim = max(victims, key=lambda r: r.arrival)
-                preempted_ids.add(victim.request_id)
-                self._preempt(victim)
-            if n == 0:
-                continue
-            take(req, n)
-            budget -= n
-
-        # admissions, first in first out; stop at the first that does not fit; none in a
-        # step that had to preempt (the pool is short)
-        preempted = self.stats["preemptions"] != preemptions_before
-        while not preempted and self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
-            req = self.waiting[0]
-            reused = self.cache.admit(req.request_id, req.tokens)
-            if reused is None:
-                break
-            req.num_computed = reused
-            n = min(req.num_tokens - req.num_computed, budget)
-            if not fits(req, n):
-                # Beside running requests a newcomer waits for room for its whole first
-                # portion; alone it starts with what fits.
-                n = 0 if (self.running or plan) else self._largest_fit(req, n, reserved)
-            if n == 0:
-                self.cache.free(req.request_id)
-                req.num_computed = 0
-                break
-            if req.preemptions == 0:
-                req.reused_prompt_tokens = reused
-            self.waiting.popleft()
-            self.running.append(req)
-            self.stats["admitted"] += 1
-            take(req, n)
-            budget -= n
-
-        self.stats["steps"] += 1
-        self.stats["scheduled_tokens"] += sum(len(s.tokens) for s in plan)
-        self.stats["max_batch_width"] = max(self.stats["max_batch_width"], len(plan))
-        return plan
+        n = self._lib.coheryn_planner_schedule(self._h)
+        cap = max(len(self._jobs), 1)
+        buf = (ctypes.c_int * cap)()
+        for i in range(self._lib.coheryn_planner_list(self._h, 0, buf, cap)):      # preempted in this step
+            req = self._jobs[buf[i]]
+            req.num_computed = 0
+            req.preemptions += 1
+        for i in range(self._lib.coheryn_planner_list(self._h, 1, buf, cap)):      # admitted in this step
+            req = self._jobs[buf[i]]
+            req.num_computed = int(self._lib.coheryn_planner_job(self._h, req.handle, 0))
+            req.reused_prompt_tokens = int(self._lib.coheryn_planner_job(self._h, req.handle, 1))
+            self.cache.zero_state(req.request_id)
+        return self._plan(n)
 
     def lookahead(self, plan: Sequence[Scheduled]) -> Optional[List[Scheduled]]:
         """The plan of the step AFTER ``plan`` when that can be said before ``plan``'s tokens
@@ -212,31 +221,20 @@ class Scheduler:
         end by length or context with the token ``plan`` yields, and the pages are there.  The
         entries carry a placeholder id (the real one is still on the device).  Call after
         ``advance(plan)``.  None when the ordinary ``schedule`` has to decide."""
-        if self.waiting or not plan or len(plan) != len(self.running) or len(plan) > self.max_num_batched_tokens:
+        if not plan:
             return None
-        reserved = [0] * len(self.cache.groups)
-        avail = self.cache.available_pages()
-        out: List[Scheduled] = []
-        for s in plan:
-            req = s.request
-            if req.finished or not s.samples or len(s.tokens) != 1 or req not in self.running:
-                return None
-            if len(req.output) + 2 > req.max_tokens or req.num_tokens + 2 > self.context:
-                return None
-            if req.sampler is None or req.sampler.params.penalised:
-                return None     # the penalties of the next step need this step's id
-            for i, x in enumerate(self.cache.pages_needed(req.request_id, 1)):
-                reserved[i] += x
-            out.append(Scheduled(req, [PLACEHOLDER_TOKEN], True))
-        if any(r > a for r, a in zip(reserved, avail)):
+        jobs, n = _ints([s.request.handle for s in plan])
+        counts, _ = _ints([len(s.tokens) for s in plan])
+        samples, _ = _ints([1 if s.samples else 0 for s in plan])
+        if not self._lib.coheryn_planner_lookahead(self._h, n, jobs, counts, samples):
             return None
-        self.stats["steps"] += 1
-        self.stats["scheduled_tokens"] += len(out)
-        self.stats["max_batch_width"] = max(self.stats["max_batch_width"], len(out))
-        return out
+        return self._plan(n, placeholder=True)
 
     # ------------------------------------------------------------------ after the step
     def advance(self, plan: Sequence[Scheduled]) -> None:
+        jobs, n = _ints([s.request.handle for s in plan])
+        counts, _ = _ints([len(s.tokens) for s in plan])
+        self._lib.coheryn_planner_advance(self._h, n, jobs, counts)
         for s in plan:
             s.request.num_computed += len(s.tokens)
 
@@ -244,26 +242,17 @@ class Scheduler:
         """Record a sampled token; returns True when the request is finished.  The last
         sampled token is not run through the model (generation.rs:386-388)."""
         req.output.append(token)
-        if token in req.stop_token_ids:
-            req.finish_reason = FINISH_STOP        # the stop token stays in the ids
-        elif len(req.output) >= req.max_tokens:
-            req.finish_reason = FINISH_LENGTH
-        if req.finished:
-            self.finish(req, req.finish_reason)
+        reason = self._lib.coheryn_planner_append_token(self._h, req.handle, int(token))
+        if reason > 0:
+            req.finish_reason = _REASONS[reason]
         return req.finished
 
     def finish(self, req: Request, reason: str) -> None:
         req.finish_reason = reason
-        if req in self.running:
-            self.running.remove(req)
-            self.cache.free(req.request_id)
-            self.stats["finished"] += 1
-        elif req in self.waiting:
-            self.waiting.remove(req)
-            self.stats["finished"] += 1
+        self._lib.coheryn_planner_finish(self._h, req.handle, _REASON_CODES.get(reason, 3))
 
     def abort(self, request_id: str) -> bool:
-        for req in list(self.running) + list(self.waiting):
+        for req in self.running + self.waiting:
             if req.request_id == request_id:
                 self.finish(req, FINISH_CANCELLED)
                 return True

@@ -16,8 +16,9 @@ static index buffers, and a step then costs one host-to-device copy and one grap
 """
 from __future__ import annotations
 
+import ctypes
 import os
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -55,6 +56,7 @@ class _Layout:
     tables: List[List[List[int]]]     # per group, per request: pages
     slots: List[np.ndarray]           # per group: [T]
     q_lens: List[int]
+    serials: List[int] = field(default_factory=list)     # per request: the number of its admission
 
 
 class _DecodeGraph:
@@ -244,45 +246,41 @@ class StepRunner:
             done.append(e.request_id)
 
     def _layout(self, entries: Sequence[StepEntry]) -> _Layout:
+        """The step's arrays from the native book (positions, request of each token, slots, offsets,
+        lengths, state slots, admission serials) and the entries (ids, wanted rows)."""
         cache = self.cache
         B = len(entries)
         q_lens = [len(e.tokens) for e in entries]
-        starts = [cache.length(e.request_id) for e in entries]
         T = sum(q_lens)
-        if T == B:       # one token each (decoding): no per-request arrays
-            ar = np.arange(B + 1, dtype=np.int32)
-            st = np.asarray(starts, np.int32)
+        groups = len(cache.groups)
+        keys = (ctypes.c_char_p * B)(*[str(e.request_id).encode() for e in entries])
+        pos = np.empty(T, np.int32); req = np.empty(T, np.int32)
+        slots = np.empty(max(groups, 1) * T, np.int32)
+        cu = np.empty(B + 1, np.int32); kv_lens = np.empty(B, np.int32); state_slots = np.empty(B, np.int32)
+        serials = np.empty(B, np.int64)
+        as_int = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+        got = cache._lib.coheryn_book_layout(cache.book_handle, B, keys, as_int(pos), as_int(req), as_int(slots), T, as_int(cu),
+                                             as_int(kv_lens), as_int(state_slots),
+                                             serials.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong)))
+        if got != T:
+            raise RuntimeError(f"the cache book laid out {got} tokens where the step brings {T}")
+        if T == B:
+            ids = np.asarray([e.tokens[0] for e in entries], np.int32)
             rows = [b for b, e in enumerate(entries) for _ in e.want]
-            groups = range(len(cache.groups))
-            return _Layout(
-                B=B, T=T, ids=np.asarray([e.tokens[0] for e in entries], np.int32), pos=st, req=ar[:B], cu=ar,
-                kv_lens=st + 1, state_slots=np.asarray([cache.state_slot(e.request_id) for e in entries], np.int32),
-                rows=np.asarray(rows, np.int32),
-                tables=[[cache.block_table(e.request_id, g) for e in entries] for g in groups],
-                slots=[np.asarray([cache.slot_ids(e.request_id, g)[0] for e in entries], np.int32) for g in groups],
-                q_lens=q_lens)
-        ids = np.empty(T, np.int32); pos = np.empty(T, np.int32); req = np.empty(T, np.int32)
-        cu = np.zeros(B + 1, np.int32)
-        rows: List[int] = []
-        o = 0
-        for b, e in enumerate(entries):
-            n = q_lens[b]
-            ids[o:o + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos[o:o + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
-            req[o:o + n] = b
-            rows.extend(o + int(w) for w in e.want)
-            o += n
-            cu[b + 1] = o
-        groups = range(len(cache.groups))
-        return _Layout(
-            B=B, T=T, ids=ids, pos=pos, req=req, cu=cu,
-            kv_lens=np.asarray([s + n for s, n in zip(starts, q_lens)], np.int32),
-            state_slots=np.asarray([cache.state_slot(e.request_id) for e in entries], np.int32),
+        else:
+            ids = np.empty(T, np.int32)
+            rows = []
+            for b, e in enumerate(entries):
+                o = int(cu[b])
+                ids[o:o + q_lens[b]] = np.asarray(e.tokens, dtype=np.int32)
+                rows.extend(o + int(w) for w in e.want)
+        lay = _Layout(
+            B=B, T=T, ids=ids, pos=pos, req=req, cu=cu, kv_lens=kv_lens, state_slots=state_slots,
             rows=np.asarray(rows, np.int32),
-            tables=[[cache.block_table(e.request_id, g) for e in entries] for g in groups],
-            slots=[np.concatenate([np.asarray(cache.slot_ids(e.request_id, g), np.int32) for e in entries])
-                   for g in groups],
-            q_lens=q_lens)
+            tables=[[cache.block_table(e.request_id, g) for e in entries] for g in range(groups)],
+            slots=[slots[g * T:(g + 1) * T] for g in range(groups)], q_lens=q_lens)
+        lay.serials = serials.tolist()
+        return lay
 
     def _context(self, lay: _Layout):
         tables, host_tables = [], []
@@ -357,7 +355,7 @@ class StepRunner:
                 g = self._graphs.get(width)
                 if g is None:
                     g = self._graphs[width] = _DecodeGraph(self, width)
-                g.fill(lay, [self.cache.serial(e.request_id) for e in entries])
+                g.fill(lay, lay.serials)
                 self.h2d_bytes += g.nbytes
                 if ids_device is not None:
                     g.d["ids"][:lay.B].copy_(ids_device, non_blocking=True)

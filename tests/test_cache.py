@@ -179,3 +179,36 @@ def test_the_pools_are_the_native_ones():
         pool.release(99)
     with pytest.raises(CacheError):
         pool.check({a[1]: 2, a[2]: 1, got[0]: 1, got[1]: 1})
+
+
+def test_native_step_layout_equals_the_tables():
+    """The native book lays a step out (position, request and slot of every reserved token, offsets,
+    lengths, state slots, serials); the same numbers follow from the block tables."""
+    import ctypes
+    import numpy as np
+    m = manager([PagedKV(1, 4, None)], pages=16, page=4)
+    m.admit("a"); m.admit("b"); m.admit("c")
+    assert m.reserve("a", list(range(9))); m.commit("a")
+    assert m.reserve("a", [1]) and m.reserve("b", list(range(6))) and m.reserve("c", [7, 8])
+    ids = ["b", "a", "c"]
+    counts = [6, 1, 2]
+    T = sum(counts)
+    keys = (ctypes.c_char_p * 3)(*[i.encode() for i in ids])
+    pos, req, slots = np.empty(T, np.int32), np.empty(T, np.int32), np.empty(T, np.int32)
+    cu, kv, st, ser = np.empty(4, np.int32), np.empty(3, np.int32), np.empty(3, np.int32), np.empty(3, np.int64)
+    ip = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+    got = m._lib.coheryn_book_layout(m.book_handle, 3, keys, ip(pos), ip(req), ip(slots), T, ip(cu), ip(kv), ip(st),
+                                     ser.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong)))
+    assert got == T and cu.tolist() == [0, 6, 7, 9] and kv.tolist() == [6, 10, 2]
+    assert pos.tolist() == [0, 1, 2, 3, 4, 5, 9, 0, 1] and req.tolist() == [0] * 6 + [1] + [2, 2]
+    want = []
+    for rid in ids:
+        want += m.slot_ids(rid, 0)
+    assert slots.tolist() == want
+    for i, rid in enumerate(ids):
+        table = m.block_table(rid, 0)
+        for t in range(cu[i], cu[i + 1]):
+            assert slots[t] == table[pos[t] // 4] * 4 + pos[t] % 4
+    assert st.tolist() == [m.state_slot(r) for r in ids] and ser.tolist() == [m.serial(r) for r in ids]
+    assert m._lib.coheryn_book_layout(m.book_handle, 3, keys, ip(pos), ip(req), ip(slots), T - 1, ip(cu), ip(kv), ip(st),
+                                      ser.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong))) == -1     # buffer too small

@@ -141,3 +141,33 @@ def test_prefix_reuse_shortens_the_prompt_work():
     sched.add(b)
     plan = run_step(cache, sched)
     assert len(plan[0].tokens) == 1 and b.reused_prompt_tokens == 12
+
+
+def test_a_request_whose_pages_are_already_there_is_adopted():
+    """``adopt_running``: the caller filled the cache under the request's id; the planner takes the
+    request in as running and decodes it from where the cache ends."""
+    cache, sched = make(pages=8, page=4)
+    prompt = list(range(1, 10))
+    assert cache.admit("x") is not None and cache.reserve("x", prompt[:-1])
+    cache.commit("x")
+    r = Request("x", prompt, 3)
+    sched.adopt_running(r, len(prompt) - 1)
+    assert sched.running == [r] and not sched.waiting and r.num_computed == 8
+    plan = sched.schedule()
+    assert len(plan) == 1 and plan[0].tokens == [9] and plan[0].samples
+    with pytest.raises(RequestRefused):
+        sched.adopt_running(Request("x", prompt, 3), 8)                  # the id is in use
+
+
+def test_the_planner_forgets_the_tokens_of_finished_requests():
+    cache, sched = make(pages=16, page=4)
+    reqs = [Request(f"r{i}", [1 + i] * 5, 2) for i in range(3)]
+    for r in reqs:
+        sched.add(r)
+    while sched.has_work():
+        run_step(cache, sched)
+    assert all(r.finish_reason == "length" and len(r.output) == 2 for r in reqs)
+    assert sched.stats["finished"] == 3 and cache.available_pages() == [16] and not cache.requests
+    for r in reqs:        # the native side keeps the numbers of a finished job, not its token lists
+        assert sched._lib.coheryn_planner_job(sched._h, r.handle, 4) == 0
+        assert sched._lib.coheryn_planner_job(sched._h, r.handle, 3) == 2
