@@ -60,6 +60,7 @@ def _host():
             "coheryn_book_mark_unknown": (I, [P, S, I]), "coheryn_book_patch_token": (I, [P, S, I, I]),
             "coheryn_book_table": (I, [P, S, I, IP, I]), "coheryn_book_slot_ids": (I, [P, S, I, IP, I]),
             "coheryn_book_available": (None, [P, IP]), "coheryn_book_check": (I, [P, IP, IP, IP]),
+            "coheryn_book_tables": (I, [P, I, ctypes.POINTER(S), I, IP, I, IP]),
             "coheryn_book_layout": (I, [P, I, ctypes.POINTER(S), IP, IP, IP, I, IP, IP, IP, ctypes.POINTER(L)]),
             "coheryn_planner_new": (P, [P, I, I, I]), "coheryn_planner_delete": (None, [P]),
             "coheryn_planner_max_seqs": (I, [P]),

@@ -612,6 +612,27 @@ HOST_EXPORT int coheryn_book_layout(void* h, int n, const char* const* ids, int*
   return T;
 }
 
+// The block tables of n requests for one group: row i of out (width entries, -1 beyond the table)
+// and lens[i]; returns the longest table's length (nothing is written when it exceeds width), or -1.
+HOST_EXPORT int coheryn_book_tables(void* h, int n, const char* const* ids, int group, int* out, int width, int* lens) {
+  CacheBook* b = static_cast<CacheBook*>(h);
+  int longest = 0;
+  std::vector<const Held*> rs(n);
+  for (int i = 0; i < n; ++i) {
+    rs[i] = b->find(str(ids[i]));
+    if (!rs[i] || group < 0 || group >= (int)rs[i]->tables.size()) return -1;
+    longest = std::max(longest, (int)rs[i]->tables[group].size());
+  }
+  if (longest > width) return longest;
+  for (int i = 0; i < n; ++i) {
+    const auto& t = rs[i]->tables[group];
+    int* row = out + (size_t)i * width;
+    for (int k = 0; k < width; ++k) row[k] = k < (int)t.size() ? t[k] : -1;
+    lens[i] = (int)t.size();
+  }
+  return longest;
+}
+
 // ------------------------------------------------------------------------- C interface: planner
 HOST_EXPORT void* coheryn_planner_new(void* book, int context, int max_num_seqs, int max_num_batched_tokens) {
   if (!book || max_num_seqs < 1 || max_num_batched_tokens < 1) return nullptr;

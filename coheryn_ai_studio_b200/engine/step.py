@@ -53,7 +53,7 @@ class _Layout:
     kv_lens: np.ndarray
     state_slots: np.ndarray
     rows: np.ndarray
-    tables: List[List[List[int]]]     # per group, per request: pages
+    tables: List[List[np.ndarray]]    # per group, per request: pages
     slots: List[np.ndarray]           # per group: [T]
     q_lens: List[int]
     serials: List[int] = field(default_factory=list)     # per request: the number of its admission
@@ -277,10 +277,25 @@ class StepRunner:
         lay = _Layout(
             B=B, T=T, ids=ids, pos=pos, req=req, cu=cu, kv_lens=kv_lens, state_slots=state_slots,
             rows=np.asarray(rows, np.int32),
-            tables=[[cache.block_table(e.request_id, g) for e in entries] for g in range(groups)],
+            tables=[self._tables(keys, B, g, int(kv_lens.max())) for g in range(groups)],
             slots=[slots[g * T:(g + 1) * T] for g in range(groups)], q_lens=q_lens)
         lay.serials = serials.tolist()
         return lay
+
+    def _tables(self, keys, B: int, group: int, max_len: int) -> List[np.ndarray]:
+        """The block tables of the step's requests for one group, one native call: per request a row
+        of page ids (-1 where a window has given the page back)."""
+        cache = self.cache
+        width = max(1, -(-max_len // cache.page_size))
+        as_int = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+        while True:
+            out, lens = np.empty((B, width), np.int32), np.empty(B, np.int32)
+            longest = cache._lib.coheryn_book_tables(cache.book_handle, B, keys, group, as_int(out), width, as_int(lens))
+            if longest < 0:
+                raise RuntimeError("the cache book does not know a request of the step")
+            if longest <= width:
+                return [out[b, :lens[b]] for b in range(B)]
+            width = longest
 
     def _context(self, lay: _Layout):
         tables, host_tables = [], []

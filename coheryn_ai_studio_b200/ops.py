@@ -697,8 +697,19 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
 ATTN_OPROJ_M = int(os.environ.get("COHERYN_ATTN_OPROJ_M", "16"))
 
 
+# ... and only while the merging stays cheap: every CTA of the merged kernel (one per head and tile of
+# 128 output features) reads the splits of its head for all requests again, so the bytes read grow with
+# width / 128 x heads x requests x splits.  Beyond this many bytes the splits are merged once, by the
+# kernel of their own.
+ATTN_OPROJ_MERGE_BYTES = int(os.environ.get("COHERYN_ATTN_OPROJ_BYTES", str(32 << 20)))
+
+
 def attention_oproj_ok(q: torch.Tensor, w_o: torch.Tensor, step, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
-    return (q.dtype == torch.bfloat16 and w_o.dtype == torch.bfloat16 and step.max_q_len == 1
+    if step.max_kv_len is None or step.max_q_len != 1:
+        return False
+    tiles = -(-w_o.shape[0] // 128)
+    merge_bytes = tiles * num_heads * step.num_requests * (-(-step.max_kv_len // 128)) * head_dim * 4
+    return (merge_bytes <= ATTN_OPROJ_MERGE_BYTES and q.dtype == torch.bfloat16 and w_o.dtype == torch.bfloat16 and step.max_q_len == 1
             and 0 < step.num_requests <= min(ATTN_OPROJ_M, 16) and q.shape[0] == step.num_requests
             and num_heads // num_kv_heads <= 16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
             and step.max_kv_len is not None and (step.max_kv_len + 127) // 128 + 1 <= 512
