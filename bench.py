@@ -196,6 +196,53 @@ def other_workload(args) -> int:
     return 0
 
 
+def timeline(args, make_engine, StepEntry, ops, torch) -> int:
+    """Where a decode step's time goes, kernel by kernel, measured inside graph-replayed steps (the
+    kernels overlap through programmatic dependent launch, so a kernel's own duration says little):
+    ``advance`` is how far a kernel's end lies behind the end of everything before it; the advances
+    add up to the step."""
+    import collections
+    from torch.profiler import ProfilerActivity, profile
+    eng, lens, rng = make_engine(args.batch)
+    ids = [f"t{i}" for i in range(args.batch)]
+    for rid, n in zip(ids, lens):
+        assert eng.cache.admit(rid) is not None and eng.cache.reserve(rid, [0] * n)
+        eng.cache.commit(rid)
+    out = torch.empty(args.batch, dtype=torch.int32, device="cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+
+    def one():
+        logits = eng.runner.step([StepEntry(rid, [5], [0]) for rid in ids])
+        ops.argmax(logits, out, status)
+    for _ in range(max(args.warmup, 4)):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(4):
+            one()
+        torch.cuda.synchronize()
+    events = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+              and "emcpy" not in e.name and "emset" not in e.name]
+    events.sort(key=lambda e: e.time_range.start)
+    first = [i for i, e in enumerate(events) if "embed_gather" in e.name][-1]
+    step = events[first:]
+    t0 = prev_end = step[0].time_range.start
+    rows = collections.OrderedDict()
+    for e in step:
+        start, end = e.time_range.start, e.time_range.end
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
+        r = rows.setdefault(name, [0, 0.0, 0.0])
+        r[0] += 1
+        r[1] += end - start
+        r[2] += max(0.0, end - prev_end)
+        prev_end = max(prev_end, end)
+    print(f"decode step, batch {args.batch}, {args.layers} layers: {prev_end - t0:.1f} us from the first kernel's start to the last one's end")
+    print(f"{'launches':>8} {'duration us':>12} {'advance us':>11} {'step share':>10}  kernel")
+    for name, (n, dur, adv) in rows.items():
+        print(f"{n:8d} {dur / n:12.2f} {adv / n:11.2f} {adv / (prev_end - t0):10.3f}  {name}")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -212,6 +259,9 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b"],
                     help="decode: the contract's line (default); the others: see the header")
+    ap.add_argument("--timeline", action="store_true",
+                    help="instead of the benchmark: the kernels of one graph-replayed decode step with their times "
+                         "inside the step (CUPTI through torch.profiler), one text line per kernel")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -368,6 +418,10 @@ def main() -> int:
         torch.cuda.empty_cache()
         return {"value": tokens / (best / 1e3), "tokens": tokens, "ms": best, "frac": flops / (best / 1e3) / peak,
                 "tflops": flops / (best / 1e3) / 1e12}
+
+    if args.timeline:
+        sampler.stop()
+        return timeline(args, make_engine, StepEntry, ops, torch)
 
     main_run = decode_device_timed(args.batch, args.steps, args.warmup)
     clocks = ClockSampler.summary(sampler.window(*main_run["window"]))
