@@ -26,3 +26,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """How close the bfloat16 rows of this session came to their bound (1.0 would fail)."""
+    try:
+        from replay import LARGEST_EXCESS
+    except Exception:
+        return
+    if LARGEST_EXCESS["rows"]:
+        terminalreporter.write_line(f"bfloat16 rows compared with the plain implementation: {LARGEST_EXCESS['rows']}, "
+                                    f"largest distance {LARGEST_EXCESS['value']:.2f} of the bound")

@@ -41,12 +41,19 @@ def tol_bf16_rms(ref_row: np.ndarray, rounded_row: np.ndarray) -> float:
     return BF16_RMS_FACTOR * max(0.25 * BF16_MIN_SIGMAS * sigma, float(np.sqrt(np.mean(d * d))))
 
 
-def bf16_excess(row: np.ndarray, ref_row: np.ndarray, rounded_row: np.ndarray) -> float:
+LARGEST_EXCESS = {"value": 0.0, "rows": 0}      # over a test session, reported by conftest.py
+
+
+def bf16_excess(row: np.ndarray, ref_row: np.ndarray, rounded_row: np.ndarray, record: bool = False) -> float:
     """How far a bfloat16 row is from the plain row, in units of what is allowed (<= 1 passes): the
     larger of rms error / rms bound and largest error / bound on the largest."""
     d = (row - ref_row).astype(np.float64)
-    return max(float(np.sqrt(np.mean(d * d))) / tol_bf16_rms(ref_row, rounded_row),
-               float(np.abs(d).max()) / tol_bf16(ref_row, rounded_row))
+    excess = max(float(np.sqrt(np.mean(d * d))) / tol_bf16_rms(ref_row, rounded_row),
+                 float(np.abs(d).max()) / tol_bf16(ref_row, rounded_row))
+    if record:                                   # rows of the engine (not the deliberately wrong rows of the self-checks)
+        LARGEST_EXCESS["value"] = max(LARGEST_EXCESS["value"], excess)
+        LARGEST_EXCESS["rows"] += 1
+    return excess
 
 
 def tol_bf16_spread(row: np.ndarray, sigmas: float = 0.04) -> float:
@@ -178,7 +185,7 @@ def compare(replay: Replay, model_dir: str, sequences: Dict[str, List[int]], lab
             assert int(row.argmax()) == int(ref.argmax()) or np.sort(ref)[-1] - np.sort(ref)[-2] < 2 * TOL_F32, \
                 f"{label} {rid}@{pos}: argmax differs"
         else:
-            excess = bf16_excess(row, ref, plain_logits(model_dir, sequences[rid], rounded=True)[pos])
+            excess = bf16_excess(row, ref, plain_logits(model_dir, sequences[rid], rounded=True)[pos], record=True)
             assert excess <= 1.0, f"{label} {rid}@{pos}: {excess:.2f} of the bfloat16 bound (largest |d| = {diff:.3e})"
     return worst
 

@@ -104,7 +104,7 @@ def test_layer_sizes_against_the_plain_implementation(size):
             for i, pos in enumerate(rows):
                 got, want = r.rows[(rid, pos)], ref[rid][i]
                 diff = float(np.abs(got - want).max())
-                excess = diff / TOL_F32 if dtype == "float32" else bf16_excess(got, want, twin[rid][i])
+                excess = diff / TOL_F32 if dtype == "float32" else bf16_excess(got, want, twin[rid][i], record=True)
                 worst = max(worst, excess)
                 largest = max(largest, diff if dtype == "float32" else diff / float(np.std(want)))
                 if dtype == "float32":

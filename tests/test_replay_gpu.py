@@ -205,7 +205,7 @@ def test_trace_run_program(dtype, folders, tmp_path):
     for rows, ref, rnd in ((got[0], ref_a[[0, 29]], rnd_a[[0, 29]]), (got[1], ref_a[[31]], rnd_a[[31]]),
                            (got[2], ref_b[[18, 19]], rnd_b[[18, 19]]), (got[3], ref_a[[36]], rnd_a[[36]])):
         for row, want, twin in zip(rows, ref, rnd):
-            assert np.abs(row - want).max() <= 1e-4 if dtype == "float32" else bf16_excess(row, want, twin) <= 1.0
+            assert np.abs(row - want).max() <= 1e-4 if dtype == "float32" else bf16_excess(row, want, twin, record=True) <= 1.0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
