@@ -240,6 +240,12 @@ def timeline(args, make_engine, StepEntry, ops, torch) -> int:
     print(f"{'launches':>8} {'duration us':>12} {'advance us':>11} {'step share':>10}  kernel")
     for name, (n, dur, adv) in rows.items():
         print(f"{n:8d} {dur / n:12.2f} {adv / n:11.2f} {adv / (prev_end - t0):10.3f}  {name}")
+    if args.timeline_raw:
+        # every kernel of the step with its own start and end, relative to the step's start
+        print(f"{'start us':>9} {'end us':>9}  kernel")
+        for e in step:
+            name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
+            print(f"{e.time_range.start - t0:9.1f} {e.time_range.end - t0:9.1f}  {name}")
     return 0
 
 
@@ -259,6 +265,7 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b"],
                     help="decode: the contract's line (default); the others: see the header")
+    ap.add_argument("--timeline-raw", action="store_true", help="with --timeline: also every kernel's start and end")
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the benchmark: the kernels of one graph-replayed decode step with their times "
                          "inside the step (CUPTI through torch.profiler), one text line per kernel")

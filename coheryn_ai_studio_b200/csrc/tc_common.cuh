@@ -4,6 +4,8 @@
 #pragma once
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -174,29 +176,65 @@ EncodeTiled encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps are kept: a map is a function of the address, the extents, the strides and
+// the box alone, the same few dozen (weights, the step's activation buffers) come back every step,
+// and encoding one costs the host about as much as launching a kernel.  Direct-mapped, 512 entries.
+struct MapKey {
+  const void* base;
+  unsigned long long dims[3], strides[2];
+  unsigned box[3];
+  int rank;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rank == o.rank && dims[0] == o.dims[0] && dims[1] == o.dims[1] && dims[2] == o.dims[2] &&
+           strides[0] == o.strides[0] && strides[1] == o.strides[1] && box[0] == o.box[0] && box[1] == o.box[1] &&
+           box[2] == o.box[2];
+  }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+
+bool cached_map(CUtensorMap* map, const MapKey& key) {
+  static MapSlot slots[512];
+  static std::mutex lock;
+  unsigned long long h = (unsigned long long)(uintptr_t)key.base * 0x9E3779B97F4A7C15ull;
+  h ^= (key.dims[0] + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+  h ^= (key.dims[1] * 31 + key.dims[2] * 131 + key.strides[0] * 17 + key.strides[1] * 257 + key.box[1] * 7 + key.box[0] + key.box[2] * 3 +
+        0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+  std::lock_guard<std::mutex> guard(lock);
+  MapSlot& slot = slots[(h >> 20) & 511];
+  if (slot.used && slot.key == key) { *map = slot.map; return true; }
+  EncodeTiled fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {key.dims[0], key.dims[1], key.dims[2]};
+  cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
+  cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
+  cuuint32_t elem[3] = {1, 1, 1};
+  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)key.rank, const_cast<void*>(key.base), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  slot.key = key; slot.map = *map; slot.used = true;
+  return true;
+}
+
 // A [rows, K] bfloat16 matrix with row stride ld (elements) as a 2-D tensor map whose box is
 // box_rows x 64 elements, 128-byte swizzled, zero filled out of bounds.
 bool make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
-  EncodeTiled fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  MapKey key = {};
+  key.base = base; key.rank = 2;
+  key.dims[0] = (unsigned long long)K; key.dims[1] = (unsigned long long)rows;
+  key.strides[0] = (unsigned long long)ld * 2;
+  key.box[0] = (unsigned)BK; key.box[1] = (unsigned)box_rows;
+  return cached_map(map, key);
 }
 
 // A bfloat16 tensor of rank 2 or 3 (dims and byte strides innermost first, strides[0] being
 // that of dims[1]) whose box is `box`, 128-byte swizzled, zero filled out of bounds.
 bool make_map_nd(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
                  const cuuint32_t* box) {
-  EncodeTiled fn = encode_fn();
-  if (!fn) return false;
-  cuuint32_t elem[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  MapKey key = {};
+  key.base = base; key.rank = rank;
+  for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+  return cached_map(map, key);
 }
 }  // namespace

@@ -6,6 +6,7 @@ or without the compiled library they raise.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 from typing import Optional
 
@@ -40,6 +41,7 @@ def core():
         lib.coheryn_last_error.restype = ctypes.c_char_p
         lib.coheryn_launch_count.restype = ctypes.c_ulonglong
         lib.coheryn_argmax_scratch_slots.restype = ctypes.c_long
+        lib.coheryn_gemm_tc_workspace_floats.restype = ctypes.c_long
         _core = lib
     return _core
 
@@ -68,7 +70,17 @@ def _ptr(t: Optional[torch.Tensor]):
     return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
 
 
+try:
+    _raw_stream, _current_device = torch._C._cuda_getCurrentRawStream, torch._C._cuda_getDevice
+except AttributeError:          # another torch: the documented, slower way
+    _raw_stream = _current_device = None
+
+
 def _stream():
+    """The current CUDA stream of the current device as a pointer (asked on every launch: a few
+    microseconds through ``torch.cuda.current_stream``, a tenth of one through the raw call)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(_current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -402,10 +414,10 @@ _tc_status = {}
 
 def tc_status(device) -> torch.Tensor:
     """Device word that the tensor-core GEMM sets when one of its bounded waits runs out."""
-    key = str(device)
-    if key not in _tc_status:
-        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tc_status[key]
+    t = _tc_status.get(device)
+    if t is None:
+        t = _tc_status[device] = _tc_status.setdefault(str(torch.device(device)), torch.zeros(1, dtype=torch.int32, device=device))
+    return t
 
 
 STATUS_MESSAGES = {1: "a token id was outside the embedding table", 2: "non-finite logits"}
@@ -444,8 +456,7 @@ def gemm_bf16_tc(x, w, bias, out, gated: int = 0) -> None:
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == K
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N // 2 if gated else N)
     lib = core()
-    lib.coheryn_gemm_tc_workspace_floats.restype = ctypes.c_long
-    floats = int(lib.coheryn_gemm_tc_workspace_floats(c_int(M), c_int(N), c_int(K)))   # > 0: K is split
+    floats = _tc_workspace_floats(M, N, K)   # > 0: K is split
     workspace = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
     _check(lib, lib.coheryn_gemm_bf16_tc(
         _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
@@ -456,13 +467,12 @@ def gemm_bf16_tc(x, w, bias, out, gated: int = 0) -> None:
 def set_gemm_pairs(on: bool) -> None:
     """Whether ``gemm_bf16_tc`` hands suitable shapes to the kernel of CTA pairs (default: yes)."""
     core().coheryn_gemm_tc_set_pairs(c_int(1 if on else 0))
+    _tc_workspace_floats.cache_clear()      # the pairs take shapes that would otherwise split K
 
 
 def gemm_tc_splits(M: int, N: int, K: int) -> int:
     """K splits that ``gemm_bf16_tc`` uses for this shape (1: none; a shape run by CTA pairs: 1)."""
-    lib = core()
-    lib.coheryn_gemm_tc_workspace_floats.restype = ctypes.c_long
-    return max(1, int(lib.coheryn_gemm_tc_workspace_floats(c_int(M), c_int(N), c_int(K))) // (M * N))
+    return max(1, _tc_workspace_floats(M, N, K) // (M * N))
 
 
 def gemm_bf16_tc_pair(x, w, bias, out, gated: int = 0) -> None:
@@ -497,9 +507,20 @@ def _few_workspace(device, floats: int) -> torch.Tensor:
     return ws
 
 
+@functools.lru_cache(maxsize=None)
 def few_splits(N: int, K: int) -> int:
     """Into how many slices of K the few-rows product cuts this weight shape (1: none)."""
     return int(core().coheryn_gemm_tc_few_splits(c_int(N), c_int(K)))
+
+
+@functools.lru_cache(maxsize=None)
+def _tc_workspace_floats(M: int, N: int, K: int) -> int:
+    return int(core().coheryn_gemm_tc_workspace_floats(c_int(M), c_int(N), c_int(K)))
+
+
+@functools.lru_cache(maxsize=None)
+def _few_workspace_floats(M: int, N: int, K: int) -> int:
+    return int(core().coheryn_gemm_tc_few_workspace_floats(c_int(M), c_int(N), c_int(K)))
 
 
 def gemm_bf16_tc_few(x, w, bias, out, gated: int = 0, defer: bool = False) -> None:
@@ -518,8 +539,7 @@ def gemm_bf16_tc_few(x, w, bias, out, gated: int = 0, defer: bool = False) -> No
         floats = 0
     else:
         assert out.shape == (M, N // 2 if gated else N)
-        lib.coheryn_gemm_tc_few_workspace_floats.restype = ctypes.c_long
-        floats = int(lib.coheryn_gemm_tc_few_workspace_floats(c_int(M), c_int(N), c_int(K)))   # > 0: K is split
+        floats = _few_workspace_floats(M, N, K)   # > 0: K is split
     workspace = _few_workspace(x.device, floats) if floats else None
     _check(lib, lib.coheryn_gemm_bf16_tc_few(
         _ptr(x), _ptr(w), _ptr(bias), c_int(_code(bias) if bias is not None else F32), _ptr(out),
