@@ -988,6 +988,7 @@ CO_EXPORT int coheryn_attn_head_dim() { return HD; }
 CO_EXPORT int coheryn_attn_split_keys() { return SPLIT_MIN; }
 // keys = 128, 256 or 512 fixes the positions per CTA of the decode kernel; 0 restores the choice by batch size.
 CO_EXPORT void coheryn_attn_set_tc_cluster(int cluster) { coheryn_attention_tc_set_cluster(cluster); }
+CO_EXPORT void coheryn_attn_set_tc_two_tiles(int mode) { coheryn_attention_tc_set_two_tiles(mode); }
 CO_EXPORT void coheryn_attn_set_split(int keys) { g_forced_split = (keys == 128 || keys == 256 || keys == 512) ? keys : 0; }
 
 // Floats of scratch that coheryn_attention_bf16 needs for B requests of at most

@@ -17,7 +17,8 @@
 //              memory for the next MMA, and rescale their half of the row of O when the
 //              reference maximum moved.  At the end they divide by the sum and store the row.
 // S for the next key tile is issued as soon as the softmax threads hold the current one in
-// registers, so the exponentials overlap the next Q K^T.
+// registers, so the exponentials overlap the next Q K^T.  (attn_tc2_kernel further down gives a
+// CTA two row tiles that share every fetched key tile; it takes long prompts.)
 //
 // A short portion over a long context makes few row tiles with many key tiles each.  The kernel
 // then runs as clusters of 2, 4 or 8 CTAs along x that share a row tile: CTA r takes the key
@@ -79,6 +80,16 @@ __device__ __forceinline__ float ld_cluster1(const float* local, unsigned rank) 
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
   return v;
 }
+// The rows of a query tile beyond its RT = TOK * G whole tokens are not fetched; they are zeroed (by the
+// thread that issues the MMAs, once the tile has landed) so that their scores are 0 and their softmax
+// threads, whose results nobody reads, walk the same path as the others.
+__device__ __forceinline__ void zero_spare_rows(unsigned char* q_tile, int RT) {
+  for (int c = 0; c < KCH; ++c)
+    for (int r = RT; r < 128; ++r)
+      for (int piece = 0; piece < 8; ++piece)
+        *reinterpret_cast<uint4*>(q_tile + c * CHUNK_BYTES + r * 128 + piece * 16) = make_uint4(0, 0, 0, 0);
+  fence_proxy_async();
+}
 constexpr int XLD = HD + 4;                       // row stride (floats) of a CTA's published accumulator
 constexpr int MAX_CLUSTER = 8;
 static_assert(!SUPPORTED || (size_t)(128 * XLD + 256) * 4 <= (size_t)Q_BYTES + (size_t)NST * 2 * KV_BYTES, "a published accumulator fits the tiles");
@@ -99,8 +110,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   unsigned long long* v_full = k_full + NST;        // [NST]
   unsigned long long* kv_empty = v_full + NST;      // [NST]
   unsigned long long* s_full = kv_empty + NST;      // MMA -> softmax: S is complete
-  unsigned long long* s_free = s_full + 1;          // softmax -> MMA: S is in registers (256 arrivals)
-  unsigned long long* p_full = s_free + 1;          // softmax -> MMA: P written, O rescaled (256 arrivals)
+  unsigned long long* s_free = s_full + 1;          // softmax -> MMA: S is in registers (one arrival per warp)
+  unsigned long long* p_full = s_free + 1;          // softmax -> MMA: P written, O rescaled (one arrival per warp)
   unsigned long long* pv_done = p_full + 1;         // MMA -> softmax: O += P V is complete
   unsigned* tmem_slot = (unsigned*)(pv_done + 1);
   float (*row_ex)[128] = (float (*)[128])((unsigned char*)bars + 256);   // [half][row]: the two threads of a row meet here
@@ -110,7 +121,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_full, 1); mbar_init(s_free, 256); mbar_init(p_full, 256); mbar_init(pv_done, 1);
+    mbar_init(s_full, 1); mbar_init(s_free, 8); mbar_init(p_full, 8); mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -188,6 +199,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       constexpr unsigned idesc_pv = umma_idesc_b_mn(128, HD);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(status, 32);
+      zero_spare_rows(q_s, RT);
       auto issue_qk = [&](int j) {
         const int s = j % NST;
         if (!mbar_wait(&k_full[s], (unsigned)(j / NST) & 1)) { atomicExch(status, 33); return false; }
@@ -246,10 +258,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       tmem_ld32_nowait(lane_addr + COL_S + half * 64 + 32, sr[1]);
       tmem_wait_ld();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(s_free);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
       const int key0 = (tile_first + j) * BN + half * 64;
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (key0 >= lo && key0 + 63 <= hi) {
+      if (!valid || (key0 >= lo && key0 + 63 <= hi)) {
 #pragma unroll
         for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -315,7 +328,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       tmem_st32(lane_addr + COL_P + half * 32, pr);
       tmem_wait_st();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
     }
     if (ok) {
       if (!mbar_wait(pv_done, (unsigned)(n_tiles - 1) & 1)) { if (lane == 0) atomicExch(status, 39); ok = false; }
@@ -416,10 +430,331 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Two query tiles per CTA.  Every CTA of a (request, kv head) streams the same keys and values
+// out of L2, and with one tile of 128 rows per CTA that stream, not the tensor pipe or the
+// softmax, bounds the kernel (8.4 MFLOP per 64 KB).  Here a CTA owns two consecutive row tiles
+// A and B (256 rows), fetches every key tile once for both, and keeps S_A, S_B, O_A, O_B in the
+// 512 columns of tensor memory; the probabilities go back into the first 64 columns of the
+// scores they came from (bfloat16 pairs).  The MMA thread alternates between the tiles:
+//   P V_A(j), Q K_A^T(j+1), P V_B(j), Q K_B^T(j+1), ...
+// so while one tile's softmax warps (eight per tile, two threads per row) work, the tensor pipe
+// runs the other tile's products.  The next S of a tile is issued behind the P V that read the
+// P in the same columns: the pipe runs MMAs in order.  K stages and V stages are released
+// separately (K after the second Q K^T, V after the second P V), two of each.  Tile A sees
+// fewer keys than tile B by at most one key tile and stops early.  Head sizes up to 128.
+constexpr bool TWO_OK = SUPPORTED && HD <= 128;
+constexpr int NST2 = 2;
+constexpr int SMEM2_BYTES = 2 * Q_BYTES + NST2 * 2 * KV_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 2048 /* row_ex */;
+static_assert(!TWO_OK || SMEM2_BYTES <= 227 * 1024, "two query tiles and the stages fit shared memory");
+
+__global__ void __launch_bounds__(576, 1)
+attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long out_stride,
+                const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
+                const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int cache_rows, int window,
+                float scale_log2, int skip_small, int rows_per_box, int* __restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_s = tiles;                                   // [tile][KCH][128 rows][128 B]
+  unsigned char* k_s = tiles + 2 * Q_BYTES;                     // [NST2][KCH][128 rows][128 B]
+  unsigned char* v_s = k_s + NST2 * KV_BYTES;                   // [NST2][KCH][128 rows][128 B]
+  unsigned long long* bars = (unsigned long long*)(v_s + NST2 * KV_BYTES);
+  unsigned long long* q_full = bars;                // 1
+  unsigned long long* k_full = bars + 1;            // [NST2]
+  unsigned long long* v_full = k_full + NST2;       // [NST2]
+  unsigned long long* k_empty = v_full + NST2;      // [NST2] both tiles' Q K^T have read the stage
+  unsigned long long* v_empty = k_empty + NST2;     // [NST2] both tiles' P V have read the stage
+  unsigned long long* s_full = v_empty + NST2;      // [2] MMA -> softmax of tile t: S is complete
+  unsigned long long* p_full = s_full + 2;          // [2] softmax -> MMA: P written, O rescaled (one arrival per warp)
+  unsigned long long* pv_done = p_full + 2;         // [2] MMA -> softmax: O += P V is complete
+  unsigned* tmem_slot = (unsigned*)(pv_done + 2);
+  float (*row_ex)[2][128] = (float (*)[2][128])((unsigned char*)bars + 256);   // [tile][half][row]
+  static_assert((1 + 4 * NST2 + 6) * 8 + 4 <= 256, "barriers fit their slot");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < NST2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 8); mbar_init(&pv_done[t], 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+
+  // Late rows see the most keys: their pairs of tiles are started first.
+  const int b = blockIdx.z, kvh = blockIdx.y, pair = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int G = nh / nkv, TOK = 128 / G, RT = TOK * G;
+  const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
+  const int rows = q_len * G;
+  const bool active_a = 2 * pair * RT < rows && !(skip_small && rows <= 16);
+  const bool active_b = active_a && (2 * pair + 1) * RT < rows;
+  const int base_pos = kv_len - q_len;
+  const int first_a = 2 * pair * RT, first_b = first_a + RT;
+  const int last_a = min(rows, first_a + RT) - 1, last_b = min(rows, first_b + RT) - 1;
+  const int pos_lo = base_pos + first_a / G;                                  // the pair's first position
+  const int pos_hi_a = base_pos + last_a / G, pos_hi_b = base_pos + last_b / G;
+  const int key_first = window > 0 ? max(0, pos_lo - window + 1) : 0;
+  const int tile_first = key_first / BN;
+  const int n_a = active_a ? pos_hi_a / BN - tile_first + 1 : 0;              // key tiles of tile A, of tile B
+  const int n_b = active_b ? pos_hi_b / BN - tile_first + 1 : 0;
+  const int n_tiles = n_b > n_a ? n_b : n_a;
+  constexpr unsigned COL_SA = 0, COL_OA = 256;                                // tile t: + 128 t
+
+  if (warp == 0) {
+    if (n_tiles > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(q_full, (unsigned)(KCH * RT * 128 * (active_b ? 2 : 1)));
+        for (int t = 0; t < (active_b ? 2 : 1); ++t)
+          for (int c = 0; c < KCH; ++c)
+            tma_load_3d(q_s + t * Q_BYTES + c * CHUNK_BYTES, &map_q, c * 64, kvh * G, tok0 + (2 * pair + t) * TOK, q_full);
+      }
+      const int* table = block_tables + (size_t)b * max_blocks;
+      const int boxes = BN / rows_per_box;       // lane i < boxes fetches box i of every tile
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % NST2;
+        int row = 0;
+        if (lane < boxes) {                      // the box's first row in the cache tensors
+          const int pos = (tile_first + j) * BN + lane * rows_per_box;
+          const int blk = pos / page_size;
+          const int page = blk < max_blocks ? table[blk] : -1;
+          // a page that is not there: a box beyond the tensor, fetched as zeros
+          row = page >= 0 ? (page * nkv + kvh) * page_size + (pos - blk * page_size) : cache_rows;
+        }
+        for (int kv = 0; kv < 2 && ok; ++kv) {
+          unsigned long long* empty = kv ? &v_empty[s] : &k_empty[s];
+          unsigned long long* full = kv ? &v_full[s] : &k_full[s];
+          if (j >= NST2) {
+            if (lane == 0 && !mbar_wait(empty, (unsigned)((j / NST2) - 1) & 1)) { atomicExch(status, 31); ok = false; }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+          }
+          if (lane == 0) mbar_expect_tx(full, (unsigned)KV_BYTES);
+          __syncwarp();
+          unsigned char* dst = (kv ? v_s : k_s) + (size_t)s * KV_BYTES;
+          if (lane < boxes)
+            for (int c = 0; c < KCH; ++c)
+              tma_load_2d(dst + c * CHUNK_BYTES + lane * rows_per_box * 128, kv ? &map_v : &map_k, c * 64, row, full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr unsigned idesc_qk = umma_idesc(128, BN);
+      constexpr unsigned idesc_pv = umma_idesc_b_mn(128, HD);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) atomicExch(status, 32);
+      zero_spare_rows(q_s, RT);
+      zero_spare_rows(q_s + Q_BYTES, RT);
+      auto issue_qk = [&](int t, int j) {        // S_t = Q_t K(j)^T; the caller has waited for K(j)
+        const unsigned char* k_src = k_s + (size_t)(j % NST2) * KV_BYTES;
+#pragma unroll
+        for (int c = 0; c < KCH; ++c) {
+          const unsigned long long dq = umma_desc(q_s + t * Q_BYTES + c * CHUNK_BYTES), dk = umma_desc(k_src + c * CHUNK_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + COL_SA + 128 * t, dq + 2 * k, dk + 2 * k, idesc_qk, (c | k) != 0);
+        }
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int j) {        // O_t += P_t V(j); the caller has waited for P and V(j)
+        const unsigned char* v_src = v_s + (size_t)(j % NST2) * KV_BYTES;
+        const unsigned long long dv = umma_desc_offsets(v_src, CHUNK_BYTES, 1024);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_bf16_a_tmem(tmem_base + COL_OA + 128 * t, tmem_base + COL_SA + 128 * t + kk * 8, dv + (unsigned long long)(kk * 128),
+                           idesc_pv, (j | kk) != 0);
+        umma_commit(&pv_done[t]);
+      };
+      if (ok && !mbar_wait(&k_full[0], 0)) { atomicExch(status, 33); ok = false; }
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_qk(0, 0);
+        if (n_b > 0) issue_qk(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % NST2, s1 = (j + 1) % NST2;
+        bool k_next = false;                     // K(j + 1) has been waited for
+        if (j < n_a) {
+          if (!mbar_wait(&p_full[0], (unsigned)j & 1)) { atomicExch(status, 35); ok = false; break; }
+          if (!mbar_wait(&v_full[s], (unsigned)(j / NST2) & 1)) { atomicExch(status, 36); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_pv(0, j);
+        }
+        if (j + 1 < n_a) {
+          if (!mbar_wait(&k_full[s1], (unsigned)((j + 1) / NST2) & 1)) { atomicExch(status, 33); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          k_next = true;
+          issue_qk(0, j + 1);
+        }
+        if (j < n_b) {
+          if (!mbar_wait(&p_full[1], (unsigned)j & 1)) { atomicExch(status, 35); ok = false; break; }
+          if (!mbar_wait(&v_full[s], (unsigned)(j / NST2) & 1)) { atomicExch(status, 36); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_pv(1, j);
+        }
+        umma_commit(&v_empty[s]);
+        if (j + 1 < n_tiles) {
+          if (j + 1 < n_b) {
+            if (!k_next && !mbar_wait(&k_full[s1], (unsigned)((j + 1) / NST2) & 1)) { atomicExch(status, 33); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_qk(1, j + 1);
+          }
+          umma_commit(&k_empty[s1]);
+        }
+      }
+    }
+  } else {
+    // Softmax warps: 2..9 for tile A, 10..17 for tile B; TMEM lane quarter = warp % 4; two threads
+    // per row, the first four warps of a tile taking key columns 0..63 of every key tile (and the
+    // first half of the head dim of O), the other four the rest.
+    const int t = warp >= 10 ? 1 : 0;
+    const int quarter = warp & 3, half = (warp - 2 - 8 * t) >> 2;
+    const int my_tiles = t ? n_b : n_a;
+    if (my_tiles > 0) {
+      const int row = quarter * 32 + lane;
+      const int row_first = t ? first_b : first_a;
+      const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
+      const unsigned col_s = COL_SA + 128 * t, col_o = COL_OA + 128 * t;
+      const int bar_id = 1 + 4 * t + quarter;
+      const bool valid = row < RT && row_first + row < rows;
+      const int pos = base_pos + (row_first + row) / G;
+      const int hi = valid ? pos : -1;
+      const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+      float m = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < my_tiles; ++j) {
+        if (!mbar_wait(&s_full[t], (unsigned)j & 1)) { if (lane == 0) atomicExch(status, 37); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned sr[2][32];
+        tmem_ld32_nowait(lane_addr + col_s + half * 64, sr[0]);
+        tmem_ld32_nowait(lane_addr + col_s + half * 64 + 32, sr[1]);
+        tmem_wait_ld();
+        const int key0 = (tile_first + j) * BN + half * 64;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (!valid || (key0 >= lo && key0 + 63 <= hi)) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[i][c]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int key = key0 + i * 32 + c;
+              if (key < lo || key > hi) sr[i][c] = __float_as_uint(-INFINITY);
+              mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[i][c]));
+            }
+        }
+        // The row's maximum over both halves, through shared memory.  Both threads hold their S in
+        // registers before either passes the first meeting, so the second half may write its P
+        // over the first half's score columns afterwards.
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        row_ex[t][half][row] = mx;
+        asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+        mx = fmaxf(mx, row_ex[t][half ^ 1][row]);
+        asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+        // The reference point m follows the running maximum lazily (see attn_tc_kernel).
+        const float m_row = fmaxf(m, mx * scale_log2);
+        const bool move = m == -INFINITY ? m_row != -INFINITY : m_row - m > 8.0f;
+        const bool moved = __any_sync(0xffffffffu, move);
+        const float m_new = moved ? m_row : m;
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = ex2_approx(m - m_use);
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        unsigned pr[32];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            sr[i][c] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(sr[i][c]), scale_log2, -m_use)));
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float p0 = __uint_as_float(sr[i][c]), p1 = __uint_as_float(sr[i][c + 1]);
+            sum4[(c >> 1) & 3] += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            pr[i * 16 + (c >> 1)] = *reinterpret_cast<unsigned*>(&h);
+          }
+        }
+        l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        m = m_new;
+        if (j > 0) {
+          if (!mbar_wait(&pv_done[t], (unsigned)(j - 1) & 1)) { if (lane == 0) atomicExch(status, 38); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (moved) {
+#pragma unroll 1
+            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+              unsigned o[32];
+              tmem_ld32(lane_addr + col_o + c0, o);
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+              tmem_st32(lane_addr + col_o + c0, o);
+            }
+          }
+        }
+        tmem_st32(lane_addr + col_s + half * 32, pr);
+        tmem_wait_st();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t]);
+      }
+      if (ok) {
+        if (!mbar_wait(&pv_done[t], (unsigned)(my_tiles - 1) & 1)) { if (lane == 0) atomicExch(status, 39); ok = false; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      // The row's sum: the first half's plus the second's.  (Both threads of a row come here.)
+      row_ex[t][half][row] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+      l = row_ex[t][0][row] + row_ex[t][1][row];
+      if (ok) {
+        const float inv = 1.0f / l;
+        const int rr = row_first + row;
+        bf16* orow = out + (size_t)(tok0 + rr / G) * out_stride + (size_t)(kvh * G + rr % G) * HD;
+#pragma unroll 1
+        for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+          unsigned o[32];
+          tmem_ld32(lane_addr + col_o + c0, o);     // warp-collective: invalid rows read too, and skip the store
+          if (valid) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+              __nv_bfloat162 d = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+              uint2 raw;
+              raw.x = *reinterpret_cast<unsigned*>(&a);
+              raw.y = *reinterpret_cast<unsigned*>(&d);
+              *reinterpret_cast<uint2*>(orow + c0 + c) = raw;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
+  }
+}
+
 }  // namespace
 
 static int g_forced_cluster = -1;   // -1: the environment decides at the first launch; 0: by shape
 void coheryn_attention_tc_set_cluster(int cluster) { g_forced_cluster = cluster; }
+static int g_two_tiles = -1;        // -1: the environment decides at the first launch; 0 never, 1 always, 2 by the number of CTAs
+void coheryn_attention_tc_set_two_tiles(int mode) { g_two_tiles = mode < 0 || mode > 2 ? 2 : mode; }
 
 bool coheryn_attention_tc_takes(int nh, int nkv, int page_size) {
   if (!SUPPORTED || nkv <= 0 || nh % nkv) return false;
@@ -472,6 +807,26 @@ int coheryn_attention_tc_launch(const void* q, long q_stride, int total_tokens, 
   int cluster = 1;
   while (cluster < MAX_CLUSTER && ctas * cluster * 2 <= 148L && key_tiles >= 16 * cluster) cluster *= 2;
   if (forced == 1 || forced == 2 || forced == 4 || forced == 8) cluster = forced;
+  if (g_two_tiles < 0) { const char* e = getenv("COHERYN_ATTN_TC_TWO"); g_two_tiles = e ? (e[0] == '0' ? 0 : e[0] == '1' ? 1 : 2) : 2; }
+  // Two row tiles per CTA (every key tile fetched once for 256 rows) once the pairs still fill the
+  // GPU with a quarter to spare: measured at 12 query heads in 2 groups, 4,096 tokens (196 CTAs)
+  // 100 against 109 us, 16,384 tokens 0.98 against 1.25 ms, but 2,048 tokens (98 CTAs) 55 against 37.
+  const long pair_ctas = (long)((row_tiles + 1) / 2) * nkv * B;
+  if (TWO_OK && cluster == 1 && row_tiles >= 2 && (g_two_tiles == 1 || (g_two_tiles == 2 && pair_ctas >= 185))) {
+    static bool configured2 = false;
+    if (!configured2) {
+      cudaError_t e = cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+      if (e != cudaSuccess) CO_FAIL("attention_tc: %d bytes of shared memory: %s", SMEM2_BYTES, cudaGetErrorString(e));
+      configured2 = true;
+    }
+    dim3 grid2((row_tiles + 1) / 2, nkv, B);
+    cudaError_t le2 = co_launch(attn_tc2_kernel, grid2, dim3(576), (size_t)SMEM2_BYTES, stream, mq, mk, mv, (bf16*)out, out_stride,
+                                block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows, window, scale_log2,
+                                skip_small, rows_per_box, status);
+    if (le2 != cudaSuccess) CO_FAIL("attention_tc: launch failed: %s", cudaGetErrorString(le2));
+    CO_CHECK_LAUNCH("attn_tc2");
+    return 0;
+  }
   dim3 grid(row_tiles * cluster, nkv, B);
   cudaError_t le = co_launch_cluster(cluster, attn_tc_kernel, grid, dim3(320), (size_t)SMEM_BYTES, stream, mq, mk, mv, (bf16*)out,
                                      out_stride, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows,

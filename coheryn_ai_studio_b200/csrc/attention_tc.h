@@ -9,6 +9,11 @@ bool coheryn_attention_tc_takes(int nh, int nkv, int page_size);
 // CTAs per row tile that split its key tiles (1, 2, 4 or 8; 0: chosen by shape).  For tests.
 void coheryn_attention_tc_set_cluster(int cluster);
 
+// Whether a CTA takes two consecutive row tiles and fetches every key tile once for both (head
+// sizes up to 128, unsplit row tiles): 0 never, 1 always, 2 when the pairs still fill the GPU (the
+// default).  For tests.
+void coheryn_attention_tc_set_two_tiles(int mode);
+
 // Attention of every request of the batch with more than 16 rows per kv head (all requests
 // when skip_small is 0).  q: [total_tokens, >= nh * HD] bfloat16 rows of stride q_stride;
 // caches: [num_pages][nkv][page_size][HD]; max_rows and max_kv_len bound the batch's rows per kv head and

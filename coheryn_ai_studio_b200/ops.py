@@ -665,6 +665,13 @@ def set_attention_split(head_dim: int, keys: int) -> None:
     attention_lib(head_dim).coheryn_attn_set_split(c_int(keys))
 
 
+def set_attention_tc_two_tiles(head_dim: int, on: Optional[bool]) -> None:
+    """Whether the prompt-portion attention kernel gives a CTA two consecutive row tiles that share
+    every fetched key tile (head sizes up to 128): always, never, or (None, the default) when the
+    pairs still fill the GPU.  For tests and experiments."""
+    attention_lib(head_dim).coheryn_attn_set_tc_two_tiles(c_int(2 if on is None else (1 if on else 0)))
+
+
 def set_attention_tc_cluster(head_dim: int, cluster: int) -> None:
     """Fix the number of CTAs (1, 2, 4 or 8) that share a row tile of the prompt-portion attention
     kernel and split its keys; 0 restores the choice by shape.  For tests and experiments."""

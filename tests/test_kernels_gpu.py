@@ -413,13 +413,14 @@ def test_attention_finds_a_far_key(dtype):
 @pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 16), (4, 1, 64, 8), (8, 8, 128, 64), (6, 2, 64, 128),
                                             (16, 1, 128, 256), (3, 1, 192, 32), (2, 1, 256, 16)])
 @pytest.mark.parametrize("window", [None, 200])
-@pytest.mark.parametrize("cluster", [0, 2, 8])
-def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window, cluster):
-    """Prompt portions through the tcgen05 kernel (S and O in tensor memory, P fed back from
+@pytest.mark.parametrize("cluster,two_tiles", [(0, True), (0, False), (2, False), (8, False)])
+def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window, cluster, two_tiles):
+    """Prompt portions through the tcgen05 kernels (S and O in tensor memory, P fed back from
     it): whole prompts and tails that start inside a key tile, several key tiles, row tiles
-    that end inside a token group, a window that begins inside a tile; with the key tiles of a
-    row tile split over 2 or 8 CTAs of a cluster (some of them left without a tile) and merged
-    through distributed shared memory."""
+    that end inside a token group, a window that begins inside a tile; with two row tiles per
+    CTA sharing every fetched key tile (an odd number of row tiles leaves the last CTA one), with
+    one, and with the key tiles of a row tile split over 2 or 8 CTAs of a cluster (some of them
+    left without a tile) and merged through distributed shared memory."""
     rng = np.random.default_rng(nh + hd + page)
     lens = [300, 700, 129, 64]
     q_lens = [300, 257, 20, 64]
@@ -434,6 +435,7 @@ def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window, clus
     cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     out = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
     ops().set_attention_tc_cluster(hd, cluster)
+    ops().set_attention_tc_two_tiles(hd, two_tiles)
     try:
         ops().attention_rows(q, out, kc, vc, bt, t32(np.asarray(reqs, np.int32)), t32(np.asarray(poss, np.int32)),
                              nh, nkv, hd, page, window, scale, cu_q=t32(cu), kv_lens=t32(np.asarray(lens, np.int32)),
@@ -441,10 +443,44 @@ def test_attention_prompt_portions_tensor_memory(nh, nkv, hd, page, window, clus
         ops().check_tc_status(DEV)
     finally:
         ops().set_attention_tc_cluster(hd, 0)
+        ops().set_attention_tc_two_tiles(hd, None)
     ref = attention_reference(q.float().cpu().numpy(), ks, vs, reqs, poss, nh, nkv, hd, window, scale)
     tol = 2 ** -8 * np.abs(ref) + 2 ** -8
     err = np.abs(out.float().cpu().numpy() - ref)
     assert np.all(err <= tol), (float(err.max()), np.argwhere(err > tol)[:5].tolist())
+
+
+@pytest.mark.parametrize("window", [None, 700])
+def test_attention_long_prompt_takes_two_row_tiles_per_cta(window):
+    """A prompt long enough that pairs of row tiles still fill the GPU (192 CTAs of 256 rows here)
+    goes to the kernel with two row tiles per CTA by itself; a sample of its rows is compared with
+    the plain attention, all of them with the kernel that gives every row tile a CTA of its own."""
+    nh, nkv, hd, page, n = 16, 8, 64, 16, 3000
+    rng = np.random.default_rng(77)
+    kc, vc, bt, ks, vs = paged_setup(rng, [n], nkv, hd, page, torch.bfloat16)
+    q = torch.from_numpy(rng.standard_normal((n, nh * hd)).astype(np.float32)).to(torch.bfloat16).to(DEV)
+    scale = 1.0 / np.sqrt(hd)
+    args = (kc, vc, bt, t32(np.zeros(n, np.int32)), t32(np.arange(n, dtype=np.int32)), nh, nkv, hd, page, window, scale)
+    kw = dict(cu_q=t32(np.asarray([0, n], np.int32)), kv_lens=t32(np.asarray([n], np.int32)), q_lens=[n], max_kv_len=n)
+    outs = {}
+    try:
+        for mode in (None, False):
+            ops().set_attention_tc_two_tiles(hd, mode)
+            before = ops().total_launch_count()
+            outs[mode] = torch.zeros(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+            ops().attention_rows(q, outs[mode], *args, **kw)
+            ops().check_tc_status(DEV)
+            assert ops().total_launch_count() == before + 1
+    finally:
+        ops().set_attention_tc_two_tiles(hd, None)
+    rows = np.unique(np.concatenate([rng.integers(0, n, 40), [0, 1, 127, 128, 255, 256, 699, 700, 701, n - 1]]))
+    ref = attention_reference(q.float().cpu().numpy()[rows], ks, vs, [0] * len(rows), rows.tolist(), nh, nkv, hd, window, scale)
+    got = outs[None].float().cpu().numpy()
+    tol = 2 ** -8 * np.abs(ref) + 2 ** -8
+    err = np.abs(got[rows] - ref)
+    assert np.all(err <= tol), (float(err.max()), np.argwhere(err > tol)[:5].tolist())
+    # the two kernels order their sums differently and move the exponent's reference at different tiles
+    assert float((got - outs[False].float().cpu().numpy()).max()) <= 2 ** -6
 
 
 @pytest.mark.parametrize("nh,nkv,hd,K,page", [(12, 2, 128, 1536, 16), (4, 2, 16, 64, 16), (3, 1, 32, 96, 8), (5, 5, 48, 200, 32)])
