@@ -99,7 +99,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long out_stride,
                const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int cache_rows, int window,
-               float scale_log2, int skip_small, int rows_per_box, int* __restrict__ status) {
+               float scale_log2, int skip_small, int rows_per_box, int* __restrict__ status, int n_req, int n_units) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = tiles;                                   // [KCH][128 rows][128 B]
@@ -135,10 +135,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   co_pdl_launch_dependents();
   co_pdl_wait();
 
-  // Late row tiles see the most keys: they are started first.  The CTAs of a cluster (along x)
-  // share a row tile and split its key tiles among them; the last one merges.
+  // Late row tiles see the most keys: they are started first, for ALL (request, kv head) pairs before
+  // any earlier row tile (the grid is one-dimensional and the row tile its slowest index; CTAs start
+  // in the order of their index).  The CTAs of a cluster (consecutive indices) share a row tile and
+  // split its key tiles among them; the last one merges.
   const int csize = (int)cluster_size(), crank = (int)cluster_rank();
-  const int b = blockIdx.z, kvh = blockIdx.y, rt = (int)(gridDim.x / csize) - 1 - (int)(blockIdx.x / csize);
+  const int unit = (int)(blockIdx.x / csize), heads_reqs = nkv * n_req;
+  const int b = (unit % heads_reqs) / nkv, kvh = unit % nkv, rt = n_units - 1 - unit / heads_reqs;
   const int G = nh / nkv, TOK = 128 / G, RT = TOK * G;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
   const int rows = q_len * G;
@@ -454,7 +457,7 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long out_stride,
                 const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                 const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int cache_rows, int window,
-                float scale_log2, int skip_small, int rows_per_box, int* __restrict__ status) {
+                float scale_log2, int skip_small, int rows_per_box, int* __restrict__ status, int n_req, int n_units) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = tiles;                                   // [tile][KCH][128 rows][128 B]
@@ -491,8 +494,10 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   co_pdl_launch_dependents();
   co_pdl_wait();
 
-  // Late rows see the most keys: their pairs of tiles are started first.
-  const int b = blockIdx.z, kvh = blockIdx.y, pair = (int)gridDim.x - 1 - (int)blockIdx.x;
+  // Late rows see the most keys: their pairs of tiles are started first, for all (request, kv head)
+  // pairs before any earlier pair of tiles (one-dimensional grid, the pair of tiles its slowest index).
+  const int unit = (int)blockIdx.x, heads_reqs = nkv * n_req;
+  const int b = (unit % heads_reqs) / nkv, kvh = unit % nkv, pair = n_units - 1 - unit / heads_reqs;
   const int G = nh / nkv, TOK = 128 / G, RT = TOK * G;
   const int tok0 = cu_q[b], q_len = cu_q[b + 1] - tok0, kv_len = kv_lens[b];
   const int rows = q_len * G;
@@ -819,18 +824,21 @@ int coheryn_attention_tc_launch(const void* q, long q_stride, int total_tokens, 
       if (e != cudaSuccess) CO_FAIL("attention_tc: %d bytes of shared memory: %s", SMEM2_BYTES, cudaGetErrorString(e));
       configured2 = true;
     }
-    dim3 grid2((row_tiles + 1) / 2, nkv, B);
+    const int pairs = (row_tiles + 1) / 2;
+    if (pair_ctas >= (1L << 31)) CO_FAIL("attention_tc: %ld CTAs", pair_ctas);
+    dim3 grid2((unsigned)pair_ctas);
     cudaError_t le2 = co_launch(attn_tc2_kernel, grid2, dim3(576), (size_t)SMEM2_BYTES, stream, mq, mk, mv, (bf16*)out, out_stride,
                                 block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows, window, scale_log2,
-                                skip_small, rows_per_box, status);
+                                skip_small, rows_per_box, status, B, pairs);
     if (le2 != cudaSuccess) CO_FAIL("attention_tc: launch failed: %s", cudaGetErrorString(le2));
     CO_CHECK_LAUNCH("attn_tc2");
     return 0;
   }
-  dim3 grid(row_tiles * cluster, nkv, B);
+  if (ctas * cluster >= (1L << 31)) CO_FAIL("attention_tc: %ld CTAs", ctas * cluster);
+  dim3 grid((unsigned)(ctas * cluster));
   cudaError_t le = co_launch_cluster(cluster, attn_tc_kernel, grid, dim3(320), (size_t)SMEM_BYTES, stream, mq, mk, mv, (bf16*)out,
                                      out_stride, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows,
-                                     window, scale_log2, skip_small, rows_per_box, status);
+                                     window, scale_log2, skip_small, rows_per_box, status, B, row_tiles);
   if (le != cudaSuccess) CO_FAIL("attention_tc: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("attn_tc");
   return 0;
