@@ -438,21 +438,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // Two query tiles per CTA.  Every CTA of a (request, kv head) streams the same keys and values
 // out of L2, and with one tile of 128 rows per CTA that stream, not the tensor pipe or the
 // softmax, bounds the kernel (8.4 MFLOP per 64 KB).  Here a CTA owns two consecutive row tiles
-// A and B (256 rows), fetches every key tile once for both, and keeps S_A, S_B, O_A, O_B in the
-// 512 columns of tensor memory; the probabilities go back into the first 64 columns of the
-// scores they came from (bfloat16 pairs).  The MMA thread alternates between the tiles:
-//   P V_A(j), Q K_A^T(j+1), P V_B(j), Q K_B^T(j+1), ...
-// so while one tile's softmax warps (eight per tile, two threads per row) work, the tensor pipe
-// runs the other tile's products.  The next S of a tile is issued behind the P V that read the
-// P in the same columns: the pipe runs MMAs in order.  K stages and V stages are released
-// separately (K after the second Q K^T, V after the second P V), two of each.  Tile A sees
+// A and B (256 rows) and fetches every key tile once for both: S_A, S_B, O_A, O_B fill the 512
+// columns of tensor memory.  A tile's chain S -> softmax -> P -> P V is kept from being serial:
+//   * one softmax thread per row (warps 2-5 tile A, 6-9 tile B; one of each per scheduler) takes
+//     the row's 128 scores into registers and hands the score buffer back at once, so the next
+//     Q K^T of the tile runs while the exponentials are computed;
+//   * the probabilities go to SHARED memory (128 x 128 bfloat16 per row tile, written row by row
+//     in the 128-byte swizzle) and P V reads both operands from there;
+//   * the MMA thread issues Q K_A^T(j+1), Q K_B^T(j+1), P V_A(j), P V_B(j): the products of one
+//     tile run while the other tile's softmax works.
+// Key tiles are 128 positions (an MMA instruction takes about 70 cycles however narrow it is).
+// Two K stages and one V stage, released separately; K runs one tile ahead of V.  Tile A sees
 // fewer keys than tile B by at most one key tile and stops early.  Head sizes up to 128.
 constexpr bool TWO_OK = SUPPORTED && HD <= 128;
-constexpr int NST2 = 2;
-constexpr int SMEM2_BYTES = 2 * Q_BYTES + NST2 * 2 * KV_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 2048 /* row_ex */;
-static_assert(!TWO_OK || SMEM2_BYTES <= 227 * 1024, "two query tiles and the stages fit shared memory");
+constexpr int NKS2 = 2;                           // K stages (V has one)
+constexpr int P2_BYTES = 2 * CHUNK_BYTES;         // 128 rows x 128 bfloat16, as two 64-column chunks
+constexpr int SMEM2_BYTES = 2 * Q_BYTES + (NKS2 + 1) * KV_BYTES + 2 * P2_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+static_assert(!TWO_OK || SMEM2_BYTES <= 227 * 1024, "two query tiles, the stages and the probabilities fit shared memory");
 
-__global__ void __launch_bounds__(576, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long out_stride,
                 const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
@@ -461,26 +465,27 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = tiles;                                   // [tile][KCH][128 rows][128 B]
-  unsigned char* k_s = tiles + 2 * Q_BYTES;                     // [NST2][KCH][128 rows][128 B]
-  unsigned char* v_s = k_s + NST2 * KV_BYTES;                   // [NST2][KCH][128 rows][128 B]
-  unsigned long long* bars = (unsigned long long*)(v_s + NST2 * KV_BYTES);
+  unsigned char* k_s = q_s + 2 * Q_BYTES;                       // [NKS2][KCH][128 rows][128 B]
+  unsigned char* v_s = k_s + NKS2 * KV_BYTES;                   // [KCH][128 rows][128 B]
+  unsigned char* p_s = v_s + KV_BYTES;                          // [tile][2][128 rows][128 B]
+  unsigned long long* bars = (unsigned long long*)(p_s + 2 * P2_BYTES);
   unsigned long long* q_full = bars;                // 1
-  unsigned long long* k_full = bars + 1;            // [NST2]
-  unsigned long long* v_full = k_full + NST2;       // [NST2]
-  unsigned long long* k_empty = v_full + NST2;      // [NST2] both tiles' Q K^T have read the stage
-  unsigned long long* v_empty = k_empty + NST2;     // [NST2] both tiles' P V have read the stage
-  unsigned long long* s_full = v_empty + NST2;      // [2] MMA -> softmax of tile t: S is complete
-  unsigned long long* p_full = s_full + 2;          // [2] softmax -> MMA: P written, O rescaled (one arrival per warp)
-  unsigned long long* pv_done = p_full + 2;         // [2] MMA -> softmax: O += P V is complete
+  unsigned long long* k_full = bars + 1;            // [NKS2]
+  unsigned long long* k_empty = k_full + NKS2;      // [NKS2] both tiles' Q K^T have read the stage
+  unsigned long long* v_full = k_empty + NKS2;      // 1
+  unsigned long long* v_empty = v_full + 1;         // 1: both tiles' P V have read the stage
+  unsigned long long* s_full = v_empty + 1;         // [tile] MMA -> softmax: S is complete
+  unsigned long long* s_free = s_full + 2;          // [tile] softmax -> MMA: S is in registers (one arrival per warp)
+  unsigned long long* p_full = s_free + 2;          // [tile] softmax -> MMA: P written, O rescaled (one arrival per warp)
+  unsigned long long* pv_done = p_full + 2;         // [tile] MMA -> softmax: O += P V is complete
   unsigned* tmem_slot = (unsigned*)(pv_done + 2);
-  float (*row_ex)[2][128] = (float (*)[2][128])((unsigned char*)bars + 256);   // [tile][half][row]
-  static_assert((1 + 4 * NST2 + 6) * 8 + 4 <= 256, "barriers fit their slot");
+  static_assert((3 + 2 * NKS2 + 8) * 8 + 4 <= 256, "barriers fit their slot");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < NST2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 8); mbar_init(&pv_done[t], 1); }
+    mbar_init(q_full, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    for (int s = 0; s < NKS2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&s_free[t], 4); mbar_init(&p_full[t], 4); mbar_init(&pv_done[t], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -513,7 +518,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int n_a = active_a ? pos_hi_a / BN - tile_first + 1 : 0;              // key tiles of tile A, of tile B
   const int n_b = active_b ? pos_hi_b / BN - tile_first + 1 : 0;
   const int n_tiles = n_b > n_a ? n_b : n_a;
-  constexpr unsigned COL_SA = 0, COL_OA = 256;                                // tile t: + 128 t
 
   if (warp == 0) {
     if (n_tiles > 0) {
@@ -525,32 +529,43 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       const int* table = block_tables + (size_t)b * max_blocks;
       const int boxes = BN / rows_per_box;       // lane i < boxes fetches box i of every tile
+      // The first row of this lane's box of key tile j in the cache tensors.  A page that is not
+      // there: a box beyond the tensor, fetched as zeros.
+      auto box_row = [&](int j) {
+        if (lane >= boxes || j >= n_tiles) return 0;
+        const int pos = (tile_first + j) * BN + lane * rows_per_box;
+        const int blk = pos / page_size;
+        const int page = blk < max_blocks ? table[blk] : -1;
+        return page >= 0 ? (page * nkv + kvh) * page_size + (pos - blk * page_size) : cache_rows;
+      };
+      auto fetch = [&](const CUtensorMap* map, unsigned char* dst, int row, unsigned long long* full) {
+        if (lane == 0) mbar_expect_tx(full, (unsigned)KV_BYTES);
+        __syncwarp();
+        if (lane < boxes)
+          for (int c = 0; c < KCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES + lane * rows_per_box * 128, map, c * 64, row, full);
+      };
+      auto wait_for = [&](unsigned long long* bar, unsigned parity) {
+        int ok = 1;
+        if (lane == 0 && !mbar_wait(bar, parity)) { atomicExch(status, 31); ok = 0; }
+        return __shfl_sync(0xffffffffu, ok, 0) != 0;
+      };
+      // K runs one tile ahead of V: K(0), then K(i + 1) and V(i).  The table entries of a tile are
+      // read one step before they are needed.
+      int row_v = box_row(0), row_k = box_row(1);
+      fetch(&map_k, k_s, row_v, &k_full[0]);
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % NST2;
-        int row = 0;
-        if (lane < boxes) {                      // the box's first row in the cache tensors
-          const int pos = (tile_first + j) * BN + lane * rows_per_box;
-          const int blk = pos / page_size;
-          const int page = blk < max_blocks ? table[blk] : -1;
-          // a page that is not there: a box beyond the tensor, fetched as zeros
-          row = page >= 0 ? (page * nkv + kvh) * page_size + (pos - blk * page_size) : cache_rows;
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int row_next = box_row(i + 2);
+        if (i + 1 < n_tiles) {
+          const int s = (i + 1) % NKS2;
+          if (i + 1 >= NKS2) ok = wait_for(&k_empty[s], (unsigned)(((i + 1) / NKS2) - 1) & 1);
+          if (!ok) break;
+          fetch(&map_k, k_s + (size_t)s * KV_BYTES, row_k, &k_full[s]);
         }
-        for (int kv = 0; kv < 2 && ok; ++kv) {
-          unsigned long long* empty = kv ? &v_empty[s] : &k_empty[s];
-          unsigned long long* full = kv ? &v_full[s] : &k_full[s];
-          if (j >= NST2) {
-            if (lane == 0 && !mbar_wait(empty, (unsigned)((j / NST2) - 1) & 1)) { atomicExch(status, 31); ok = false; }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) break;
-          }
-          if (lane == 0) mbar_expect_tx(full, (unsigned)KV_BYTES);
-          __syncwarp();
-          unsigned char* dst = (kv ? v_s : k_s) + (size_t)s * KV_BYTES;
-          if (lane < boxes)
-            for (int c = 0; c < KCH; ++c)
-              tma_load_2d(dst + c * CHUNK_BYTES + lane * rows_per_box * 128, kv ? &map_v : &map_k, c * 64, row, full);
-        }
+        if (i >= 1) ok = wait_for(v_empty, (unsigned)(i - 1) & 1);
+        if (!ok) break;
+        fetch(&map_v, v_s, row_v, v_full);
+        row_v = row_k; row_k = row_next;
       }
     }
   } else if (warp == 1) {
@@ -561,23 +576,23 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!ok) atomicExch(status, 32);
       zero_spare_rows(q_s, RT);
       zero_spare_rows(q_s + Q_BYTES, RT);
-      auto issue_qk = [&](int t, int j) {        // S_t = Q_t K(j)^T; the caller has waited for K(j)
-        const unsigned char* k_src = k_s + (size_t)(j % NST2) * KV_BYTES;
+      auto issue_qk = [&](int t, int j) {        // S_t = Q_t K(j)^T; K(j) has landed and S_t is free
+        const unsigned char* k_src = k_s + (size_t)(j % NKS2) * KV_BYTES;
 #pragma unroll
         for (int c = 0; c < KCH; ++c) {
           const unsigned long long dq = umma_desc(q_s + t * Q_BYTES + c * CHUNK_BYTES), dk = umma_desc(k_src + c * CHUNK_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + COL_SA + 128 * t, dq + 2 * k, dk + 2 * k, idesc_qk, (c | k) != 0);
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + 128 * t, dq + 2 * k, dk + 2 * k, idesc_qk, (c | k) != 0);
         }
         umma_commit(&s_full[t]);
       };
-      auto issue_pv = [&](int t, int j) {        // O_t += P_t V(j); the caller has waited for P and V(j)
-        const unsigned char* v_src = v_s + (size_t)(j % NST2) * KV_BYTES;
-        const unsigned long long dv = umma_desc_offsets(v_src, CHUNK_BYTES, 1024);
+      auto issue_pv = [&](int t, int j) {        // O_t += P_t V(j); P and V(j) have been waited for
+        const unsigned long long dv = umma_desc_offsets(v_s, CHUNK_BYTES, 1024);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          umma_bf16_a_tmem(tmem_base + COL_OA + 128 * t, tmem_base + COL_SA + 128 * t + kk * 8, dv + (unsigned long long)(kk * 128),
-                           idesc_pv, (j | kk) != 0);
+        for (int kk = 0; kk < BN / 16; ++kk) {   // 16 positions: 32 bytes along a row of P (64 per chunk), 16 rows of V further
+          const unsigned long long dp = umma_desc(p_s + t * P2_BYTES + (kk >> 2) * CHUNK_BYTES) + 2 * (kk & 3);
+          umma_bf16(tmem_base + 256 + 128 * t, dp, dv + (unsigned long long)(kk * 128), idesc_pv, (j | kk) != 0);
+        }
         umma_commit(&pv_done[t]);
       };
       if (ok && !mbar_wait(&k_full[0], 0)) { atomicExch(status, 33); ok = false; }
@@ -588,50 +603,40 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         umma_commit(&k_empty[0]);
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % NST2, s1 = (j + 1) % NST2;
-        bool k_next = false;                     // K(j + 1) has been waited for
-        if (j < n_a) {
-          if (!mbar_wait(&p_full[0], (unsigned)j & 1)) { atomicExch(status, 35); ok = false; break; }
-          if (!mbar_wait(&v_full[s], (unsigned)(j / NST2) & 1)) { atomicExch(status, 36); ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_pv(0, j);
-        }
-        if (j + 1 < n_a) {
-          if (!mbar_wait(&k_full[s1], (unsigned)((j + 1) / NST2) & 1)) { atomicExch(status, 33); ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          k_next = true;
-          issue_qk(0, j + 1);
-        }
-        if (j < n_b) {
-          if (!mbar_wait(&p_full[1], (unsigned)j & 1)) { atomicExch(status, 35); ok = false; break; }
-          if (!mbar_wait(&v_full[s], (unsigned)(j / NST2) & 1)) { atomicExch(status, 36); ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_pv(1, j);
-        }
-        umma_commit(&v_empty[s]);
+        // The next scores first: they wait only for the softmax threads to hold S(j) in registers.
         if (j + 1 < n_tiles) {
-          if (j + 1 < n_b) {
-            if (!k_next && !mbar_wait(&k_full[s1], (unsigned)((j + 1) / NST2) & 1)) { atomicExch(status, 33); ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_qk(1, j + 1);
-          }
-          umma_commit(&k_empty[s1]);
+          if (!mbar_wait(&k_full[(j + 1) % NKS2], (unsigned)((j + 1) / NKS2) & 1)) { atomicExch(status, 33); ok = false; break; }
+          for (int t = 0; t < 2 && ok; ++t)
+            if (j + 1 < (t ? n_b : n_a)) {
+              if (!mbar_wait(&s_free[t], (unsigned)j & 1)) { atomicExch(status, 34); ok = false; break; }
+              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+              issue_qk(t, j + 1);
+            }
+          if (!ok) break;
+          umma_commit(&k_empty[(j + 1) % NKS2]);
         }
+        for (int t = 0; t < 2 && ok; ++t)
+          if (j < (t ? n_b : n_a)) {
+            if (!mbar_wait(&p_full[t], (unsigned)j & 1)) { atomicExch(status, 35); ok = false; break; }
+            if (!mbar_wait(v_full, (unsigned)j & 1)) { atomicExch(status, 36); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_pv(t, j);
+          }
+        if (!ok) break;
+        umma_commit(v_empty);
       }
     }
   } else {
-    // Softmax warps: 2..9 for tile A, 10..17 for tile B; TMEM lane quarter = warp % 4; two threads
-    // per row, the first four warps of a tile taking key columns 0..63 of every key tile (and the
-    // first half of the head dim of O), the other four the rest.
-    const int t = warp >= 10 ? 1 : 0;
-    const int quarter = warp & 3, half = (warp - 2 - 8 * t) >> 2;
+    // Softmax warps: 2..5 for tile A, 6..9 for tile B; TMEM lane quarter = warp % 4; one thread per row.
+    const int t = warp >= 6 ? 1 : 0;
+    const int quarter = warp & 3;
     const int my_tiles = t ? n_b : n_a;
     if (my_tiles > 0) {
       const int row = quarter * 32 + lane;
       const int row_first = t ? first_b : first_a;
       const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
-      const unsigned col_s = COL_SA + 128 * t, col_o = COL_OA + 128 * t;
-      const int bar_id = 1 + 4 * t + quarter;
+      const unsigned col_s = 128 * t, col_o = 256 + 128 * t;
+      unsigned char* p_row = p_s + t * P2_BYTES + row * 128;
       const bool valid = row < RT && row_first + row < rows;
       const int pos = base_pos + (row_first + row) / G;
       const int hi = valid ? pos : -1;
@@ -641,20 +646,23 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int j = 0; j < my_tiles; ++j) {
         if (!mbar_wait(&s_full[t], (unsigned)j & 1)) { if (lane == 0) atomicExch(status, 37); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        unsigned sr[2][32];
-        tmem_ld32_nowait(lane_addr + col_s + half * 64, sr[0]);
-        tmem_ld32_nowait(lane_addr + col_s + half * 64 + 32, sr[1]);
-        tmem_wait_ld();
-        const int key0 = (tile_first + j) * BN + half * 64;
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (!valid || (key0 >= lo && key0 + 63 <= hi)) {
+        unsigned sr[4][32];
 #pragma unroll
-          for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < 4; ++i) tmem_ld32_nowait(lane_addr + col_s + 32 * i, sr[i]);
+        tmem_wait_ld();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[t]);
+        const int key0 = (tile_first + j) * BN;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (!valid || (key0 >= lo && key0 + BN - 1 <= hi)) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[i][c]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 2; ++i)
+          for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
               const int key = key0 + i * 32 + c;
@@ -662,25 +670,37 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[i][c]));
             }
         }
-        // The row's maximum over both halves, through shared memory.  Both threads hold their S in
-        // registers before either passes the first meeting, so the second half may write its P
-        // over the first half's score columns afterwards.
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        row_ex[t][half][row] = mx;
-        asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-        mx = fmaxf(mx, row_ex[t][half ^ 1][row]);
-        asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-        // The reference point m follows the running maximum lazily (see attn_tc_kernel).
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // The reference point m follows the running maximum lazily (see attn_tc_kernel); the warp
+        // decides together, because rescaling O is a warp-wide access to tensor memory.
         const float m_row = fmaxf(m, mx * scale_log2);
         const bool move = m == -INFINITY ? m_row != -INFINITY : m_row - m > 8.0f;
         const bool moved = __any_sync(0xffffffffu, move);
         const float m_new = moved ? m_row : m;
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
         const float corr = ex2_approx(m - m_use);
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        unsigned pr[32];
+        if (j > 0) {
+          // P V(j - 1) has read the P tile that is about to be overwritten, and O is whole again
+          if (!mbar_wait(&pv_done[t], (unsigned)(j - 1) & 1)) { if (lane == 0) atomicExch(status, 38); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (moved) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+              unsigned o[32];
+              tmem_ld32(lane_addr + col_o + c0, o);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+              tmem_st32(lane_addr + col_o + c0, o);
+            }
+            tmem_wait_st();
+          }
+        }
+        // Exponentials, 32 columns at a time, each group packed and stored at once: row `row` of
+        // chunk i / 2 of the P tile, 16-byte piece c at c ^ (row % 8).
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          unsigned pr[16];
 #pragma unroll
           for (int c = 0; c < 32; ++c)
             sr[i][c] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(sr[i][c]), scale_log2, -m_use)));
@@ -689,27 +709,16 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             const float p0 = __uint_as_float(sr[i][c]), p1 = __uint_as_float(sr[i][c + 1]);
             sum4[(c >> 1) & 3] += p0 + p1;
             __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-            pr[i * 16 + (c >> 1)] = *reinterpret_cast<unsigned*>(&h);
+            pr[c >> 1] = *reinterpret_cast<unsigned*>(&h);
           }
+          unsigned char* dst = p_row + (i >> 1) * CHUNK_BYTES;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(dst + ((((i & 1) * 4 + c) ^ (row & 7)) << 4)) = make_uint4(pr[4 * c], pr[4 * c + 1], pr[4 * c + 2], pr[4 * c + 3]);
         }
         l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m = m_new;
-        if (j > 0) {
-          if (!mbar_wait(&pv_done[t], (unsigned)(j - 1) & 1)) { if (lane == 0) atomicExch(status, 38); ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (moved) {
-#pragma unroll 1
-            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
-              unsigned o[32];
-              tmem_ld32(lane_addr + col_o + c0, o);
-#pragma unroll
-              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
-              tmem_st32(lane_addr + col_o + c0, o);
-            }
-          }
-        }
-        tmem_st32(lane_addr + col_s + half * 32, pr);
-        tmem_wait_st();
+        fence_proxy_async();
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[t]);
@@ -718,16 +727,12 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait(&pv_done[t], (unsigned)(my_tiles - 1) & 1)) { if (lane == 0) atomicExch(status, 39); ok = false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
-      // The row's sum: the first half's plus the second's.  (Both threads of a row come here.)
-      row_ex[t][half][row] = l;
-      asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-      l = row_ex[t][0][row] + row_ex[t][1][row];
       if (ok) {
         const float inv = 1.0f / l;
         const int rr = row_first + row;
         bf16* orow = out + (size_t)(tok0 + rr / G) * out_stride + (size_t)(kvh * G + rr % G) * HD;
 #pragma unroll 1
-        for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           unsigned o[32];
           tmem_ld32(lane_addr + col_o + c0, o);     // warp-collective: invalid rows read too, and skip the store
           if (valid) {
@@ -827,7 +832,7 @@ int coheryn_attention_tc_launch(const void* q, long q_stride, int total_tokens, 
     const int pairs = (row_tiles + 1) / 2;
     if (pair_ctas >= (1L << 31)) CO_FAIL("attention_tc: %ld CTAs", pair_ctas);
     dim3 grid2((unsigned)pair_ctas);
-    cudaError_t le2 = co_launch(attn_tc2_kernel, grid2, dim3(576), (size_t)SMEM2_BYTES, stream, mq, mk, mv, (bf16*)out, out_stride,
+    cudaError_t le2 = co_launch(attn_tc2_kernel, grid2, dim3(320), (size_t)SMEM2_BYTES, stream, mq, mk, mv, (bf16*)out, out_stride,
                                 block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size, (int)cache_rows, window, scale_log2,
                                 skip_small, rows_per_box, status, B, pairs);
     if (le2 != cudaSuccess) CO_FAIL("attention_tc: launch failed: %s", cudaGetErrorString(le2));
