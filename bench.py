@@ -453,7 +453,7 @@ def main() -> int:
             "seq_len": args.context, "parallelism": "single-gpu", "layers": L,
             "layers_of_config": SIZES["num_hidden_layers"], "hidden": H, "heads": nh, "kv_heads": nkv,
             "head_dim": hd, "intermediate": I, "vocab": V, "tied_embeddings": True,
-            "context_per_request": "uniform[512,4096]", "mean_context": round(main_run["mean_ctx"], 1),
+            "context_per_request": f"uniform[512,{args.context}]", "mean_context": round(main_run["mean_ctx"], 1),
             "page_size": args.page_size, "cuda_graphs": not args.no_graphs,
             "l2": "weights+cache per step exceed L2 (126 MB)", "peaks": pk["source"],
         },
