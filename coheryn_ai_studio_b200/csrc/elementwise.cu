@@ -240,6 +240,67 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, 
   }
 }
 
+// Many rows (prompt portions): W warps per row (1, 2, 4 or 8: at most 16 float4 per lane), eight warps
+// per CTA, so that a few hundred CTAs hold every row of the step at once, each row's loads are all
+// in flight together and a one-warp row is reduced by shuffles alone.
+template <typename TD, typename TO, typename TW, int VPL, int W>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const int* __restrict__ rows,
+                        const TW* __restrict__ weight, float eps, TO* __restrict__ out, int H, int update, int n_rows) {
+  __shared__ float partial[8];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (8 / W) + warp / W, wsub = warp % W;
+  const bool live = r < n_rows;
+  const size_t src = live ? (rows ? (size_t)rows[r] : (size_t)r) : 0;
+  float* x = resid + src * H;
+  const TD* d = delta ? delta + src * H : nullptr;
+  float4 v[VPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int j = ((i * W + wsub) * 32 + lane) * 4;
+    v[i] = (live && j < H) ? Vec4<float>::load(x + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (d) {
+    float4 dv[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int j = ((i * W + wsub) * 32 + lane) * 4;
+      dv[i] = (live && j < H) ? Vec4<TD>::load(d + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int j = ((i * W + wsub) * 32 + lane) * 4;
+      v[i].x += dv[i].x; v[i].y += dv[i].y; v[i].z += dv[i].z; v[i].w += dv[i].w;
+      if (update && live && j < H) Vec4<float>::store(x + j, v[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  ss = co_warp_sum(ss);
+  if (W > 1) {
+    if (lane == 0) partial[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < W; ++k) ss += partial[(warp / W) * W + k];
+  }
+  if (!live) return;
+  const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* o = out + (size_t)r * H;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int j = ((i * W + wsub) * 32 + lane) * 4;
+    if (j < H) {
+      const float4 w = Vec4<TW>::load(weight + j);
+      Vec4<TO>::store(o + j, make_float4((v[i].x * scale) * w.x, (v[i].y * scale) * w.y, (v[i].z * scale) * w.z,
+                                         (v[i].w * scale) * w.w));
+    }
+  }
+}
+
 // With few rows one CTA per row leaves the GPU idle and the row's latency long: a cluster of
 // four CTAs shares each row (from 1024 columns on, up to 64 rows).
 inline int norm_cluster(int n_rows, int H) { return (n_rows <= 64 && H >= 1024 && (H / 4) % 4 == 0) ? 4 : 1; }
@@ -247,6 +308,22 @@ inline int norm_cluster(int n_rows, int H) { return (n_rows <= 64 && H >= 1024 &
 template <typename TD, typename TO, typename TW>
 void launch_rmsnorm_vec(float* resid, const void* delta, const int* rows, const void* weight, float eps, void* out,
                         int n_rows, int H, int update, cudaStream_t stream) {
+  if (n_rows > 64) {
+    // warps per row and float4 per lane: the fewest warps that keep a lane at 16 float4 or fewer
+    int W = 1;
+    while (W < 8 && (H / 4 + 32 * W - 1) / (32 * W) > 16) W *= 2;
+    const int vpl = (H / 4 + 32 * W - 1) / (32 * W);
+    const dim3 grid((n_rows + 8 / W - 1) / (8 / W));
+#define ROWS(V, WW) co_launch(add_rmsnorm_rows_kernel<TD, TO, TW, V, WW>, grid, dim3(256), 0, stream, resid, (const TD*)delta, rows, \
+                              (const TW*)weight, eps, (TO*)out, H, update, n_rows)
+#define ROWS_W(WW) do { if (vpl <= 4) ROWS(4, WW); else if (vpl <= 8) ROWS(8, WW); else if (vpl <= 12) ROWS(12, WW); else ROWS(16, WW); } while (0)
+    if (vpl <= 16) {
+      if (W == 1) ROWS_W(1); else if (W == 2) ROWS_W(2); else if (W == 4) ROWS_W(4); else ROWS_W(8);
+      return;
+    }
+#undef ROWS_W
+#undef ROWS
+  }
   const int cl = norm_cluster(n_rows, H);
   const int steps = (H / 4 / cl + 255) / 256;
 #define GO(S) co_launch_cluster(cl, add_rmsnorm_vec_kernel<TD, TO, TW, S>, dim3(n_rows * cl), dim3(256), 0, stream, resid, \

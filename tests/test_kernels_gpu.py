@@ -93,6 +93,36 @@ def test_add_rmsnorm(H, dtype):
     assert ref.shape == (7, H)
 
 
+@pytest.mark.parametrize("H", [64, 520, 1536, 3584, 5120, 8192])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm_many_rows(H, dtype):
+    """More than 64 rows: one, two, four or eight warps per row (by the width), eight warps per CTA; a row
+    count that does not fill the last CTA, rows gathered, the residual updated in float32."""
+    n = 203
+    rng = np.random.default_rng(H + 1)
+    resid = rng.standard_normal((n, H)).astype(np.float32) * 3
+    delta = rng.standard_normal((n, H)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    d_dev = t32(delta).to(dtype)
+    x = resid + d_dev.float().cpu().numpy()
+    ref = plain.rms_norm(x, w, 1e-6)
+    r_dev = t32(resid)
+    out = torch.full((n, H), 7.0, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(r_dev, d_dev, t32(w), 1e-6, out)
+    tol = 2e-6 * np.abs(ref).max() if dtype == torch.float32 else 2 ** -8 * np.abs(ref).max()
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
+    assert np.abs(r_dev.cpu().numpy() - x).max() == 0.0
+    # gathered rows, no delta: the residual stays as it is
+    pick = rng.permutation(n)[:100].astype(np.int32)
+    r_dev = t32(resid)
+    out2 = torch.empty(100, H, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(r_dev, None, t32(w), 1e-6, out2, rows=t32(pick))
+    ref2 = plain.rms_norm(resid[pick], w, 1e-6)
+    tol = 2e-6 * np.abs(ref2).max() if dtype == torch.float32 else 2 ** -8 * np.abs(ref2).max()
+    assert np.abs(out2.float().cpu().numpy() - ref2).max() <= tol
+    assert torch.equal(r_dev, t32(resid))
+
+
 @pytest.mark.parametrize("shape", [(1, 50, 37), (5, 129, 200), (67, 96, 1000), (130, 300, 77)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gemm_simt(shape, dtype):
