@@ -1,8 +1,8 @@
 // out[M, N] = x[M, K] . W[N, K]^T (+ bias | gated SiLU) for FEW rows (decode batches, short
-// prompt portions: M <= 64) in bfloat16 on the 5th-generation tensor cores.  The product is
+// prompt portions: M <= 256) in bfloat16 on the 5th-generation tensor cores.  The product is
 // bound by reading W once, so the operands swap places: the OUTPUT FEATURES sit on the 128
 // lanes of the accumulator in tensor memory (W tile 128 x 64 = operand A) and the tokens on
-// its BT columns (x tile BT x 64 = operand B, BT = 16, 32 or 64).  No lane is wasted on
+// its BT columns (x tile BT x 64 = operand B, BT = 16, 32, 64, 128 or 256).  No lane is wasted on
 // padding rows, and the weight stream is moved by TMA alone: 16 KB per copy, STAGES copies
 // in flight per CTA, no thread computes an address.
 //
@@ -113,6 +113,43 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const bool waited = mbar_wait(accum_full, 0);
     if (!waited && lane == 0) atomicExch(status, 13);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if constexpr (BT > 64) {
+      // Many token columns: sixteen at a time from tensor memory straight to their destination.  K
+      // slices are always left to the consumer here (the host refuses anything else).
+      const int n_out = N >> 1;
+      const float bv = (n < N && bias && (splits == 1 || blockIdx.y == 0)) ? co_load_any(bias, bias_dtype, n) : 0.f;
+      float* mine = (float*)out + (size_t)blockIdx.y * M * N + n;
+      for (int c0 = 0; c0 < BT && c0 < M && waited; c0 += 16) {
+        unsigned r[16];
+        tmem_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+        if (splits > 1) {
+          if (n < N)
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < M) mine[(size_t)(c0 + j) * N] = __uint_as_float(r[j]) + bv;
+        } else if (epilogue == EPI_GATED_SILU) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g = __uint_as_float(r[j]);
+            const float other = __shfl_xor_sync(0xffffffffu, g, 1);
+            if (c0 + j < M && !(lane & 1) && n + 1 < N && (n >> 1) < n_out) {
+              const float y = __fdividef(g, 1.0f + __expf(-g)) * other;
+              const size_t o = (size_t)(c0 + j) * ldo + (n >> 1);
+              if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(y);
+              else ((float*)out)[o] = y;
+            }
+          }
+        } else if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < M) {
+              const size_t o = (size_t)(c0 + j) * ldo + n;
+              if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(__uint_as_float(r[j]) + bv);
+              else ((float*)out)[o] = __uint_as_float(r[j]) + bv;
+            }
+        }
+      }
+    } else {
     float v[BT];
     if (waited) {
 #pragma unroll
@@ -195,6 +232,7 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
       }
     }
+    }   // BT <= 64
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -259,7 +297,7 @@ CO_EXPORT long coheryn_gemm_tc_few_workspace_floats(int M, int N, int K) {
 // The number of K splits of this shape (1: none).
 CO_EXPORT int coheryn_gemm_tc_few_splits(int N, int K) { return (N <= 0 || K <= 0) ? 1 : few_splits(N, K); }
 
-// x: [M, K] bfloat16 with row stride ldx, M <= 64; w: [N, K] bfloat16 contiguous; K and ldx
+// x: [M, K] bfloat16 with row stride ldx, M <= 256 (above 64 rows a product whose K is cut needs defer = 1); w: [N, K] bfloat16 contiguous; K and ldx
 // multiples of 8, bases 16-byte aligned.  epilogue 0: out[M, N] (+ bias); 1: gated SiLU over
 // interleaved rows of w, out[M, N/2].  status: device word that receives 11/12/13 if a
 // bounded wait of the producer / the MMA issuer / the epilogue ran out.  workspace: see above.
@@ -270,7 +308,7 @@ CO_EXPORT int coheryn_gemm_bf16_tc_few(const void* x, const void* w, const void*
                                        int* status, float* workspace, long workspace_floats, int defer,
                                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 64) CO_FAIL("gemm_bf16_tc_few: M = %d exceeds 64", M);
+  if (M > 256) CO_FAIL("gemm_bf16_tc_few: M = %d exceeds 256", M);
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc_few: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc_few: operands must be 16-byte aligned");
   if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc_few: gated epilogue needs an even number of rows");
@@ -279,7 +317,9 @@ CO_EXPORT int coheryn_gemm_bf16_tc_few(const void* x, const void* w, const void*
   if (defer && (epilogue != 0 || out_dtype != CO_F32)) CO_FAIL("gemm_bf16_tc_few: deferred splits are float32 and take no gate");
   if (splits > 1 && !defer && (!workspace || workspace_floats < coheryn_gemm_tc_few_workspace_floats(M, N, K)))
     CO_FAIL("gemm_bf16_tc_few: the workspace of %ld floats is too small for M=%d N=%d K=%d", workspace_floats, M, N, K);
-  const int bt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const int bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+  if (bt > 64 && splits > 1 && !defer)
+    CO_FAIL("gemm_bf16_tc_few: with more than 64 rows the K slices of N=%d K=%d have to be left to the consumer", N, K);
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, N, K, K, BF) || !make_map(&mx, x, M, K, ldx, bt))
     CO_FAIL("gemm_bf16_tc_few: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%ld)", M, N, K, ldx);
@@ -292,7 +332,9 @@ CO_EXPORT int coheryn_gemm_bf16_tc_few(const void* x, const void* w, const void*
   if (bt == 16) GO(16, 5);
   if (bt == 32 && one_wave) GO(32, 7);
   if (bt == 32) GO(32, 5);
-  if (one_wave) GO(64, 7);
-  GO(64, 4);
+  if (bt == 64 && one_wave) GO(64, 7);
+  if (bt == 64) GO(64, 4);
+  if (bt == 128) GO(128, 6);     // 32 KB per stage
+  GO(256, 4);                    // 48 KB per stage
 #undef GO
 }

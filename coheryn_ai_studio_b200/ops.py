@@ -278,6 +278,9 @@ def seeded_fill(out: torch.Tensor, key: int, first: int, mean: float, deviation:
 # Up to this many rows a q/k/v product whose K the many-rows kernel splits leaves the addition of
 # its slices to the rotation kernel (one kernel less between the product and the attention).
 QKV_PARTS_M = int(os.environ.get("COHERYN_QKV_PARTS_M", "256"))
+# ... by the few-rows product above this many rows (up to FEW_DEFER_M), by the many-rows product otherwise
+# (at 64 rows the latter is 2 % of a decode step faster).
+QKV_PARTS_FEW_FROM = 64
 
 
 def qkv_parts_count(x, w_qkv, k_cache, rotary_dim: int, head_dim: int) -> int:
@@ -288,13 +291,17 @@ def qkv_parts_count(x, w_qkv, k_cache, rotary_dim: int, head_dim: int) -> int:
             and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w_qkv.is_contiguous()
             and w_qkv.data_ptr() % 16 == 0):
         return 0
+    few = few_splits(w_qkv.shape[0], K)           # the few-rows product (weights streamed once) where it cuts K
+    if few > 1 and QKV_PARTS_FEW_FROM < M <= FEW_DEFER_M:
+        return few
     return int(core().coheryn_gemm_tc_parts_count(c_int(M), c_int(w_qkv.shape[0]), c_int(K)))
 
 
 def qkv_rope_parts(x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], positions: torch.Tensor,
                    cos_sin: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                    num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, count: int) -> torch.Tensor:
-    """q, k, v = x @ w_qkv.T (+ b) by the many-rows product with K cut into ``count`` slices, whose
+    """q, k, v = x @ w_qkv.T (+ b) by the few-rows product (or, where that does not cut K, the many-rows
+    product) with K cut into ``count`` slices, whose
     addition, the bias, the rotation of q and k and the cache write of k and v happen in ONE following
     kernel (see ``rope_kv_write``).  Returns the rotated q ``[T, num_heads * head_dim]``."""
     _dev(x, w_qkv, b_qkv, positions, cos_sin, slots, k_cache, v_cache)
@@ -306,8 +313,11 @@ def qkv_rope_parts(x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.T
     assert k_cache.is_contiguous() and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
     lib = core()
     parts = torch.empty((count, T, N), dtype=torch.float32, device=x.device)
-    _check(lib, lib.coheryn_gemm_bf16_tc_parts(_ptr(x), _ptr(w_qkv), _ptr(parts), c_int(T), c_int(N), c_int(K),
-                                               c_long(x.stride(0)), _ptr(tc_status(x.device)), _stream()))
+    if count == few_splits(N, K):
+        gemm_bf16_tc_few(x, w_qkv, None, parts, defer=True)
+    else:
+        _check(lib, lib.coheryn_gemm_bf16_tc_parts(_ptr(x), _ptr(w_qkv), _ptr(parts), c_int(T), c_int(N), c_int(K),
+                                                   c_long(x.stride(0)), _ptr(tc_status(x.device)), _stream()))
     q = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
     _check(lib, lib.coheryn_rope_kv_write_parts(
         _ptr(parts), c_int(count), c_long(T * N), _ptr(b_qkv), c_int(_code(b_qkv) if b_qkv is not None else F32), _ptr(q),
@@ -553,8 +563,14 @@ def gemm_bf16_tc_few(x, w, bias, out, gated: int = 0, defer: bool = False) -> No
 # add its own splits goes to the mma.sync kernel instead: measured on a B200, the in-kernel
 # addition through memory costs several dependent round trips.
 FEW_M = int(os.environ.get("COHERYN_FEW_M", "32"))
-# ... and up to this many rows the products whose K slices the consumer adds.
-FEW_DEFER_M = int(os.environ.get("COHERYN_FEW_DEFER_M", "64"))
+# ... and up to this many rows the products whose K slices the consumer adds.  The kernel takes up to
+# 256 rows, but every CTA re-reads all rows of x beside its weight tile, and from 129 rows on that costs
+# what the many-rows kernel with its extra kernel for the K slices costs (1.5B sizes, down projection:
+# 128 rows 15.9 -> 12.7 us, 256 rows 21.1 -> 18.8; a decode step at batch 128 3.64 -> 3.45 ms, at 256 no change).
+FEW_DEFER_M = int(os.environ.get("COHERYN_FEW_DEFER_M", "128"))
+# The output head (a very large weight) takes the few-rows product up to this many rows only: every CTA
+# re-reads all rows of x, which beyond that costs more than the weight stream.
+FEW_HEAD_M = 64
 
 
 # A product hands its K slices to the consumer only from this K on.  Measured on a B200 at 8
@@ -567,12 +583,12 @@ DEFER_MIN_K_WIDE = int(os.environ.get("COHERYN_DEFER_MIN_K_WIDE", "1024"))
 
 
 # A weight matrix of at least this many elements (the output head over a large vocabulary) goes
-# through the few-rows product up to FEW_DEFER_M rows: its stream is all that matters there.
+# through the few-rows product up to FEW_HEAD_M rows: its stream is all that matters there.
 FEW_LARGE_WEIGHT = 128 << 20
 
 
 def _few_ok(x, w, partial_ok: bool = False) -> bool:
-    if not _few_shape_ok(x, w, FEW_DEFER_M if w.numel() >= FEW_LARGE_WEIGHT else None):
+    if not _few_shape_ok(x, w, FEW_HEAD_M if w.numel() >= FEW_LARGE_WEIGHT else None):
         return False
     return partial_ok or few_splits(w.shape[0], w.shape[1]) == 1
 

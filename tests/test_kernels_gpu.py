@@ -176,7 +176,8 @@ def test_gemm_bf16_small(shape, gated):
 
 @pytest.mark.parametrize("shape", [(1, 256, 1536), (8, 2048, 1536), (16, 17920, 1536), (5, 100, 72), (9, 50, 40),
                                    (17, 1536, 8960), (33, 300, 520), (64, 1536, 1536), (64, 151936, 64),
-                                   (40, 2048, 1536), (3, 1000, 96), (2, 136, 4104)])
+                                   (40, 2048, 1536), (3, 1000, 96), (2, 136, 4104), (100, 17920, 1536), (128, 1536, 8960),
+                                   (200, 2048, 1536), (256, 300, 520), (65, 100, 72)])
 @pytest.mark.parametrize("gated", [False, True])
 def test_gemm_bf16_tc_few(shape, gated):
     """The few-rows tcgen05 kernel (features on the accumulator's lanes, K split over CTAs
@@ -187,7 +188,10 @@ def test_gemm_bf16_tc_few(shape, gated):
     x = t32(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
     w = t32((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
     acc = x.double().cpu() @ w.double().cpu().T
-    if gated:
+    if gated and M > 64 and ops().few_splits(N, K) > 1:
+        with pytest.raises(Exception, match="left to the consumer"):
+            ops().gemm_bf16_tc_few(x, w, None, torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV), gated=True)
+    elif gated:
         g, u = acc[:, 0::2], acc[:, 1::2]
         ref = g / (1 + torch.exp(-g)) * u
         out = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
@@ -197,6 +201,20 @@ def test_gemm_bf16_tc_few(shape, gated):
         again = torch.full_like(out, 3.0)
         ops().gemm_bf16_tc_few(x, w, None, again, gated=True)
         assert torch.equal(out, again)
+    elif M > 64 and ops().few_splits(N, K) > 1:
+        # more than 64 rows: a product whose K is cut leaves its slices to the consumer, or is refused
+        b = t32(rng.standard_normal(N).astype(np.float32))
+        ref = acc + b.double().cpu()
+        S = ops().few_splits(N, K)
+        parts = torch.full((S, M, N), 7.0, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc_few(x, w, b, parts, defer=True)
+        ops().check_tc_status(DEV)
+        assert (parts.double().sum(0).cpu() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+        alone = torch.empty(S, 1, N, dtype=torch.float32, device=DEV)
+        ops().gemm_bf16_tc_few(x[M - 1:], w, b, alone, defer=True)
+        assert torch.equal(alone[:, 0], parts[:, M - 1])        # the same bits as inside the batch
+        with pytest.raises(Exception, match="left to the consumer"):
+            ops().gemm_bf16_tc_few(x, w, b, torch.empty(M, N, dtype=torch.float32, device=DEV))
     else:
         b = t32(rng.standard_normal(N).astype(np.float32))
         ref = acc + b.double().cpu()
