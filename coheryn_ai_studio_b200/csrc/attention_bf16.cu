@@ -33,8 +33,9 @@
 namespace {
 constexpr int HD = CO_HEAD_DIM;
 constexpr int LDS = HD + 8;       // shared-memory row stride: 16 bytes of padding keep ldmatrix conflict-free
-constexpr int SPLIT_MIN = 128;    // positions per CTA of attn_stream: one of 128, 256, 512
-constexpr int SPLIT_MAX = 512;
+constexpr int SPLIT_MIN = 128;    // positions per CTA of attn_stream: a power of two from 128 to 2048
+constexpr int SPLIT_MAX = 2048;
+constexpr int SPLIT_PAGES = 258;  // block-table entries a CTA keeps: a split spans at most 256 pages (+ 2)
 constexpr int CHUNKS = HD / 8;    // 16-byte pieces per row
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
 
@@ -505,7 +506,7 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
                    int split, int settled) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long long rowoff[SSTAGES][STILE];   // element offset of a tile's rows in a cache tensor, -1: not read
-  __shared__ int pages_s[SPLIT_MAX / 2 + 2];     // block-table entries of the split's pages (pages of one position: splits of at most 256)
+  __shared__ int pages_s[SPLIT_PAGES];           // block-table entries of the split's pages
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][LDS]
   bf16* ring = Qs + 16 * LDS;                                   // [SSTAGES][K, V][STILE][LDS]
   float* merge = reinterpret_cast<float*>(ring);               // reused after the tiles: [4][16][PART]
@@ -749,16 +750,25 @@ int split_keys(int B, int nkv, int max_kv_len, int page_size) {
   if (g_forced_split < 0) {
     const char* e = getenv("COHERYN_ATTN_SPLIT");
     const int v = e ? atoi(e) : 0;
-    g_forced_split = (v == 128 || v == 256 || v == 512) ? v : 0;
+    g_forced_split = (v == 128 || v == 256 || v == 512 || v == 1024 || v == 2048) ? v : 0;
   }
-  const int cap = page_size >= 2 ? SPLIT_MAX : SPLIT_MAX / 2;   // the kernel keeps split / page_size + 2 table entries
+  int cap = SPLIT_MAX;                                    // the kernel keeps split / page_size + 2 table entries
+  while (cap > SPLIT_MIN && cap / page_size + 2 > SPLIT_PAGES) cap >>= 1;
   if (g_forced_split) return g_forced_split < cap ? g_forced_split : cap;
-  // Measured at batch 4 to 64 with contexts up to 4,096: the largest split fills the resident slots
-  // outright; the middle one already pays at four fifths of them (batch 8: 256 positions per CTA and
-  // half as many partial results to merge beat 128 by 2.4 %).
+  // Measured at batch 4 to 256 with contexts of 4,096 to 32,768 (lengths uniform up to the bound, so about
+  // two thirds of the counted CTAs have keys).  1,024 positions per CTA pay where those CTAs either all fit
+  // the three resident slots per SM of the shallow ring at once or queue up four deep and more (batch 64 at
+  // 4,096: 2.59 -> 2.48 ms per step; batch 16 at 16,384: 2.28 -> 2.11; batch 256: 5.74 -> 5.59), not in
+  // between, where the second round is half empty (batch 128: 3.45 -> 3.56), and not below (batch 4 at
+  // 32,768: 1.72 -> 1.87); 2,048 never paid.  512 when they fill the two slots per SM of the deep ring; 256
+  // already at four fifths of those (batch 8: half as many partial results to merge beat 128 by 2.4 %).
   const long slots = (stream_smem(3) + 4 * 1024 <= 227 * 1024 / 2 ? 2 : 1) * 148L;
-  for (int s = cap; s > SPLIT_MIN; s >>= 1)
-    if ((long)B * nkv * ((max_kv_len + s - 1) / s) >= (s == SPLIT_MAX ? slots : slots * 4 / 5)) return s;
+  if (cap >= 1024) {
+    const long wide = (long)B * nkv * ((max_kv_len + 1023) / 1024);
+    if ((wide >= 3 * 148L && wide <= 640) || wide >= 12 * 148L) return 1024;
+  }
+  for (int s = cap < 512 ? cap : 512; s > SPLIT_MIN; s >>= 1)
+    if ((long)B * nkv * ((max_kv_len + s - 1) / s) >= (s >= 512 ? slots : slots * 4 / 5)) return s;
   return SPLIT_MIN;
 }
 
@@ -989,7 +999,9 @@ CO_EXPORT int coheryn_attn_split_keys() { return SPLIT_MIN; }
 // keys = 128, 256 or 512 fixes the positions per CTA of the decode kernel; 0 restores the choice by batch size.
 CO_EXPORT void coheryn_attn_set_tc_cluster(int cluster) { coheryn_attention_tc_set_cluster(cluster); }
 CO_EXPORT void coheryn_attn_set_tc_two_tiles(int mode) { coheryn_attention_tc_set_two_tiles(mode); }
-CO_EXPORT void coheryn_attn_set_split(int keys) { g_forced_split = (keys == 128 || keys == 256 || keys == 512) ? keys : 0; }
+CO_EXPORT void coheryn_attn_set_split(int keys) {
+  g_forced_split = (keys == 128 || keys == 256 || keys == 512 || keys == 1024 || keys == 2048) ? keys : 0;
+}
 
 // Floats of scratch that coheryn_attention_bf16 needs for B requests of at most
 // max_kv_len positions when some request takes the split path.

@@ -676,8 +676,8 @@ def attention_lib(head_dim: int):
 
 
 def set_attention_split(head_dim: int, keys: int) -> None:
-    """Fix the positions per CTA of the decode attention kernel for this head size (128, 256
-    or 512); 0 restores the choice by batch size.  For tests and experiments."""
+    """Fix the positions per CTA of the decode attention kernel for this head size (a power of two
+    from 128 to 2048, capped at 256 pages); 0 restores the choice by batch size and context.  For tests and experiments."""
     attention_lib(head_dim).coheryn_attn_set_split(c_int(keys))
 
 

@@ -561,16 +561,16 @@ def test_qkv_product_with_rotation_and_cache_write(nh, nkv, hd, K, page, T):
     assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
 
 
-@pytest.mark.parametrize("split", [128, 256, 512, 0])
-@pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 64), (3, 1, 32, 16), (14, 2, 64, 8)])
+@pytest.mark.parametrize("split", [128, 256, 512, 1024, 2048, 0])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 64), (3, 1, 32, 16), (14, 2, 64, 8), (4, 2, 16, 2)])
 def test_decode_attention_split_sizes(split, nh, nkv, hd, page):
-    """The decode kernel at each of its split sizes: lengths around tile (64) and split edges,
-    two-token tails, and windows that begin inside a tile and inside a split."""
+    """The decode kernel at each of its split sizes (pages of two positions cap the split at 512): lengths
+    around tile (64) and split edges, two-token tails, and windows that begin inside a tile and inside a split."""
     rng = np.random.default_rng(split + hd)
-    lens = [1, 63, 64, 65, 129, 511, 512, 513, 700, 1300]
+    lens = [1, 63, 64, 65, 129, 511, 512, 513, 700, 1300, 2049, 2500]
     dtype = torch.bfloat16
     kc, vc, bt, ks, vs = paged_setup(rng, lens, nkv, hd, page, dtype)
-    q_lens = [1, 1, 1, 2, 1, 1, 2, 1, 1, 1] if (nh // nkv) * 2 <= 16 else [1] * len(lens)
+    q_lens = [1, 1, 1, 2, 1, 1, 2, 1, 1, 1, 2, 1] if (nh // nkv) * 2 <= 16 else [1] * len(lens)
     reqs, poss = [], []
     for b, (n, ql) in enumerate(zip(lens, q_lens)):
         ql = min(ql, n)
