@@ -820,9 +820,13 @@ int coheryn_attention_tc_launch(const void* q, long q_stride, int total_tokens, 
   if (g_two_tiles < 0) { const char* e = getenv("COHERYN_ATTN_TC_TWO"); g_two_tiles = e ? (e[0] == '0' ? 0 : e[0] == '1' ? 1 : 2) : 2; }
   // Two row tiles per CTA (every key tile fetched once for 256 rows) once the pairs still fill the
   // GPU with a quarter to spare: measured at 12 query heads in 2 groups, 4,096 tokens (196 CTAs)
-  // 100 against 109 us, 16,384 tokens 0.98 against 1.25 ms, but 2,048 tokens (98 CTAs) 55 against 37.
+  // 96 against 109 us, 16,384 tokens 0.91 against 1.25 ms, but 2,048 tokens (98 CTAs) 53 against 37.
+  // A portion at the end of a long context has few row tiles and many key tiles each; there the pairs
+  // pay from somewhat over half the SMs on (2,048 tokens after 14,336: 98 CTAs, 331 against 405 us;
+  // 40 heads in 8 groups, 512 tokens after 15,872: 88 CTAs, 326 against 448; but 60 CTAs: 317 against 227).
   const long pair_ctas = (long)((row_tiles + 1) / 2) * nkv * B;
-  if (TWO_OK && cluster == 1 && row_tiles >= 2 && (g_two_tiles == 1 || (g_two_tiles == 2 && pair_ctas >= 185))) {
+  const bool pairs_pay = pair_ctas >= 185 || (pair_ctas >= 84 && key_tiles >= 48);
+  if (TWO_OK && cluster == 1 && row_tiles >= 2 && (g_two_tiles == 1 || (g_two_tiles == 2 && pairs_pay))) {
     static bool configured2 = false;
     if (!configured2) {
       cudaError_t e = cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
