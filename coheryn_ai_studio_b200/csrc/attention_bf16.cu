@@ -497,7 +497,7 @@ static_assert((size_t)4 * 16 * PART * sizeof(float) <= (size_t)2 * 2 * STILE * L
               "the merge area fits the ring");
 static_assert(stream_smem(3) + 6 * 1024 <= 227 * 1024, "the ring fits shared memory at every head size");
 
-template <int SSTAGES>
+template <int SSTAGES, bool PER_WARP = false>
 __global__ void __launch_bounds__(128)
 attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict__ scratch, int max_splits,
                    const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -608,6 +608,21 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
   st[0].m[0] = st[0].m[1] = -INFINITY;
   st[0].l[0] = st[0].l[1] = 0.f;
 
+  if constexpr (PER_WARP) {
+    // At most SSTAGES tiles, all of them requested by now: every warp takes a whole tile of its own (eight
+    // independent accumulators in Q K^T instead of two), so the tiles are worked on side by side.
+    cp_async_wait<0>();
+    __syncthreads();
+    const int i = t_first + warp;
+    const int key0 = c0 + i * STILE;
+    if (i < t_end && key0 < hi_key && key0 + STILE > lo_key) {
+      const bf16* Ks = stage_of(i);
+      if (key0 >= all_lo && key0 + STILE - 1 <= all_hi)
+        attend_tile<1, STILE, false, false>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
+      else
+        attend_tile<1, STILE, false, true>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
+    }
+  } else {
 #pragma unroll 1
   for (int i = t_first; i < t_end; ++i) {
     // Tile i is group i - t_first; groups complete in order.
@@ -623,6 +638,7 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
       else
         attend_tile<1, 16, false, true>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
     }
+  }
   }
   cp_async_wait<0>();
   __syncthreads();   // all warps are done with their tiles: the ring becomes the merge area
@@ -745,12 +761,19 @@ static_assert((size_t)(KG - 1) * 4 * 16 * (HD + 2) * sizeof(float) <= (size_t)4 
 // Positions per CTA of attn_stream.  coheryn_attn_set_split (or COHERYN_ATTN_SPLIT = 128 |
 // 256 | 512 in the environment, read at first use) fixes it; otherwise the largest of the
 // three whose grid still fills the GPU (two CTAs per SM), else the smallest.
+// COHERYN_ATTN_PER_WARP=0 switches the tile-per-warp variant (and the split of 192 positions chosen for it) off.
+bool per_warp_on() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("COHERYN_ATTN_PER_WARP"); on = (e && e[0] == '0') ? 0 : 1; }
+  return on != 0;
+}
+
 int g_forced_split = -1;
 int split_keys(int B, int nkv, int max_kv_len, int page_size) {
   if (g_forced_split < 0) {
     const char* e = getenv("COHERYN_ATTN_SPLIT");
     const int v = e ? atoi(e) : 0;
-    g_forced_split = (v == 128 || v == 256 || v == 512 || v == 1024 || v == 2048) ? v : 0;
+    g_forced_split = (v == 128 || v == 192 || v == 256 || v == 512 || v == 1024 || v == 2048) ? v : 0;
   }
   int cap = SPLIT_MAX;                                    // the kernel keeps split / page_size + 2 table entries
   while (cap > SPLIT_MIN && cap / page_size + 2 > SPLIT_PAGES) cap >>= 1;
@@ -768,11 +791,18 @@ int split_keys(int B, int nkv, int max_kv_len, int page_size) {
     if ((wide >= 3 * 148L && wide <= 640) || wide >= 12 * 148L) return 1024;
   }
   for (int s = cap < 512 ? cap : 512; s > SPLIT_MIN; s >>= 1)
-    if ((long)B * nkv * ((max_kv_len + s - 1) / s) >= (s >= 512 ? slots : slots * 4 / 5)) return s;
+    if ((long)B * nkv * ((max_kv_len + s - 1) / s) >= (s >= 512 ? slots : slots * 4 / 5)) {
+      // Where 256 positions would be chosen, 192 are three tiles that three warps work on side by side
+      // (see attn_stream_kernel), as long as the CTAs counted from the context bound still about fit the
+      // resident slots: batch 8 with contexts uniform up to 4,096: 1.345 -> 1.29 ms per step; every context
+      // at 2,000: 1.330 -> 1.285; every context at 3,900 (more CTAs than slots): 1.405 -> 1.442.
+      if (s == 256 && cap >= 192 && per_warp_on() && (long)B * nkv * ((max_kv_len + 191) / 192) <= slots * 6 / 5) return 192;
+      return s;
+    }
   return SPLIT_MIN;
 }
 
-template <int SSTAGES>
+template <int SSTAGES, bool PER_WARP = false>
 int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_stride, float* scratch, int max_splits,
                          const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks,
                          const int* cu_q, const int* kv_lens, int nh, int nkv, int page_size, int window,
@@ -780,11 +810,11 @@ int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_s
   constexpr size_t SMEM = stream_smem(SSTAGES);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_stream_kernel<SSTAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_stream_kernel<SSTAGES, PER_WARP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
     if (e != cudaSuccess) CO_FAIL("attention_bf16: %zu bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
     configured = true;
   }
-  co_launch(attn_stream_kernel<SSTAGES>, grid, dim3(128), SMEM, stream, (const bf16*)q, q_stride, scratch, max_splits,
+  co_launch(attn_stream_kernel<SSTAGES, PER_WARP>, grid, dim3(128), SMEM, stream, (const bf16*)q, q_stride, scratch, max_splits,
             (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
             window, scale_log2, split, settled);
   CO_CHECK_LAUNCH("attn_stream");
@@ -971,6 +1001,10 @@ int launch_stream_splits(const void* q, long q_stride, const void* k_cache, cons
   const bool shallow = forced_stages ? forced_stages == 2 : (long)B * nkv * ((max_kv_len + split - 1) / split) > 3 * 148L;
   *split_out = split;
   *max_splits_out = max_splits;
+  // Splits of three tiles: a tile per warp, all three resident in the deep ring (two CTAs per SM).
+  if (split == 3 * STILE && !forced_stages && per_warp_on())
+    return launch_stream_kernel<3, true>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache, block_tables,
+                                         max_blocks, cu_q, kv_lens, nh, nkv, page_size, window, scale_log2, split, settled);
   return shallow ? launch_stream_kernel<2>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache, block_tables,
                                            max_blocks, cu_q, kv_lens, nh, nkv, page_size, window, scale_log2, split, settled)
                  : launch_stream_kernel<3>(grid, stream, q, q_stride, scratch, max_splits, k_cache, v_cache, block_tables,

@@ -561,7 +561,7 @@ def test_qkv_product_with_rotation_and_cache_write(nh, nkv, hd, K, page, T):
     assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
 
 
-@pytest.mark.parametrize("split", [128, 256, 512, 1024, 2048, 0])
+@pytest.mark.parametrize("split", [128, 192, 256, 512, 1024, 2048, 0])
 @pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 64), (3, 1, 32, 16), (14, 2, 64, 8), (4, 2, 16, 2)])
 def test_decode_attention_split_sizes(split, nh, nkv, hd, page):
     """The decode kernel at each of its split sizes (pages of two positions cap the split at 512): lengths
