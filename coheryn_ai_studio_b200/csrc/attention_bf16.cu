@@ -649,13 +649,12 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
     float l = st[0].l[h];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (r >= rows) continue;            // rows without a query are not merged
     float* dst = merge + ((size_t)warp * 16 + r) * PART;
-    if (t == 0) { dst[0] = st[0].m[h]; dst[1] = l; }
+    if (t == 0) *reinterpret_cast<float2*>(dst) = make_float2(st[0].m[h], l);
 #pragma unroll
-    for (int dt = 0; dt < HD / 8; ++dt) {
-      dst[2 + dt * 8 + 2 * t] = o[0][dt][2 * h];
-      dst[2 + dt * 8 + 2 * t + 1] = o[0][dt][2 * h + 1];
-    }
+    for (int dt = 0; dt < HD / 8; ++dt)
+      *reinterpret_cast<float2*>(dst + 2 + dt * 8 + 2 * t) = make_float2(o[0][dt][2 * h], o[0][dt][2 * h + 1]);
   }
   __syncthreads();
   // Merge the four warps in warp order; write the valid rows.
