@@ -309,11 +309,12 @@ def main() -> int:
     sampler = ClockSampler()
     sampler.start()
 
-    def make_engine(batch):
+    def make_engine(batch, context=None):
         margin = 2 * total_steps + 8
-        eng = Engine(model, dtype="bfloat16", context=args.context, max_num_seqs=batch,
+        context = context or args.context
+        eng = Engine(model, dtype="bfloat16", context=context, max_num_seqs=batch,
                      max_num_batched_tokens=max(2048, args.prefill_tokens), page_size=args.page_size,
-                     kv_cache_tokens=batch * (args.context + 64), prefix_reuse=False,
+                     kv_cache_tokens=batch * (context + 64), prefix_reuse=False,
                      use_graphs=not args.no_graphs)
         for g in eng.cache.groups:
             g.tensor.normal_(0.0, 1.0)
@@ -397,7 +398,7 @@ def main() -> int:
                 "d2h_bytes_per_step": d2h // steps, "ms_per_step": dt / steps * 1e3}
 
     def prefill_timed(tokens, repeats=3):
-        eng, _, rng = make_engine(1)
+        eng, _, rng = make_engine(1, max(args.context, tokens + 64))   # a context shorter than the prompt: room for it
         best = None
         for r in range(repeats + 1):            # the first run is the warm-up
             rid = f"p{r}"
