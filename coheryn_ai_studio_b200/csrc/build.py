@@ -29,7 +29,8 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompil
 
 # The core library: everything that is not specialised by a compile-time size.
 CORE_SOURCES = ["runtime.cu", "elementwise.cu", "gemm_simt.cu", "attention_simple.cu",
-                "sampling.cu", "gemm_bf16_small.cu", "gemm_tc.cu", "gemm_tc_few.cu", "seeded_fill.cu", "selftest.cu"]
+                "sampling.cu", "gemm_bf16_small.cu", "gemm_tc.cu", "gemm_tc_few.cu", "seeded_fill.cu", "selftest.cu",
+                "block_runner.cu"]
 HEADERS = ["common.cuh"]
 
 

@@ -747,6 +747,16 @@ ATTN_OPROJ_M = int(os.environ.get("COHERYN_ATTN_OPROJ_M", "16"))
 ATTN_OPROJ_MERGE_BYTES = int(os.environ.get("COHERYN_ATTN_OPROJ_BYTES", str(32 << 20)))
 
 
+# Whether a pre-norm block made of the built-in parts is enqueued by one call into the library
+# (csrc/block_runner.cu) instead of part by part; the kernels and their order are the same.
+NATIVE_BLOCK = os.environ.get("COHERYN_NATIVE_BLOCK", "1") != "0"
+
+
+def set_native_block(on: bool) -> None:
+    global NATIVE_BLOCK
+    NATIVE_BLOCK = bool(on)
+
+
 def attention_oproj_ok(q: torch.Tensor, w_o: torch.Tensor, step, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
     if step.max_kv_len is None or step.max_q_len != 1:
         return False

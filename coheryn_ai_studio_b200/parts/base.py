@@ -104,6 +104,9 @@ class StepContext:
     # kernels.  False for the context of the wanted rows (``tail``): its one-token "requests" look
     # back on keys and values that this same step has just written.
     prior_positions_settled: bool = True
+    # Scratch of parts/native_block.py: what the blocks of this step share once the first of them
+    # has described the step to the library.
+    native: Optional[object] = None
 
 
 # ------------------------------------------------------------------------------- parts

@@ -11,6 +11,7 @@ from typing import Dict
 
 from .. import ops
 from .base import Arrangement, Part, register_arrangement
+from .native_block import NativeBlock
 
 
 class PreNormResidual(Arrangement):
@@ -20,7 +21,21 @@ class PreNormResidual(Arrangement):
         return {"input_layernorm": self.mixer_norm, "self_attn": self.mixer,
                 "post_attention_layernorm": self.feed_forward_norm, "mlp": self.feed_forward}
 
+    _native = None     # None: not looked at yet; False: not made of the built-in parts
+
+    def _native_block(self):
+        nb = self._native
+        if nb is None or (nb is not False and not nb.current(self)):
+            nb = self._native = NativeBlock.build(self) or False
+        return nb
+
     def forward(self, residual, delta, step, cache):
+        if ops.NATIVE_BLOCK:
+            nb = self._native_block()
+            if nb:
+                out = nb.run(residual, delta, step, cache)   # the whole block from one call into the library
+                if out is not None:
+                    return residual, out
         mixed = self.mixer.forward(self.mixer_norm.forward(residual, delta), step, cache)
         out = self.feed_forward.forward(self.feed_forward_norm.forward(residual, mixed), step)
         return residual, out

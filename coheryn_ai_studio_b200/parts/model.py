@@ -109,6 +109,7 @@ class DecoderModel:
         """Run the step's tokens through the schedule; return float32 logits
         ``[len(logit_rows), vocab]`` of the rows asked for."""
         T, H = step.num_tokens, self.spec.hidden_size
+        step.native = None      # a step object may be run again (warm-up, then capture): on another stream
         residual = torch.empty((T, H), dtype=torch.float32, device=self.runtime.device)
         ops.embed_gather(self.embedding, step.token_ids, residual, self.status, scale=self.spec.embedding_scale)
         delta = None

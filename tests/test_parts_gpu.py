@@ -576,3 +576,50 @@ def test_describe_reports_capabilities_and_cache_cost(toy_folder):
     # four cache entries hold keys and values (three full, one windowed): 2 * kv heads * head size each
     assert caps["kv_bytes_per_token"] == {"bfloat16": 2 * 4 * 2 * 16, "float32": 4 * 4 * 2 * 16}
     assert d["attention_windows"] == [11] and d["schedule_entries"] == 6 and d["layers"] == 4
+
+
+@pytest.mark.parametrize("name", ["A_loud", "B_loud"])
+def test_block_enqueued_by_one_call_equals_the_parts_bit_for_bit(tmp_path, name):
+    """A block of the built-in parts in bfloat16 is enqueued by one call into the library
+    (csrc/block_runner.cu), which chooses the kernels as ops.py does; so its logits equal, bit for
+    bit, those of the parts run one by one: whole prompts of many lengths (every row wanted), requests
+    decoding together, decoded tokens beside prompt portions.  float32 keeps the parts' own path."""
+    import tiny
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.engine import Engine, StepEntry
+    from coheryn_ai_studio_b200.parts import native_block
+    folder = tiny.make_folder(tmp_path, name)
+    cfg = tiny.CONFIGS[name][0]
+    context = min(256, cfg.max_position_embeddings)
+
+    def run(native, dtype="bfloat16"):
+        ops.set_native_block(native)
+        try:
+            eng = Engine.from_folder(folder, dtype, context=context, max_num_seqs=4, page_size=16, use_graphs=False)
+            before = native_block.runs
+            outs = []
+            for n in (1, 2, 5, 16, 17, 33, 40, 64, 70, 130, 200):
+                eng.cache.admit(f"w{n}")
+                outs.append(eng.runner.step([StepEntry(f"w{n}", tiny.prompt(n, n, cfg.vocab_size), list(range(n)))]).clone())
+                eng.cache.free(f"w{n}")
+            for i, n in enumerate((30, 7, 90)):
+                eng.cache.admit(f"r{i}")
+                outs.append(eng.runner.step([StepEntry(f"r{i}", tiny.prompt(100 + i, n, cfg.vocab_size), [n - 1])]).clone())
+            for t in range(3):
+                outs.append(eng.runner.step([StepEntry(f"r{i}", [3 + 5 * t + i], [0]) for i in range(3)]).clone())
+            eng.cache.admit("m")
+            outs.append(eng.runner.step([StepEntry("r0", [9], [0]), StepEntry("m", tiny.prompt(5, 21, cfg.vocab_size), list(range(21))),
+                                         StepEntry("r2", [11, 12], [0, 1])]).clone())
+            eng.runner.check_status()
+            return outs, native_block.runs - before, eng.model.layers[0]._native
+        finally:
+            ops.set_native_block(True)
+
+    parts, none_native, _ = run(False)
+    whole, some_native, described = run(True)
+    assert none_native == 0 and some_native >= len(whole) * (cfg.num_hidden_layers - 1)
+    assert isinstance(described, native_block.NativeBlock)
+    for k, (a, b) in enumerate(zip(parts, whole)):
+        assert torch.isfinite(b).all() and torch.equal(a, b), k
+    _, in_float32, described = run(True, "float32")
+    assert in_float32 == 0 and described is False
