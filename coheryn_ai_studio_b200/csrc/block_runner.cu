@@ -148,6 +148,8 @@ struct Router {
 struct Arena {
   char* base;
   size_t off;
+  void* workspace = nullptr;      // one area for the K slices of whichever many-rows product is running
+  long workspace_floats = 0;
   void* take(size_t bytes) {
     off = (off + 255) & ~(size_t)255;
     void* p = base ? (void*)(base + off) : nullptr;
@@ -197,7 +199,8 @@ int run_linear(Route route, Arena& A, bool launch, const CoBlockStep& S, const v
       return 0;
     case R_TC: {
       const long floats = coheryn_gemm_tc_workspace_floats(M, N, K);     // > 0: K is split
-      float* ws = floats ? (float*)A.take((size_t)floats * 4) : nullptr;
+      float* ws = floats ? (float*)A.workspace : nullptr;                 // consumed before the call returns its stream
+      if (floats > A.workspace_floats) return CO_BLOCK_UNSUPPORTED;
       RUN(coheryn_gemm_bf16_tc(x, w, bias, bd, out, CO_BF16, M, N, K, ldx, ldo, epilogue, S.tc_status, ws, floats,
                                S.stream));
       return 0;
@@ -215,6 +218,19 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
   const Router R{tn};
   Arena A{scratch, 0};
   cudaStream_t stream = S.stream;
+
+  // The many-rows product adds its K slices with a kernel of its own before the next product starts:
+  // the four products share one area for them.
+  {
+    long f = coheryn_gemm_tc_workspace_floats(T, Nqkv, H);
+    const long f2 = coheryn_gemm_tc_workspace_floats(T, H, Nq), f3 = coheryn_gemm_tc_workspace_floats(T, 2 * I, H),
+               f4 = coheryn_gemm_tc_workspace_floats(T, H, I);
+    f = f > f2 ? f : f2;
+    f = f > f3 ? f : f3;
+    f = f > f4 ? f : f4;
+    A.workspace_floats = f;
+    A.workspace = f ? A.take((size_t)f * 4) : nullptr;
+  }
 
   // x^ = norm(residual += delta)
   void* xn = A.take((size_t)T * H * 2);
@@ -309,8 +325,8 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
     mixed = mb;
   }
 
-  // x^ = norm(residual += mixer output)
-  void* xn2 = A.take((size_t)T * H * 2);
+  // x^ = norm(residual += mixer output), where the first one was: the q/k/v product has consumed that
+  void* xn2 = xn;
   if (mixed_kind == 2)
     RUN(coheryn_add_parts_rmsnorm(io.resid, (const float*)mixed, mixed_splits, (long)T * H, nullptr, L.norm2_w,
                                   L.norm2_wdtype, L.eps2, xn2, CO_BF16, T, H, 1, stream));
