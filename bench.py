@@ -20,7 +20,10 @@ baseline names instead (their own JSON line, through ``Engine.generate``): conti
 batching of 64 requests at the 7B layer sizes (prompts uniform in [128, 2048], 256 output
 tokens each, context 8,192, pages of 16), and a 16,384-token context at the 14B layer sizes
 whose prefix 8 requests share (prefill in 2,048-token portions, prefix pages reused), then
-decoding at batch 8.
+decoding at batch 8.  ``--workload chat-1.5b`` is this repository's own: 256 short requests at the
+1.5B layer sizes (prompts uniform in [16, 256], 16 to 128 output tokens each, at most 32 running), so
+that requests end and begin all the time and many steps carry a new prompt beside decoded tokens,
+which no graph replays: it measures what such steps cost the host.
 """
 from __future__ import annotations
 
@@ -135,14 +138,16 @@ class ClockSampler:
 
 
 def other_workload(args) -> int:
-    """configs[3] (serving-7b) or configs[4] (long-14b) of the baseline through Engine.generate."""
+    """configs[3] (serving-7b) or configs[4] (long-14b) of the baseline through Engine.generate, or the
+    short-request workload of this repository (chat-1.5b) through Engine.add_request / step."""
     import numpy as np
     import torch
 
     from coheryn_ai_studio_b200.config import Qwen2Config
     from coheryn_ai_studio_b200.engine import Engine, random_model_on_device
     serving = args.workload == "serving-7b"
-    sizes = dict(SIZES_7B if serving else SIZES_14B)
+    chat = args.workload == "chat-1.5b"
+    sizes = dict(SIZES if chat else SIZES_7B if serving else SIZES_14B)
     full_layers = sizes["num_hidden_layers"]
     if args.layers != SIZES["num_hidden_layers"]:
         sizes["num_hidden_layers"] = args.layers
@@ -150,7 +155,32 @@ def other_workload(args) -> int:
     model = random_model_on_device(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     rng = np.random.default_rng(0)
     V = cfg.vocab_size
-    if serving:
+    if chat:
+        eng = Engine(model, context=1024, max_num_seqs=32, max_num_batched_tokens=2048, page_size=16,
+                     kv_cache_tokens=32 * 448, prefix_reuse=False, use_graphs=not args.no_graphs)
+        prompts = [rng.integers(0, V, int(n)).tolist() for n in rng.integers(16, 257, 256)]
+        outs = [int(n) for n in rng.integers(16, 129, 256)]
+
+        def run_all():
+            ids = [eng.add_request(p, n) for p, n in zip(prompts, outs)]
+            steps = 0
+            while eng.scheduler.has_work():
+                eng.step()
+                steps += 1
+            return [eng.result(rid) for rid in ids], steps
+        run_all()                                          # untimed: compilation, a graph per batch width met
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res, steps = run_all()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        out_tokens = sum(r.completion_tokens for r in res)
+        line = {"metric": "serving_output_tokens_per_s", "value": round(out_tokens / dt, 1), "unit": "tok/s",
+                "seconds": round(dt, 3), "prompt_tokens": sum(len(p) for p in prompts), "output_tokens": out_tokens,
+                "steps": steps, "ms_per_step": round(dt / steps * 1e3, 3),
+                "preemptions": eng.scheduler.stats["preemptions"]}
+        what = "Qwen2.5-1.5B layer sizes, 256 requests, prompts uniform[16,256], 16..128 outputs, 32 running, page 16"
+    elif serving:
         eng = Engine(model, context=8192, max_num_seqs=64, max_num_batched_tokens=2048, page_size=16,
                      kv_cache_tokens=64 * 2400, prefix_reuse=False, use_graphs=not args.no_graphs)
         prompts = [rng.integers(0, V, int(n)).tolist() for n in rng.integers(128, 2049, 64)]
@@ -263,7 +293,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b"],
                     help="decode: the contract's line (default); the others: see the header")
     ap.add_argument("--timeline-raw", action="store_true", help="with --timeline: also every kernel's start and end")
     ap.add_argument("--timeline", action="store_true",
