@@ -118,3 +118,52 @@ def test_layer_sizes_against_the_plain_implementation(size):
               + f", {worst:.2f} of the bound; plain {t_plain:.0f} s, total {time.time() - t0:.0f} s")
         del r
         torch.cuda.empty_cache()
+
+
+def test_block_enqueued_by_one_call_chooses_the_kernels_of_the_parts_at_real_widths():
+    """The library's one-call block (csrc/block_runner.cu) restates the choice of kernels by row count
+    that ops.py makes; only real widths reach every branch of it (K slices left to the consumer need
+    K >= 1,024, the few-rows product a weight that it does not cut).  At the 1.5B layer sizes (a small
+    vocabulary: every row's logits are compared) whole prompts on both sides of every row threshold,
+    requests decoding together (attention merged into the output projection) and decoded tokens
+    beside prompt portions give the same bits either way."""
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.engine import Engine, StepEntry, random_model_on_device
+    from coheryn_ai_studio_b200.parts import native_block
+    sizes = dict(SIZES["1.5b"], vocab_size=2048)
+    sizes.pop("layers_of_config")
+    cfg = Qwen2Config(num_hidden_layers=LAYERS, max_position_embeddings=32768, rope_theta=1e6, **sizes)
+    model = random_model_on_device(cfg, SEED)
+    V = cfg.vocab_size
+
+    def run(native):
+        ops.set_native_block(native)
+        try:
+            eng = Engine(model, context=4096, max_num_seqs=8, kv_cache_tokens=8 * 4200, prefix_reuse=False, use_graphs=False)
+            rng = np.random.default_rng(7)
+            before, outs = native_block.runs, []
+            for T in (1, 8, 16, 17, 32, 33, 64, 65, 128, 129, 256, 257, 512, 2048):
+                eng.cache.admit(f"w{T}")
+                want = list(range(T)) if T <= 256 else [T - 1]
+                outs.append((f"whole {T}", eng.runner.step([StepEntry(f"w{T}", rng.integers(0, V, T).tolist(), want)]).clone()))
+                eng.cache.free(f"w{T}")
+            for i, n in enumerate((300, 17, 1000, 64)):
+                eng.cache.admit(f"r{i}")
+                outs.append((f"prompt {i}", eng.runner.step([StepEntry(f"r{i}", rng.integers(0, V, n).tolist(), [n - 1])]).clone()))
+            for s in range(2):
+                outs.append((f"decode {s}", eng.runner.step([StepEntry(f"r{i}", [int(rng.integers(0, V))], [0])
+                                                             for i in range(4)]).clone()))
+            eng.cache.admit("m")
+            outs.append(("mixed", eng.runner.step([StepEntry("r0", [5], [0]), StepEntry("m", rng.integers(0, V, 40).tolist(), list(range(40))),
+                                                   StepEntry("r2", [9], [0])]).clone()))
+            eng.runner.check_status()
+            return outs, native_block.runs - before
+        finally:
+            ops.set_native_block(True)
+
+    parts, none = run(False)
+    whole, some = run(True)
+    assert none == 0 and some >= len(whole) * (LAYERS - 1)
+    for (name, a), (_, b) in zip(parts, whole):
+        assert torch.isfinite(b).all() and torch.equal(a, b), name
