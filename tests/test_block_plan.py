@@ -1,0 +1,88 @@
+"""The planning half of the one-call block (csrc/block_runner.cu) needs no GPU: asked for a plan only,
+it chooses routes and sizes and launches nothing.  Its choice for the block's output (bfloat16 rows, or
+float32 K slices that the next norm adds) has to be the one ``ops.linear`` makes from the same
+thresholds, at every row count and at the widths of the real configurations; thresholds changed in
+``ops`` have to reach it; a shape that no tensor-core kernel takes has to be refused, not guessed."""
+import ctypes
+
+import pytest
+import torch
+
+from coheryn_ai_studio_b200 import ops
+from coheryn_ai_studio_b200.parts import native_block as nb
+
+WIDTHS = {   # hidden, heads, kv heads, head size, intermediate
+    "0.5b": (896, 14, 2, 64, 4864), "1.5b": (1536, 12, 2, 128, 8960), "7b": (3584, 28, 4, 128, 18944),
+    "14b": (5120, 40, 8, 128, 13824)}
+
+
+class Operand:
+    """What the predicates of ops.py look at in a tensor."""
+
+    def __init__(self, rows, cols):
+        self.shape, self.dtype = (rows, cols), torch.bfloat16
+
+    def stride(self, i):
+        return self.shape[1] if i == 0 else 1
+
+    def data_ptr(self):
+        return 1 << 20
+
+    def numel(self):
+        return self.shape[0] * self.shape[1]
+
+
+def plan(width, T, B, q_len, max_kv_len, partial=True):
+    H, nh, nkv, hd, I = WIDTHS[width] if isinstance(width, str) else width
+    lib = ops.attention_lib(hd)
+    fn = lambda f: ctypes.cast(f, ctypes.c_void_p).value
+    a = 1 << 20     # a plan reads no memory: any aligned address stands for a tensor
+    layer = nb.CoBlockLayer(a, a, a, a, a, None, a, a, a, fn(lib.coheryn_attention_bf16), fn(lib.coheryn_attention_oproj_bf16),
+                            fn(lib.coheryn_attn_scratch_floats), 1e-6, 1e-6, hd ** -0.5, ops.BF16, ops.BF16, ops.BF16, ops.F32,
+                            H, nh, nkv, hd, I, hd, 0, 1, 1 if partial else 0, 1 if partial else 0)
+    step = nb.CoBlockStep(a, a, a, a, None, T, B, q_len, q_len, max_kv_len, 1)
+    tuning = nb.CoBlockTuning(ops.SMALL_WEIGHT_ELEMENTS, ops.FEW_LARGE_WEIGHT, ops.ATTN_OPROJ_MERGE_BYTES, ops.FEW_M,
+                              ops.FEW_DEFER_M, ops.FEW_HEAD_M, ops.SMALL_M, ops.SMALL_M_SHORT, ops.DEFER_MIN_K,
+                              ops.DEFER_MIN_K_WIDE, ops.QKV_ROPE_M, ops.QKV_PARTS_M, ops.QKV_PARTS_FEW_FROM, ops.ATTN_OPROJ_M)
+    out = nb.CoBlockPlan()
+    rc = nb._entry_point()(ctypes.addressof(layer), ctypes.addressof(step), ctypes.addressof(tuning), a, a, 64, 16, a, 8, a, a, None,
+                           0, 0, None, 0, 0, None, 0, 1, ctypes.addressof(out))
+    return rc, out.out_kind, out.out_splits, out.scratch_bytes
+
+
+def expected_output(T, H, I, partial):
+    """The first branch of ops.linear for the down projection (x: [T, I], w: [H, I])."""
+    x, w = Operand(T, I), Operand(H, I)
+    if (partial and I >= (ops.DEFER_MIN_K_WIDE if T > ops.SMALL_M_SHORT else ops.DEFER_MIN_K)
+            and ops._few_shape_ok(x, w, ops.FEW_DEFER_M) and ops.few_splits(H, I) > 1):
+        return 2, ops.few_splits(H, I)
+    return 1, 1
+
+
+@pytest.mark.parametrize("width", sorted(WIDTHS))
+def test_the_plan_gives_the_output_that_ops_linear_would(width):
+    H, _, _, _, I = WIDTHS[width]
+    for T in list(range(1, 140)) + [255, 256, 257, 511, 512, 1000, 2048]:
+        for partial in (True, False):
+            rc, kind, splits, scratch = plan(width, T, 1, T, T, partial)
+            assert rc == 0, (T, partial)
+            want = expected_output(T, H, I, partial)
+            assert (kind, splits if kind == 2 else 1) == want, (T, partial)
+            assert scratch >= T * (H + I) * 2
+    # decoding together: as many requests as rows
+    for T in (1, 4, 8, 16, 17, 64):
+        rc, kind, splits, _ = plan(width, T, T, 1, 3000)
+        assert rc == 0 and (kind, splits if kind == 2 else 1) == expected_output(T, H, I, True)
+
+
+def test_thresholds_set_in_ops_reach_the_plan(monkeypatch):
+    H, _, _, _, I = WIDTHS["1.5b"]
+    assert plan("1.5b", 8, 8, 1, 2000)[1] == 2          # eight rows: the down projection leaves its K slices
+    monkeypatch.setattr(ops, "FEW_DEFER_M", 0)
+    assert plan("1.5b", 8, 8, 1, 2000)[1] == 1
+    assert expected_output(8, H, I, True) == (1, 1)
+
+
+def test_a_width_no_tensor_core_kernel_takes_is_refused():
+    rc, *_ = plan((100, 5, 1, 16, 36), 40, 1, 40, 40)     # a width of 100: rows that are no multiple of 16 bytes
+    assert rc == nb.UNSUPPORTED
