@@ -94,9 +94,15 @@ struct CoBlockTuning {
 };
 
 // What the block's output is: kind 1 = bfloat16 [T, H]; 2 = float32 [splits, T, H].
+// The rest says which way each step of the block goes (tests compare it with ops.py's predicates):
+// qkv_route 1 = rotation in the product's epilogue, 2 = K slices of the few-rows product added by the
+// rotation kernel, 3 = those of the many-rows product, 4 = product (qkv_linear) then rotation; merged = 1
+// when attention is merged into the output projection, else o_route; the products' routes are
+// 1 few rows, 2 few rows with the K slices left to the consumer, 3 small, 4 many rows.
 struct CoBlockPlan {
   long scratch_bytes;
   int out_kind, out_splits;
+  int qkv_route, qkv_parts, qkv_linear, merged, o_route, gate_route, down_route;
 };
 
 #define CO_BLOCK_UNSUPPORTED 3    // nothing was launched: run the parts one by one
@@ -246,7 +252,11 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
   const void* q;
   long q_stride;
   const bool whole_head = L.rot == hd && hd % 16 == 0 && R.operands_ok(H, H, xn, L.w_qkv);
+  plan->qkv_parts = 0;
+  plan->qkv_linear = R_NONE;
+  plan->o_route = R_NONE;
   if (whole_head && T <= tn.qkv_rope_m) {
+    plan->qkv_route = 1;
     void* qb = A.take((size_t)T * Nq * 2);
     RUN(coheryn_qkv_rope_bf16_small(xn, L.w_qkv, L.b_qkv, L.b_qkv ? L.b_qkv_dtype : CO_F32, qb, Nq, S.positions, L.cos_sin,
                                     io.slots, io.k_cache, io.v_cache, T, H, H, nh, nkv, hd, io.page_size, stream));
@@ -258,6 +268,8 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
       const int few = coheryn_gemm_tc_few_splits(Nqkv, H);
       count = (few > 1 && tn.qkv_parts_few_from < T && T <= tn.few_defer_m) ? few : coheryn_gemm_tc_parts_count(T, Nqkv, H);
     }
+    plan->qkv_parts = count > 1 ? count : 0;
+    plan->qkv_route = count > 1 ? (count == coheryn_gemm_tc_few_splits(Nqkv, H) ? 2 : 3) : 4;
     if (count > 1) {
       float* parts = (float*)A.take((size_t)count * T * Nqkv * 4);
       if (count == coheryn_gemm_tc_few_splits(Nqkv, H))
@@ -275,6 +287,7 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
       void* qkv = A.take((size_t)T * Nqkv * 2);
       int splits;
       const Route r = R.linear(T, Nqkv, H, H, xn, L.w_qkv, false, &splits);
+      plan->qkv_linear = r;
       const int rc = run_linear(r, A, launch, S, xn, H, L.w_qkv, L.b_qkv, L.b_qkv_dtype, qkv, T, Nqkv, H, Nqkv, 0);
       if (rc) return rc;
       RUN(coheryn_rope_kv_write(qkv, CO_BF16, S.positions, L.cos_sin, io.slots, io.k_cache, io.v_cache, T, nh, nkv, hd,
@@ -293,6 +306,7 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
   const bool merged = L.mixer_partial && S.max_q_len == 1 && merge_bytes <= tn.attn_oproj_merge_bytes &&
                       B <= (tn.attn_oproj_m < 16 ? tn.attn_oproj_m : 16) && T == B && G <= 16 &&
                       (S.max_kv_len + 127) / 128 + 1 <= 512 && aligned16(q) && Nq % 8 == 0 && aligned16(L.w_o) && H % 4 == 0;
+  plan->merged = merged ? 1 : 0;
   if (merged) {
     const long floats = L.attn_scratch_floats(B, nkv, S.max_kv_len);
     float* as = (float*)A.take((size_t)floats * 4);
@@ -318,6 +332,7 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
                               B, nh, nkv, io.page_size, L.window, L.scale, max_rows, any_small, any_large, S.max_kv_len, as,
                               floats, S.tc_status, T, io.num_pages, S.settled, stream));
     const Route r = R.linear(T, H, Nq, Nq, o, L.w_o, L.mixer_partial != 0, &mixed_splits);
+    plan->o_route = r;
     mixed_kind = r == R_FEW_DEFER ? 2 : 1;
     void* mb = A.take(mixed_kind == 2 ? (size_t)mixed_splits * T * H * 4 : (size_t)T * H * 2);
     const int rc = run_linear(r, A, launch, S, o, Nq, L.w_o, L.b_o, L.b_o_dtype, mb, T, H, Nq, H, 0);
@@ -340,10 +355,12 @@ int block_pass(const CoBlockLayer& L, const CoBlockStep& S, const CoBlockTuning&
   if (R.few_ok(T, 2 * I, H, H, xn2, L.w_gate_up)) gr = R_FEW;
   else if (R.small_ok(T, 2 * I, H, H, xn2, L.w_gate_up)) gr = R_SMALL;
   else if (R.tc_ok(T, H, H, xn2, L.w_gate_up)) gr = R_TC;
+  plan->gate_route = gr;
   int rc = run_linear(gr, A, launch, S, xn2, H, L.w_gate_up, nullptr, CO_F32, act, T, 2 * I, H, I, L.gated_code);
   if (rc) return rc;
   int out_splits;
   const Route dr = R.linear(T, H, I, I, act, L.w_down, L.ff_partial != 0, &out_splits);
+  plan->down_route = dr;
   rc = run_linear(dr, A, launch, S, act, I, L.w_down, nullptr, CO_F32, io.out, T, H, I, H, 0);
   if (rc) return rc;
   plan->out_kind = dr == R_FEW_DEFER ? 2 : 1;

@@ -43,7 +43,8 @@ class CoBlockTuning(ctypes.Structure):
 
 
 class CoBlockPlan(ctypes.Structure):
-    _fields_ = [("scratch_bytes", c_long), ("out_kind", c_int), ("out_splits", c_int)]
+    _fields_ = [("scratch_bytes", c_long), ("out_kind", c_int), ("out_splits", c_int)] + \
+               [(n, c_int) for n in ("qkv_route", "qkv_parts", "qkv_linear", "merged", "o_route", "gate_route", "down_route")]
 
 
 UNSUPPORTED, ATTENTION_FAILED = 3, 2

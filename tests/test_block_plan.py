@@ -31,8 +31,11 @@ class Operand:
     def numel(self):
         return self.shape[0] * self.shape[1]
 
+    def is_contiguous(self):
+        return True
 
-def plan(width, T, B, q_len, max_kv_len, partial=True):
+
+def plan(width, T, B, q_len, max_kv_len, partial=True, shortest=None):
     H, nh, nkv, hd, I = WIDTHS[width] if isinstance(width, str) else width
     lib = ops.attention_lib(hd)
     fn = lambda f: ctypes.cast(f, ctypes.c_void_p).value
@@ -40,14 +43,71 @@ def plan(width, T, B, q_len, max_kv_len, partial=True):
     layer = nb.CoBlockLayer(a, a, a, a, a, None, a, a, a, fn(lib.coheryn_attention_bf16), fn(lib.coheryn_attention_oproj_bf16),
                             fn(lib.coheryn_attn_scratch_floats), 1e-6, 1e-6, hd ** -0.5, ops.BF16, ops.BF16, ops.BF16, ops.F32,
                             H, nh, nkv, hd, I, hd, 0, 1, 1 if partial else 0, 1 if partial else 0)
-    step = nb.CoBlockStep(a, a, a, a, None, T, B, q_len, q_len, max_kv_len, 1)
+    step = nb.CoBlockStep(a, a, a, a, None, T, B, shortest or q_len, q_len, max_kv_len, 1)
     tuning = nb.CoBlockTuning(ops.SMALL_WEIGHT_ELEMENTS, ops.FEW_LARGE_WEIGHT, ops.ATTN_OPROJ_MERGE_BYTES, ops.FEW_M,
                               ops.FEW_DEFER_M, ops.FEW_HEAD_M, ops.SMALL_M, ops.SMALL_M_SHORT, ops.DEFER_MIN_K,
                               ops.DEFER_MIN_K_WIDE, ops.QKV_ROPE_M, ops.QKV_PARTS_M, ops.QKV_PARTS_FEW_FROM, ops.ATTN_OPROJ_M)
     out = nb.CoBlockPlan()
     rc = nb._entry_point()(ctypes.addressof(layer), ctypes.addressof(step), ctypes.addressof(tuning), a, a, 64, 16, a, 8, a, a, None,
                            0, 0, None, 0, 0, None, 0, 1, ctypes.addressof(out))
+    plan.last = out
     return rc, out.out_kind, out.out_splits, out.scratch_bytes
+
+
+FEW, FEW_DEFER, SMALL, MANY = 1, 2, 3, 4     # the products' routes as the plan numbers them
+
+
+def linear_route(M, N, K, partial):
+    """The if-chain of ops.linear over ops.py's own predicates."""
+    x, w = Operand(M, K), Operand(N, K)
+    if (partial and K >= (ops.DEFER_MIN_K_WIDE if M > ops.SMALL_M_SHORT else ops.DEFER_MIN_K)
+            and ops._few_shape_ok(x, w, ops.FEW_DEFER_M) and ops.few_splits(N, K) > 1):
+        return FEW_DEFER
+    return FEW if ops._few_ok(x, w) else SMALL if ops._small_ok(x, w) else MANY if ops._tc_ok(x, w) else 0
+
+
+class StepFacts:
+    def __init__(self, B, q_len, max_kv_len):
+        self.num_requests, self.max_q_len, self.max_kv_len = B, q_len, max_kv_len
+
+
+def expected_routes(width, T, B, q_len, max_kv_len, partial):
+    H, nh, nkv, hd, I = WIDTHS[width]
+    Nq, Nqkv = nh * hd, (nh + 2 * nkv) * hd
+    x, w_qkv, k_cache = Operand(T, H), Operand(Nqkv, H), Operand(1, 1)
+    want = {}
+    if ops.qkv_rope_ok(x, w_qkv, k_cache, hd, hd):
+        want["qkv_route"] = 1
+    else:
+        count = ops.qkv_parts_count(x, w_qkv, k_cache, hd, hd)
+        if count > 1:
+            want["qkv_route"], want["qkv_parts"] = (2 if count == ops.few_splits(Nqkv, H) else 3), count
+        else:
+            want["qkv_route"], want["qkv_linear"] = 4, linear_route(T, Nqkv, H, False)
+    merged = partial and ops.attention_oproj_ok(Operand(T, Nq), Operand(H, Nq), StepFacts(B, q_len, max_kv_len), nh, nkv, hd)
+    want["merged"] = 1 if merged else 0
+    if not merged:
+        want["o_route"] = linear_route(T, H, Nq, partial)
+    x2, w_gu = Operand(T, H), Operand(2 * I, H)
+    want["gate_route"] = FEW if ops._few_ok(x2, w_gu) else SMALL if ops._small_ok(x2, w_gu) else MANY if ops._tc_ok(x2, w_gu) else 0
+    want["down_route"] = linear_route(T, H, I, partial)
+    return want
+
+
+@pytest.mark.parametrize("width", sorted(WIDTHS))
+def test_every_step_of_the_plan_goes_the_way_ops_would_send_it(width):
+    cases = [(T, 1, T, T) for T in list(range(1, 140)) + [255, 256, 257, 300, 512, 2048]]     # a prompt portion
+    cases += [(T, T, 1, kv) for T in (1, 2, 8, 16, 17, 32, 64, 128) for kv in (500, 4096, 32768)]   # decoding together
+    cases += [(40, 3, 1, 900), (70, 5, 1, 3000)]      # decoded tokens beside a portion (the shortest run is one token)
+    for T, B, q_len, kv in cases:
+        for partial in (True, False):
+            longest = q_len if B in (1, T) else T - B + 1      # mixed: one request brings all the other tokens
+            rc = plan(width, T, B, longest, kv, partial, shortest=q_len)[0]
+            nb_plan = plan.last
+            want = expected_routes(width, T, B, longest, kv, partial)
+            assert rc == 0, (T, B, partial)
+            got = {k: getattr(nb_plan, k) for k in want}
+            assert got == want, (T, B, kv, partial)
 
 
 def expected_output(T, H, I, partial):
