@@ -205,7 +205,7 @@ int run_linear(Route route, Arena& A, bool launch, const CoBlockStep& S, const v
       return 0;
     case R_TC: {
       const long floats = coheryn_gemm_tc_workspace_floats(M, N, K);     // > 0: K is split
-      float* ws = floats ? (float*)A.workspace : nullptr;                 // consumed before the call returns its stream
+      float* ws = floats ? (float*)A.workspace : nullptr;      // the kernel that adds the slices follows in the same call
       if (floats > A.workspace_floats) return CO_BLOCK_UNSUPPORTED;
       RUN(coheryn_gemm_bf16_tc(x, w, bias, bd, out, CO_BF16, M, N, K, ldx, ldo, epilogue, S.tc_status, ws, floats,
                                S.stream));
