@@ -77,7 +77,7 @@ class StepFacts:
 
 
 def expected_routes(width, T, B, q_len, max_kv_len, partial):
-    H, nh, nkv, hd, I = WIDTHS[width]
+    H, nh, nkv, hd, I = WIDTHS[width] if isinstance(width, str) else width
     Nq, Nqkv = nh * hd, (nh + 2 * nkv) * hd
     x, w_qkv, k_cache = Operand(T, H), Operand(Nqkv, H), Operand(1, 1)
     want = {}
@@ -151,3 +151,27 @@ def test_thresholds_set_in_ops_reach_the_plan(monkeypatch):
 def test_a_width_no_tensor_core_kernel_takes_is_refused():
     rc, *_ = plan((100, 5, 1, 16, 36), 40, 1, 40, 40)     # a width of 100: rows that are no multiple of 16 bytes
     assert rc == nb.UNSUPPORTED
+
+
+def test_random_widths_and_row_counts_go_the_same_way():
+    """Widths nobody tuned for: any hidden and intermediate size that is a multiple of 8, head sizes in
+    steps of 16, any number of heads and groups; row counts around every threshold and at random."""
+    import numpy as np
+    rng = np.random.default_rng(11)
+    for _ in range(250):
+        hd = int(rng.choice([16, 32, 48, 64, 80, 96, 128, 192, 256]))
+        nkv = int(rng.integers(1, 9))
+        nh = nkv * int(rng.integers(1, 9))
+        width = (8 * int(rng.integers(8, 1025)), nh, nkv, hd, 8 * int(rng.integers(8, 3001)))
+        rows = [1, 16, 17, 32, 33, 64, 65, 128, 129, 256, 257] + [int(t) for t in rng.integers(1, 3000, 4)]
+        for T in rows:
+            partial = bool(rng.integers(0, 2))
+            if rng.integers(0, 2):
+                B, longest, shortest, kv = 1, T, T, T + int(rng.integers(0, 5000))          # a portion
+            else:
+                B, longest, shortest, kv = T, 1, 1, int(rng.integers(1, 40000))             # decoding together
+            rc = plan(width, T, B, longest, kv, partial, shortest=shortest)[0]
+            assert rc == 0, (width, T)
+            want = expected_routes(width, T, B, longest, kv, partial)
+            got = {k: getattr(plan.last, k) for k in want}
+            assert got == want, (width, T, B, kv, partial)
